@@ -1,0 +1,112 @@
+"""ctypes binding of libbpdq.so -- the same argtypes tables the reference's callers write
+for its libraries (bench/verify_quant_gpu.py:27-42, bench/bench_gpu_sweep.py:11-20,
+bench/bench_dequant_gpu_h2h.py:5-13, inference/llamatov_gpu_llama.py:15-31), plus the
+additive status-returning entry points.
+
+There is no fallback: if the shared library is missing or cannot be loaded this module
+raises, and every compute call launches a CUDA kernel.
+"""
+import ctypes as C
+import os
+
+from . import _build
+
+_LIB = None
+
+vp, i32, sz, f32 = C.c_void_p, C.c_int, C.c_size_t, C.c_float
+
+# name -> (restype, argtypes).  Kept in one table so tests can check that the library exports
+# every symbol the header declares.
+SIGNATURES = {
+    # library state
+    "bpdq_set_stream": (None, [vp]),
+    "bpdq_get_stream": (vp, []),
+    "bpdq_last_status": (i32, []),
+    "bpdq_device_error_word": (i32, []),
+    "bpdq_clear_status": (None, []),
+    "bpdq_set_tuning": (None, [i32, i32, i32, i32]),
+    "bpdq_sm_count": (i32, []),
+    # memory (size_t)
+    "bpdq_alloc": (vp, [sz]),
+    "bpdq_free": (None, [vp]),
+    "bpdq_h2d": (None, [vp, vp, sz]),
+    "bpdq_d2h": (None, [vp, vp, sz]),
+    "bpdq_d2d": (None, [vp, vp, sz]),
+    "bpdq_h2d_async": (i32, [vp, vp, sz, vp]),
+    "bpdq_d2h_async": (i32, [vp, vp, sz, vp]),
+    "bpdq_host_alloc": (vp, [sz]),
+    "bpdq_host_free": (None, [vp]),
+    "bpdq_sync": (None, []),
+    "bpdq_stream_sync": (i32, [vp]),
+    # events, memset, streams, graphs
+    "bpdq_event_create": (vp, []),
+    "bpdq_event_destroy": (None, [vp]),
+    "bpdq_event_record": (i32, [vp, vp]),
+    "bpdq_event_elapsed_ms": (f32, [vp, vp]),
+    "bpdq_memset_async": (i32, [vp, i32, sz, vp]),
+    "bpdq_stream_create": (vp, []),
+    "bpdq_stream_destroy": (None, [vp]),
+    "bpdq_graph_begin": (i32, [vp]),
+    "bpdq_graph_end": (vp, [vp]),
+    "bpdq_graph_launch": (i32, [vp, vp]),
+    "bpdq_graph_destroy": (None, [vp]),
+    "bpdq_set_device": (i32, [i32]),
+    "bpdq_l2_bytes": (i32, []),
+    # reference memory helpers
+    **{f"{p}_alloc": (vp, [i32]) for p in ("qgpu", "sgpu", "gpu")},
+    **{f"{p}_free": (None, [vp]) for p in ("qgpu", "sgpu", "gpu")},
+    **{f"{p}_h2d": (None, [vp, vp, i32]) for p in ("qgpu", "sgpu")},
+    **{f"{p}_d2h": (None, [vp, vp, i32]) for p in ("qgpu", "sgpu")},
+    **{f"{p}_sync": (None, []) for p in ("qgpu", "sgpu", "gpu")},
+    "galloc": (vp, [i32]), "gfree": (None, [vp]), "gh2d": (None, [vp, vp, i32]),
+    "gd2h": (None, [vp, vp, i32]), "gsync": (None, []),
+    "gpu_copy_h2d": (None, [vp, vp, i32]), "gpu_copy_d2h": (None, [vp, vp, i32]),
+    "gpu_copy_d2d": (None, [vp, vp, i32]),
+    # Q4_K dequant
+    "bpd_dequant_q4k_gpu": (None, [vp, vp, i32]),
+    "bpd_dequant_q4k_gpu_st": (i32, [vp, vp, sz, i32, vp]),
+    "run_llamacpp": (None, [vp, vp, i32]),
+    "run_bpd": (None, [vp, vp, i32]),
+    **{n: (None, [vp, vp, i32]) for n in (
+        "dequant_v1_256", "dequant_v1_128", "dequant_v1_64", "dequant_v1_32",
+        "dequant_ilp2", "dequant_multi2", "dequant_multi4", "dequant_multi8")},
+    # Q4_K x Q8_K
+    "bpd_quant_q8_K_cuda": (i32, [vp, vp, sz, vp]),
+    "bpd_qmatmul_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, vp]),
+    "bpd_qmm_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
+    "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),
+    "gpu_matmul_q4k": (None, [vp, vp, vp, i32, i32, i32]),
+}
+
+
+def lib_path():
+    return _build.LIB
+
+
+def load(build_if_missing=True):
+    """Returns the bound library; raises if it cannot be built or loaded."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = lib_path()
+    if not os.path.exists(path):
+        if not build_if_missing:
+            raise FileNotFoundError(f"{path} is missing: run bpd_substrate_b200._build.build()")
+        _build.build()
+    lib = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)   # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    _LIB = lib
+    return lib
+
+
+class BpdqError(RuntimeError):
+    pass
+
+
+def check(status, what=""):
+    if status != 0:
+        raise BpdqError(f"{what or 'libbpdq call'} failed with status {status}")
+    return status

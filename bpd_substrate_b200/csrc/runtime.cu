@@ -1,0 +1,231 @@
+// Host-side runtime of the C-ABI library: stream selection, status latch, device memory
+// helpers.  This is the Python-facing replacement for the reference's SWI-Prolog launch shim
+// (lib/cuda_launch.c:39-307): the same duties (context, alloc/free, H2D/D2H, sync, launch)
+// behind plain C symbols that ctypes can bind.
+#include "bpdq_common.cuh"
+#include "../../include/bpdq.h"
+
+#include <atomic>
+#include <mutex>
+
+namespace bpdq {
+
+static std::atomic<cudaStream_t> g_stream{nullptr};
+static std::atomic<int> g_status{0};
+static Tuning g_tuning = {16384, 4, 4, 1};
+
+__device__ int g_dev_error = 0;
+
+cudaStream_t current_stream() { return g_stream.load(std::memory_order_relaxed); }
+
+int latch(int status)
+{
+    if (status != 0) {
+        int expected = 0;
+        g_status.compare_exchange_strong(expected, status);
+    }
+    return status;
+}
+
+int check_cuda(cudaError_t e)
+{
+    if (e == cudaSuccess) return 0;
+    return latch(BPDQ_ERR_CUDA - (int)e);
+}
+
+int sm_count()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int* device_error_flag()
+{
+    static int* cached[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!cached[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_dev_error) != cudaSuccess) return nullptr;
+        cached[dev] = (int*)p;
+    }
+    return cached[dev];
+}
+
+Tuning& tuning() { return g_tuning; }
+
+static void* dev_alloc(size_t bytes)
+{
+    void* p = nullptr;
+    if (check_cuda(cudaMalloc(&p, bytes ? bytes : 1)) != 0) return nullptr;
+    return p;
+}
+static void dev_free(void* p) { check_cuda(cudaFree(p)); }
+static void copy_sync(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind)
+{
+    // Ordered after work queued on the library's stream, then blocking like the reference's
+    // cudaMemcpy helpers (bench/bpd_quant_gpu.cu:172-175).
+    cudaStream_t s = current_stream();
+    if (check_cuda(cudaMemcpyAsync(dst, src, bytes, kind, s)) != 0) return;
+    check_cuda(cudaStreamSynchronize(s));
+}
+static void sync_all() { check_cuda(cudaDeviceSynchronize()); }
+
+}  // namespace bpdq
+
+using namespace bpdq;
+
+extern "C" {
+
+// ---- library state ---------------------------------------------------------------------
+void bpdq_set_stream(void* stream) { g_stream.store((cudaStream_t)stream); }
+void* bpdq_get_stream(void) { return (void*)current_stream(); }
+
+int bpdq_last_status(void)
+{
+    // Folds in the device-side error word (set when a kernel gave up on a bounded wait).
+    int* flag = device_error_flag();
+    int dev_err = 0;
+    if (flag && cudaMemcpy(&dev_err, flag, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && dev_err != 0)
+        latch(BPDQ_ERR_DEVICE);
+    return g_status.load();
+}
+int bpdq_device_error_word(void)
+{
+    int* flag = device_error_flag();
+    int dev_err = 0;
+    if (flag) cudaMemcpy(&dev_err, flag, sizeof(int), cudaMemcpyDeviceToHost);
+    return dev_err;
+}
+void bpdq_clear_status(void)
+{
+    g_status.store(0);
+    int* flag = device_error_flag();
+    if (flag) cudaMemset(flag, 0, sizeof(int));
+    (void)cudaGetLastError();
+}
+void bpdq_set_tuning(int tile_bytes, int stages, int ctas_per_sm, int pdl)
+{
+    Tuning& t = tuning();
+    if (tile_bytes > 0) t.tile_bytes = tile_bytes;
+    if (stages > 0) t.stages = stages;
+    if (ctas_per_sm > 0) t.ctas_per_sm = ctas_per_sm;
+    if (pdl >= 0) t.pdl = pdl;
+}
+int bpdq_sm_count(void) { return sm_count(); }
+
+void* bpdq_alloc(size_t bytes) { return dev_alloc(bytes); }
+void bpdq_free(void* p) { dev_free(p); }
+void bpdq_h2d(void* dev, const void* host, size_t bytes) { copy_sync(dev, host, bytes, cudaMemcpyHostToDevice); }
+void bpdq_d2h(void* host, const void* dev, size_t bytes) { copy_sync(host, dev, bytes, cudaMemcpyDeviceToHost); }
+void bpdq_d2d(void* dst, const void* src, size_t bytes) { copy_sync(dst, src, bytes, cudaMemcpyDeviceToDevice); }
+int bpdq_h2d_async(void* dev, const void* host, size_t bytes, void* stream)
+{
+    return check_cuda(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+}
+int bpdq_d2h_async(void* host, const void* dev, size_t bytes, void* stream)
+{
+    return check_cuda(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+}
+void* bpdq_host_alloc(size_t bytes)
+{
+    void* p = nullptr;
+    if (check_cuda(cudaMallocHost(&p, bytes ? bytes : 1)) != 0) return nullptr;
+    return p;
+}
+void bpdq_host_free(void* p) { check_cuda(cudaFreeHost(p)); }
+void bpdq_sync(void) { sync_all(); }
+int bpdq_stream_sync(void* stream) { return check_cuda(cudaStreamSynchronize((cudaStream_t)stream)); }
+
+// ---- events, memset, CUDA graphs (additive) -----------------------------------------------
+void* bpdq_event_create(void)
+{
+    cudaEvent_t e = nullptr;
+    if (check_cuda(cudaEventCreate(&e)) != 0) return nullptr;
+    return (void*)e;
+}
+void bpdq_event_destroy(void* ev) { if (ev) check_cuda(cudaEventDestroy((cudaEvent_t)ev)); }
+int bpdq_event_record(void* ev, void* stream) { return check_cuda(cudaEventRecord((cudaEvent_t)ev, (cudaStream_t)stream)); }
+// Waits for `stop`, then returns the milliseconds between the two events (negative on error).
+float bpdq_event_elapsed_ms(void* start, void* stop)
+{
+    if (check_cuda(cudaEventSynchronize((cudaEvent_t)stop)) != 0) return -1.0f;
+    float ms = -1.0f;
+    if (check_cuda(cudaEventElapsedTime(&ms, (cudaEvent_t)start, (cudaEvent_t)stop)) != 0) return -1.0f;
+    return ms;
+}
+int bpdq_memset_async(void* dev, int value, size_t bytes, void* stream)
+{
+    return check_cuda(cudaMemsetAsync(dev, value, bytes, (cudaStream_t)stream));
+}
+void* bpdq_stream_create(void)
+{
+    cudaStream_t s = nullptr;
+    if (check_cuda(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking)) != 0) return nullptr;
+    return (void*)s;
+}
+void bpdq_stream_destroy(void* s) { if (s) check_cuda(cudaStreamDestroy((cudaStream_t)s)); }
+
+// Capture everything launched on `stream` between begin and end into an executable graph.
+int bpdq_graph_begin(void* stream)
+{
+    return check_cuda(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+}
+void* bpdq_graph_end(void* stream)
+{
+    cudaGraph_t g = nullptr;
+    if (check_cuda(cudaStreamEndCapture((cudaStream_t)stream, &g)) != 0 || !g) return nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int rc = check_cuda(cudaGraphInstantiate(&exec, g, 0));
+    cudaGraphDestroy(g);
+    return rc == 0 ? (void*)exec : nullptr;
+}
+int bpdq_graph_launch(void* exec, void* stream)
+{
+    return check_cuda(cudaGraphLaunch((cudaGraphExec_t)exec, (cudaStream_t)stream));
+}
+void bpdq_graph_destroy(void* exec) { if (exec) check_cuda(cudaGraphExecDestroy((cudaGraphExec_t)exec)); }
+int bpdq_set_device(int dev) { return check_cuda(cudaSetDevice(dev)); }
+int bpdq_l2_bytes(void)
+{
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrL2CacheSize, dev) != cudaSuccess) return 0;
+    return n;
+}
+
+// ---- the reference's memory helpers, name for name ----------------------------------------
+// bench/bpd_quant_gpu.cu:172-176
+void* qgpu_alloc(int bytes) { return bytes < 0 ? (latch(BPDQ_ERR_ARG), nullptr) : dev_alloc((size_t)bytes); }
+void qgpu_free(void* p) { dev_free(p); }
+void qgpu_h2d(void* d, const void* s, int bytes) { if (bytes >= 0) copy_sync(d, s, (size_t)bytes, cudaMemcpyHostToDevice); else latch(BPDQ_ERR_ARG); }
+void qgpu_d2h(void* d, const void* s, int bytes) { if (bytes >= 0) copy_sync(d, s, (size_t)bytes, cudaMemcpyDeviceToHost); else latch(BPDQ_ERR_ARG); }
+void qgpu_sync(void) { sync_all(); }
+// bench/bpd_quant_gpu_sweep.cu:145-149
+void* sgpu_alloc(int bytes) { return qgpu_alloc(bytes); }
+void sgpu_free(void* p) { dev_free(p); }
+void sgpu_h2d(void* d, const void* s, int bytes) { qgpu_h2d(d, s, bytes); }
+void sgpu_d2h(void* d, const void* s, int bytes) { qgpu_d2h(d, s, bytes); }
+void sgpu_sync(void) { sync_all(); }
+// bench/bench_dequant_gpu_h2h.cu:77-81
+void* galloc(int b) { return qgpu_alloc(b); }
+void gfree(void* p) { dev_free(p); }
+void gh2d(void* d, const void* s, int b) { qgpu_h2d(d, s, b); }
+void gd2h(void* d, const void* s, int b) { qgpu_d2h(d, s, b); }
+void gsync(void) { sync_all(); }
+// generators/generate_llama_kernels.pl:32-60
+void* gpu_alloc(int bytes) { return qgpu_alloc(bytes); }
+void gpu_free(void* p) { dev_free(p); }
+void gpu_copy_h2d(void* d, const void* h, int b) { qgpu_h2d(d, h, b); }
+void gpu_copy_d2h(void* h, const void* d, int b) { qgpu_d2h(h, d, b); }
+void gpu_copy_d2d(void* dst, const void* src, int b) { if (b >= 0) copy_sync(dst, src, (size_t)b, cudaMemcpyDeviceToDevice); else latch(BPDQ_ERR_ARG); }
+void gpu_sync(void) { sync_all(); }
+
+}  // extern "C"

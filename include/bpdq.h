@@ -1,0 +1,142 @@
+/* bpdq.h -- C ABI of libbpdq.so: B200 (sm_100a) kernels for BPD's quantized-inference path.
+ *
+ * Every function is plain C: raw pointers and sizes, no C++ or torch types.  "device"
+ * pointers are CUDA device addresses (from the *_alloc helpers below, or from any other
+ * allocator in the same process, e.g. a torch tensor's data_ptr()).
+ *
+ * Two kinds of entry point:
+ *   1. Drop-ins with the reference's own names and signatures (void return, int sizes).  They
+ *      launch on the library's current stream (bpdq_set_stream; default: the legacy default
+ *      stream, as in the reference) and latch any error for bpdq_last_status().
+ *   2. Additive *_st / *_cuda forms that return a status (0 = ok, negative = error, see the
+ *      BPDQ_ERR_* list), take size_t sizes where an int would overflow, and an explicit
+ *      stream (a cudaStream_t passed as void*).
+ *
+ * There is no CPU fallback anywhere: every compute entry launches a CUDA kernel.
+ *
+ * Each declaration names the reference interface it replaces (path:line inside
+ * heath-hunnicutt-ruach-tov/bpd-substrate).
+ */
+#ifndef BPDQ_H
+#define BPDQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes */
+#define BPDQ_STATUS_OK 0
+#define BPDQ_STATUS_ERR_ARG (-1)     /* null pointer, negative size, K not a block multiple */
+#define BPDQ_STATUS_ERR_ALIGN (-2)   /* pointer not aligned as the kernel needs (16 B for weights) */
+#define BPDQ_STATUS_ERR_RANGE (-3)   /* shape beyond what the kernel supports */
+#define BPDQ_STATUS_ERR_DEVICE (-4)  /* a kernel gave up on a bounded wait */
+#define BPDQ_STATUS_ERR_CUDA (-1000) /* minus the cudaError_t value */
+
+/* ---- library state (additive; the reference keeps none) ------------------------------ */
+void bpdq_set_stream(void* cuda_stream);   /* stream used by the void drop-ins */
+void* bpdq_get_stream(void);
+int bpdq_last_status(void);                /* first error since the last clear (synchronizes) */
+int bpdq_device_error_word(void);
+void bpdq_clear_status(void);
+void bpdq_set_tuning(int tile_bytes, int stages, int ctas_per_sm, int pdl); /* <=0 / <0 keeps a field */
+int bpdq_sm_count(void);
+
+/* ---- device memory helpers (additive, size_t) ------------------------------------------ */
+void* bpdq_alloc(size_t bytes);
+void bpdq_free(void* dev);
+void bpdq_h2d(void* dev, const void* host, size_t bytes);
+void bpdq_d2h(void* host, const void* dev, size_t bytes);
+void bpdq_d2d(void* dst, const void* src, size_t bytes);
+int bpdq_h2d_async(void* dev, const void* host, size_t bytes, void* stream);
+int bpdq_d2h_async(void* host, const void* dev, size_t bytes, void* stream);
+void* bpdq_host_alloc(size_t bytes);       /* pinned host memory */
+void bpdq_host_free(void* host);
+void bpdq_sync(void);
+int bpdq_stream_sync(void* stream);
+
+/* ---- events, memset, streams, CUDA graphs (additive) ------------------------------------ */
+void* bpdq_event_create(void);
+void bpdq_event_destroy(void* ev);
+int bpdq_event_record(void* ev, void* stream);
+float bpdq_event_elapsed_ms(void* start, void* stop);  /* waits for stop */
+int bpdq_memset_async(void* dev, int value, size_t bytes, void* stream);
+void* bpdq_stream_create(void);
+void bpdq_stream_destroy(void* stream);
+int bpdq_graph_begin(void* stream);        /* start capturing launches made on stream */
+void* bpdq_graph_end(void* stream);        /* -> executable graph handle, NULL on error */
+int bpdq_graph_launch(void* graph, void* stream);
+void bpdq_graph_destroy(void* graph);
+int bpdq_set_device(int device);
+int bpdq_l2_bytes(void);
+
+/* ---- reference memory helpers, name for name ------------------------------------------- */
+/* bench/bpd_quant_gpu.cu:172-176 (first argument of h2d/d2h is the destination) */
+void* qgpu_alloc(int bytes);
+void qgpu_free(void* p);
+void qgpu_h2d(void* dev, const void* host, int bytes);
+void qgpu_d2h(void* host, const void* dev, int bytes);
+void qgpu_sync(void);
+/* bench/bpd_quant_gpu_sweep.cu:145-149 */
+void* sgpu_alloc(int bytes);
+void sgpu_free(void* p);
+void sgpu_h2d(void* dev, const void* host, int bytes);
+void sgpu_d2h(void* host, const void* dev, int bytes);
+void sgpu_sync(void);
+/* bench/bench_dequant_gpu_h2h.cu:77-81 */
+void* galloc(int bytes);
+void gfree(void* p);
+void gh2d(void* dev, const void* host, int bytes);
+void gd2h(void* host, const void* dev, int bytes);
+void gsync(void);
+/* generators/generate_llama_kernels.pl:32-60 */
+void* gpu_alloc(int bytes);
+void gpu_free(void* p);
+void gpu_copy_h2d(void* dev, const void* host, int bytes);
+void gpu_copy_d2h(void* host, const void* dev, int bytes);
+void gpu_copy_d2d(void* dst, const void* src, int bytes);
+void gpu_sync(void);
+
+/* ---- Q4_K dequantization (device pointers) --------------------------------------------- */
+/* bench/bpd_quant_gpu.cu:162-164 -- 144-byte super-blocks -> 256 floats each, the nibble
+ * order of bench/bpd_quant.c:68-72.  Bit-exact with bpd_dequant_q4k (bench/bpd_quant.c:77). */
+void bpd_dequant_q4k_gpu(const uint8_t* qdata, float* output, int n_blocks);
+/* layout 0 = that order, 1 = the ggml order of bench/bench_dequant_gpu_h2h.cu:35-46 */
+int bpd_dequant_q4k_gpu_st(const uint8_t* qdata, float* output, size_t n_blocks, int layout, void* stream);
+/* bench/bench_dequant_gpu_h2h.cu:74-76 (ggml nibble order, both names) */
+void run_llamacpp(const void* q, float* out, int nb);
+void run_bpd(const void* q, float* out, int nb);
+/* bench/bpd_quant_gpu_sweep.cu:134-143 -- the launch-shape study; unlike the reference's
+ * v1_128/64/32 every shape here writes all 256 outputs of every block. */
+void dequant_v1_256(const uint8_t* q, float* out, int nb);
+void dequant_v1_128(const uint8_t* q, float* out, int nb);
+void dequant_v1_64(const uint8_t* q, float* out, int nb);
+void dequant_v1_32(const uint8_t* q, float* out, int nb);
+void dequant_ilp2(const uint8_t* q, float* out, int nb);
+void dequant_multi2(const uint8_t* q, float* out, int nb);
+void dequant_multi4(const uint8_t* q, float* out, int nb);
+void dequant_multi8(const uint8_t* q, float* out, int nb);
+
+/* ---- Q4_K x Q8_K (weights 4-bit, activations quantized to 8-bit in the kernel) ---------- */
+/* No counterpart in the reference (docs/llama-kernel-audit.md:65 "Q4_K . Q8_K direct" is an
+ * unbuilt design); defined from its Q8_0 analogues bench/bpd_cpu.c:4106-4136, 4263-4280.
+ * Q8_K block = 292 B: float d, int8 qs[256], int16 bsums[16] (size: lib/gguf_emit_manifest.pl:142). */
+int bpd_quant_q8_K_cuda(const float* x, uint8_t* y, size_t n_elements, void* stream);
+/* out[M] = W[M][K] . q8K(x[K]); W in the nibble order of bench/bpd_quant.c:68-72 */
+int bpd_qmatmul_q4k_q8k_cuda(const uint8_t* qweight, const float* x, float* out, int M, int K, void* stream);
+/* out[tokens][M]; layout 0/1 as above; xsrc 0: x is float [tokens][K], 1: x is Q8_K blocks
+ * [tokens][K/256]; subdots (may be NULL): int32 [M][K/256][8], token 0's exact sub-block dots */
+int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,
+                         int xsrc, int32_t* subdots, void* stream);
+/* dispatch-shaped forms: argument order of gpu_vecmat (lib/kernel_templates_llama.pl:147-158)
+ * and gpu_matmul (lib/kernel_templates_llama.pl:1104-1112) with the fp32 [K][N] weight
+ * replaced by Q4_K rows [N][K/256][144] */
+void gpu_vecmat_q4k(const float* a, const uint8_t* wq, float* c, int k, int n);
+void gpu_matmul_q4k(const float* A, const uint8_t* wq, float* C, int M, int N, int K);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BPDQ_H */

@@ -1,0 +1,81 @@
+"""Q4_K x Q8_K GEMV / small-batch GEMM against the CPU checker, through the C ABI."""
+import numpy as np
+import pytest
+
+from bpd_substrate_b200 import synth
+from tests.util import Dev, normwise
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5  # norm-wise max|d|/max|ref| on the fp32 outputs (the stated bar for GEMV outputs)
+
+
+def run_gemm(lib, W, X, tokens, M, K, layout=0, xsrc=0, want_dots=False):
+    dW, dX = Dev(lib, W), Dev(lib, X)
+    dO = Dev(lib, nbytes=tokens * M * 4, fill=0xFF)
+    dD = Dev(lib, nbytes=M * (K // 256) * 8 * 4, fill=0xEE) if want_dots else None
+    rc = lib.bpd_qmm_q4k_q8k_cuda(dW.ptr, dX.ptr, dO.ptr, tokens, M, K, layout, xsrc,
+                                  dD.ptr if dD else None, None)
+    assert rc == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == 0
+    out = dO.read(np.float32).reshape(tokens, M)
+    dots = dD.read(np.int32).reshape(M, K // 256, 8) if dD else None
+    return out, dots
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("M,K", [(1, 256), (5, 512), (64, 4096), (37, 4096), (24, 14336), (16, 8192),
+                                 (9, 28672), (300, 1024), (2, 40960)])
+def test_gemv_matches_checker(lib, oracle, M, K, layout):
+    rng = np.random.default_rng(100 + M + K)
+    W = synth.q4k_matrix(M, K, rng)
+    x = synth.activations(K, rng)
+    out, dots = run_gemm(lib, W, x, 1, M, K, layout, want_dots=True)
+    xq = oracle.quant_q8_K(x)
+    ref32, ref64 = oracle.qmatmul_q4k_q8k(W, xq, M, K, layout)
+    # integer sub-block dots: bit-exact
+    assert np.array_equal(dots, oracle.q4k_q8k_subdots(W, xq, M, K, layout))
+    assert normwise(out[0], ref64) <= TOL
+    assert normwise(out[0], ref32) <= TOL
+
+
+@pytest.mark.parametrize("tokens", [2, 3, 4, 7])
+def test_small_batch(lib, oracle, tokens):
+    M, K = 48, 4096
+    rng = np.random.default_rng(7 + tokens)
+    W = synth.q4k_matrix(M, K, rng)
+    X = synth.activations(K, rng, rows=tokens)
+    out, _ = run_gemm(lib, W, X, tokens, M, K)
+    ref32, ref64 = oracle.qmm_q4k_q8k(W, X, tokens, M, K)
+    assert normwise(out, ref64) <= TOL
+
+
+def test_prequantized_activations_give_identical_bits(lib, oracle):
+    M, K = 40, 4096
+    rng = np.random.default_rng(5)
+    W = synth.q4k_matrix(M, K, rng)
+    x = synth.activations(K, rng)
+    out_f, _ = run_gemm(lib, W, x, 1, M, K)
+    out_q, _ = run_gemm(lib, W, oracle.quant_q8_K(x), 1, M, K, xsrc=1)
+    assert np.array_equal(out_f.view(np.uint32), out_q.view(np.uint32))
+
+
+def test_quantizer_q8_K_bytes(lib, oracle):
+    rng = np.random.default_rng(11)
+    x = synth.activations(256 * 37, rng)
+    x[256:512] = 0.0            # an all-zero block: scale 0, quants 0
+    x[1000] = 1e-30
+    dX = Dev(lib, x)
+    dY = Dev(lib, nbytes=37 * 292, fill=0xAA)
+    assert lib.bpd_quant_q8_K_cuda(dX.ptr, dY.ptr, x.size, None) == 0
+    lib.bpdq_sync()
+    assert np.array_equal(dY.read(np.uint8), oracle.quant_q8_K(x))
+
+
+def test_bad_arguments_are_rejected(lib):
+    d = Dev(lib, nbytes=4096)
+    assert lib.bpd_qmatmul_q4k_q8k_cuda(d.ptr, d.ptr, d.ptr, 4, 100, None) == -1   # K not a multiple of 256
+    assert lib.bpd_qmatmul_q4k_q8k_cuda(d.ptr + 4, d.ptr, d.ptr, 4, 256, None) == -2  # misaligned weights
+    assert lib.bpd_qmatmul_q4k_q8k_cuda(None, d.ptr, d.ptr, 4, 256, None) == -1
+    lib.bpdq_clear_status()
