@@ -1,0 +1,345 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized decode path: Q4_K x Q8_K GEMVs of a Mistral-7B-shaped layer set,
+32 layers, batch 1 (seeded synthetic weights and activations).
+
+    python bench.py --gpus 1 --steps K --warmup W            # this library (CUDA kernels)
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU code
+
+A step is one pass over the 7 x 32 GEMVs.  The metric is effective HBM bandwidth: algorithmic
+bytes (quantized weights + fp32 activations in + fp32 outputs out) divided by device time.
+With N GPUs every rank holds a layer set of the same size (its row shard of an N-times
+larger model), runs the same step, and all-gathers its output slices over NCCL; the value
+is the sum of the ranks' bytes over the slowest rank's time (weak scaling).
+
+One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from bpd_substrate_b200 import synth  # noqa: E402
+
+METRIC = "Q4_K x Q8_K GEMV effective HBM bandwidth"
+UNIT = "GB/s"
+WORKLOAD = "mistral7b_layer_set_x32_q4k_decode_batch1"
+N_LAYERS = 32
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 8:
+                continue
+            try:
+                sm.append(float(r[0]))
+                smax.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(np.max(smax)) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_activations(ls, seed):
+    rng = np.random.default_rng(seed)
+    return rng.standard_normal(ls.x_bytes // 4, dtype=np.float32)
+
+
+# --------------------------------------------------------------------------- CPU baseline
+
+def cpu_reference_run(steps, warmup, layers_per_step, threads):
+    """Times the reference's own bpd_qmatmul_q4k (bench/bpd_quant.c:88-109 of the reference,
+    compiled unmodified) over `layers_per_step` layers of the workload, rows split over
+    `threads` host threads.  Falls back to this repository's C restatement when the compiled
+    reference is not present.  Returns (GB/s, kind, seconds per step)."""
+    import ctypes as C
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import binding
+    if binding.ref_available("bpd_quant.so"):
+        lib = binding.load_ref("bpd_quant.so")
+        kind = "reference"
+
+        def gemv(w, x, out, rows, cols):
+            lib.bpd_qmatmul_q4k(w, x, out, rows, cols)
+    else:
+        orc = binding.Oracle()
+        kind = "port"
+
+        def gemv(w, x, out, rows, cols):
+            orc.lib.orc_qmatmul_q4k(w, x, out, rows, cols, 0)
+    rng = np.random.default_rng(2000)
+    mats = []
+    nbytes = 0
+    for name, rows, cols in synth.MISTRAL_LAYER:
+        w = synth.q4k_matrix(rows, cols, rng)
+        x = synth.activations(cols, rng)
+        out = np.zeros(rows, np.float32)
+        mats.append((w, x, out, rows, cols))
+        nbytes += synth.gemv_bytes_q4k(rows, cols)
+    nbytes *= layers_per_step
+    pool = ThreadPoolExecutor(threads)
+
+    def one_layer():
+        jobs = []
+        for w, x, out, rows, cols in mats:
+            rb = synth.q4k_row_bytes(cols)
+            per = (rows + threads - 1) // threads
+            for t in range(threads):
+                r0, r1 = t * per, min(rows, (t + 1) * per)
+                if r0 < r1:
+                    jobs.append(pool.submit(gemv, w.ctypes.data + r0 * rb, x.ctypes.data,
+                                            out.ctypes.data + 4 * r0, r1 - r0, cols))
+        for j in jobs:
+            j.result()
+
+    for _ in range(warmup):
+        one_layer()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        for _ in range(layers_per_step):
+            one_layer()
+    dt = (time.perf_counter() - t0) / steps
+    pool.shutdown()
+    return nbytes / dt / 1e9, kind, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    steps, warmup = args.steps, max(args.warmup, 1)
+    value, kind, dt = cpu_reference_run(steps, warmup, 1, threads)
+    sample = ("1 of 32 layers per step (7 GEMVs, 218,103,808 weights), W4A32 bpd_qmatmul_q4k, "
+              "rows split over host threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def run_gpu(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    from bpd_substrate_b200 import capi
+    from bpd_substrate_b200.dispatch import LayerSet
+    lib = capi.load()
+    dist = torch = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    capi.check(lib.bpdq_set_device(local_rank), "set device")
+    lib.bpdq_clear_status()
+
+    # Every rank holds a full-size layer set: its row shard of a `world`-times larger model.
+    out_local = None
+    if world > 1:
+        # NCCL reads this rank's output arena directly: let torch own that allocation
+        o_floats = N_LAYERS * sum(rows for _, rows, _ in synth.MISTRAL_LAYER)
+        out_local = torch.empty(o_floats, dtype=torch.float32, device="cuda")
+    ls = LayerSet(synth.MISTRAL_LAYER, N_LAYERS, seed=2000 + rank,
+                  d_out=out_local.data_ptr() if out_local is not None else None)
+    step_bytes = ls.algorithmic_bytes()
+    schedule = args.schedule
+    launches = ls.launches_per_step(schedule)
+    x_host = lib.bpdq_host_alloc(ls.x_bytes)
+    o_host = lib.bpdq_host_alloc(ls.o_bytes)
+    x_np = np.ctypeslib.as_array((np.ctypeslib.ctypes.c_float * (ls.x_bytes // 4)).from_address(x_host))
+    x_np[:] = make_activations(ls, 3000 + rank)
+    ls.upload_activations(x_np)
+    ls.capture(schedule)
+
+    gathered = ext_stream = None
+    if world > 1:
+        # all-gather of the ranks' output slices (the exchange step of row sharding), queued
+        # behind the GEMVs on the same stream so that one pair of CUDA events spans both
+        gathered = torch.empty(world * (ls.o_bytes // 4), dtype=torch.float32, device="cuda")
+        ext_stream = torch.cuda.ExternalStream(ls.stream)
+
+    ev0, ev1 = lib.bpdq_event_create(), lib.bpdq_event_create()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        lib.bpdq_sync()
+
+    def exchange():
+        if world > 1:
+            with torch.cuda.stream(ext_stream):
+                dist.all_gather_into_tensor(gathered, out_local)
+
+    # ---- device-resident timing: inputs already in HBM
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    for _ in range(args.warmup):
+        ls.step(schedule)
+        exchange()
+    barrier()
+    if rank == 0:
+        sampler.rows.clear()
+    t_wall0 = time.perf_counter()
+    lib.bpdq_event_record(ev0, ls.stream)
+    for _ in range(args.steps):
+        ls.step(schedule)
+        exchange()
+    lib.bpdq_event_record(ev1, ls.stream)
+    ms_total = lib.bpdq_event_elapsed_ms(ev0, ev1)
+    barrier()
+    t_wall = time.perf_counter() - t_wall0
+    del t_wall
+    # GEMV-only device time (no exchange), for the roofline of the kernel itself
+    lib.bpdq_event_record(ev0, ls.stream)
+    for _ in range(args.steps):
+        ls.step(schedule)
+    lib.bpdq_event_record(ev1, ls.stream)
+    ms_kernel_total = lib.bpdq_event_elapsed_ms(ev0, ev1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the public call with HOST buffers
+    for _ in range(min(args.warmup, 3)):
+        ls.step_host(x_host, o_host, schedule)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ls.step_host(x_host, o_host, schedule)
+        exchange()
+    t_e2e = time.perf_counter() - t0
+
+    ms_step = ms_total / args.steps
+    ms_kernel = ms_kernel_total / args.steps
+    if world > 1:
+        t = torch.tensor([ms_step, ms_kernel, t_e2e], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, ms_kernel, t_e2e = (float(v) for v in t.tolist())
+    status = lib.bpdq_last_status()
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        total_bytes = step_bytes * world
+        value = total_bytes / (ms_step * 1e-3) / 1e9
+        achieved = step_bytes / (ms_kernel * 1e-3) / 1e9      # per GPU, kernel only
+        e2e_value = total_bytes / (t_e2e / args.steps) / 1e9
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            v, kind, dt = cpu_reference_run(1, 1, 32, threads)
+            cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": kind,
+                   "sample": "one full step (32 layers, 224 GEMVs), W4A32 bpd_qmatmul_q4k of the reference, rows "
+                             f"split over {threads} host threads, {dt:.2f} s wall"}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": N_LAYERS, "gemvs_per_step": 7 * N_LAYERS,
+                       "schedule": schedule, "launches_per_step": launches,
+                       "weights_bytes_per_gpu": ls.weight_bytes,
+                       "l2": "inputs larger than L2: 3.9 GB of weights stream through once per step",
+                       "parallelism": f"row-shard x{world}" if world > 1 else "single GPU",
+                       "exchange": "NCCL all-gather of output slices once per step" if world > 1 else "none"},
+            "pct_of_peak": 100.0 * value / (peak * world),
+            "elements_per_s": (ls.weight_bytes / synth.Q4K_BYTES * 256) * world / (ms_step * 1e-3),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)",
+                         "kernel": "k_gemv_q4k_q8k", "traffic": None,
+                         "algorithmic_bytes_per_launch": step_bytes / launches,
+                         "avg_launch_us": ms_kernel * 1e3 / launches},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": ls.x_bytes * world,
+                    "d2h_bytes_per_step": ls.o_bytes * world},
+            "gpu_launches": launches * args.steps,
+            "clocks": clocks,
+            "status": status,
+        }
+        if cpu:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    ls.close()
+    if status != 0:
+        sys.exit(1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--schedule", default="grouped", choices=["grouped", "separate"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -24,8 +24,9 @@ SIGNATURES = {
     "bpdq_last_status": (i32, []),
     "bpdq_device_error_word": (i32, []),
     "bpdq_clear_status": (None, []),
-    "bpdq_set_tuning": (None, [i32, i32, i32, i32]),
+    "bpdq_set_tuning": (None, [i32, i32, i32, i32, i32]),
     "bpdq_sm_count": (i32, []),
+    "bpdq_debug_trace": (None, [vp, sz, i32]),
     # memory (size_t)
     "bpdq_alloc": (vp, [sz]),
     "bpdq_free": (None, [vp]),
@@ -73,6 +74,7 @@ SIGNATURES = {
     # Q4_K x Q8_K
     "bpd_quant_q8_K_cuda": (i32, [vp, vp, sz, vp]),
     "bpd_qmatmul_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, vp]),
+    "bpd_qmatmul_q4k_q8k_multi_cuda": (i32, [i32, vp, vp, vp, vp, i32, vp]),
     "bpd_qmm_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),
     "gpu_matmul_q4k": (None, [vp, vp, vp, i32, i32, i32]),

@@ -40,6 +40,7 @@ struct Tuning {
     int tile_bytes;     // weight bytes staged per ring slot (target)
     int stages;         // ring depth
     int ctas_per_sm;    // persistent CTAs per SM (upper bound)
+    int warps;          // consumer warps per CTA (target)
     int pdl;            // launch GEMVs with programmatic dependent launch
 };
 Tuning& tuning();

@@ -35,22 +35,50 @@
 namespace bpdq {
 
 constexpr int kMaxTokens = 4;       // tokens per pass (activation registers: 32 words each)
-constexpr int kXqStride = 144;      // 128 int8 + 16 B pad per half-super-block: conflict-free 16 B reads
+
+constexpr int kMaxProblems = 4;     // weight matrices per launch that share one activation vector
+
+// One weight matrix of a launch.  All matrices of a launch have the same K and read the same
+// activations; their rows are cut into tiles of rt rows and numbered consecutively.
+struct GemvProblem {
+    const uint8_t* W;   // [M][K/256][144]
+    float* out;         // [T][M]
+    int M;
+    int tile_begin;     // first tile number of this matrix
+};
 
 struct GemvPlan {
     int nb;          // super-blocks per row
     int row_bytes;   // nb * 144
     int kc;          // K-chunks (warps) per row, ceil(nb / 16)
-    int rw;          // row-warps: rows processed concurrently inside a tile
-    int nw;          // consumer warps = kc * rw
-    int rt;          // rows per tile (multiple of rw)
-    int stages;
-    int n_tiles;
+    int ng;          // consumer groups per CTA (each owns whole tiles)
+    int nw;          // consumer warps = ng * kc
+    int rt;          // rows per tile (1, 2 or 4)
+    int slots;       // ring slots per group
+    int n_tiles;     // tiles of all matrices together
+    int n_problems;
     int grid;
     size_t smem;
     // smem offsets
     int off_ring, off_xq, off_xd, off_part, off_bar;
+    // Tile hand-out is static: round n gives group g of CTA c tile (n*ng + g)*grid + c.
+    // optional timeline capture (debug): 8 global-timer stamps per CTA, or null
+    unsigned long long* trace;
+    GemvProblem prob[kMaxProblems];
 };
+
+__device__ __forceinline__ unsigned long long global_timer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define BPDQ_TRACE(slot)                                                              \
+    do {                                                                              \
+        if (p.trace && lane == 0 && (warp == 0 || (slot) == 7))                       \
+            p.trace[(size_t)blockIdx.x * 8 + (slot)] = global_timer_ns();             \
+    } while (0)
+
 
 // ---------------------------------------------------------------- activation quantizer (device)
 
@@ -182,114 +210,190 @@ __device__ __forceinline__ void half_block_fma(const uint8_t* sbp, int half, con
 
 // ---------------------------------------------------------------- the GEMV / small-batch GEMM kernel
 
-// XSRC: 0 = x is fp32 [T][K], quantized here; 1 = x is Q8_K blocks [T][K/256][292].
-// MAXTHREADS bounds the CTA size (and so the registers the compiler may use per thread).
-template <int T, int LAYOUT, int XSRC, int MAXTHREADS>
-__global__ void __launch_bounds__(MAXTHREADS, 1)
-k_gemv_q4k_q8k(const uint8_t* __restrict__ W, const void* __restrict__ xin, float* __restrict__ out, int M, int K,
-               GemvPlan p, int* __restrict__ err, int32_t* __restrict__ dbg)
+// Stages the quantized activations of all T tokens in shared memory, cooperatively by the
+// consumer warps of the CTA: xq is [T][2*nb] half-super-blocks of 128 int8 padded to 144 B (so
+// that the 16-byte reads of 32 consecutive lanes hit distinct banks), xds is [T][nb] block
+// scales.  XSRC 0: x is fp32 and is quantized here, one warp per 256-block, UNR blocks in
+// flight per warp so that the loop costs about one L2 round trip; XSRC 1: x is Q8_K blocks.
+constexpr int kXqStride = 144;
+
+template <int T, int XSRC>
+__device__ __forceinline__ void stage_activations(const void* __restrict__ xin, int K, int nb, uint8_t* xq,
+                                                  float* xds, int warp, int lane, int n_warps)
+{
+    const int n_hb = 2 * nb;
+    if (XSRC == 0) {
+        constexpr int UNR = 4;
+        const float* x = reinterpret_cast<const float*>(xin);
+        const int total = T * nb;
+        for (int blk0 = warp; blk0 < total; blk0 += n_warps * UNR) {
+            float4 v0[UNR], v1[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; u++) {
+                const int blk = blk0 + u * n_warps;
+                if (blk < total) {
+                    // blk = t*nb + b and x is [T][K] with K = 256*nb: block blk starts at 256*blk
+                    const float4* xb = reinterpret_cast<const float4*>(x + (size_t)blk * 256);
+                    v0[u] = __ldg(xb + lane);
+                    v1[u] = __ldg(xb + 32 + lane);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNR; u++) {
+                const int blk = blk0 + u * n_warps;
+                if (blk < total) {
+                    uint32_t p0, p1;
+                    float d;
+                    quantize_block_256(v0[u], v1[u], p0, p1, d);
+                    uint8_t* dst = xq + (size_t)2 * blk * kXqStride;  // half-block index t*n_hb + 2b = 2*blk
+                    reinterpret_cast<uint32_t*>(dst)[lane] = p0;
+                    reinterpret_cast<uint32_t*>(dst + kXqStride)[lane] = p1;
+                    if (lane == 0) xds[blk] = d;
+                }
+            }
+        }
+    } else {
+        const uint8_t* xb = reinterpret_cast<const uint8_t*>(xin);
+        const int tid = warp * 32 + lane, n_threads = n_warps * 32;
+        for (int i = tid; i < T * nb * 64; i += n_threads) {
+            const int blk = i >> 6, w = i & 63;  // word w of the 64 qs words of block blk = t*nb + b
+            const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(xb + (size_t)blk * BPDQ_Q8K_BYTES + 4) + w);
+            uint8_t* dst = xq + ((size_t)2 * blk + (w >> 5)) * kXqStride;
+            reinterpret_cast<uint32_t*>(dst)[w & 31] = v;
+        }
+        for (int i = tid; i < T * nb; i += n_threads)
+            xds[i] = __uint_as_float(__ldg(reinterpret_cast<const uint32_t*>(xb + (size_t)i * BPDQ_Q8K_BYTES)));
+    }
+    (void)n_hb;
+    (void)K;
+}
+
+// Sums R per-lane partials across the 32 lanes of a warp.  After the call the total of row
+// rr sits in lane rr*(32/R) (the other lanes hold partial garbage).  Fixed order: for R=4
+// lanes are folded by xor 16 (rows split 0,1 | 2,3), xor 8 (row split), then xor 4, 2, 1; for
+// R=2 by xor 16 (row split) then 8, 4, 2, 1; for R=1 a plain butterfly 16, 8, 4, 2, 1.
+template <int R>
+__device__ __forceinline__ float fold_rows(const float (&v)[R], int lane)
+{
+    float c;
+    if constexpr (R == 4) {
+        const bool up = (lane & 16) != 0;
+        float a = (up ? v[2] : v[0]) + __shfl_xor_sync(0xFFFFFFFFu, up ? v[0] : v[2], 16);
+        float b = (up ? v[3] : v[1]) + __shfl_xor_sync(0xFFFFFFFFu, up ? v[1] : v[3], 16);
+        const bool up2 = (lane & 8) != 0;
+        c = (up2 ? b : a) + __shfl_xor_sync(0xFFFFFFFFu, up2 ? a : b, 8);
+        c += __shfl_xor_sync(0xFFFFFFFFu, c, 4);
+    } else if constexpr (R == 2) {
+        const bool up = (lane & 16) != 0;
+        c = (up ? v[R - 1] : v[0]) + __shfl_xor_sync(0xFFFFFFFFu, up ? v[0] : v[R - 1], 16);
+        c += __shfl_xor_sync(0xFFFFFFFFu, c, 8);
+        c += __shfl_xor_sync(0xFFFFFFFFu, c, 4);
+    } else {
+        c = v[0] + __shfl_xor_sync(0xFFFFFFFFu, v[0], 16);
+        c += __shfl_xor_sync(0xFFFFFFFFu, c, 8);
+        c += __shfl_xor_sync(0xFFFFFFFFu, c, 4);
+    }
+    c += __shfl_xor_sync(0xFFFFFFFFu, c, 2);
+    c += __shfl_xor_sync(0xFFFFFFFFu, c, 1);
+    return c;
+}
+
+
+// Kernel structure.  A CTA has `ng` consumer groups of `kc` warps and one producer warp.  A
+// group owns whole tiles of R consecutive weight rows (one contiguous byte span) and has its
+// own ring of `slots` shared-memory slots with full/empty mbarriers, so groups never wait for
+// each other.  Tile hand-out is static (round n gives group g of CTA c tile (n*ng + g)*grid + c),
+// so producer and consumers walk the same sequence without talking; lane g of the producer
+// warp feeds group g, which keeps the copy issue rate above what HBM can deliver.
+// Inside a group, warp c covers K-chunk c of all R rows; the R rows are independent
+// instruction streams, which is what hides shared-memory and dot-product latency.
+// MAXTHREADS / MINBLOCKS bound the CTA size and the registers per thread so that CTAs of
+// consecutive launches can be resident on one SM together (programmatic dependent launch).
+template <int T, int R, int LAYOUT, int XSRC, int MAXTHREADS, int MINBLOCKS>
+__global__ void __launch_bounds__(MAXTHREADS, MINBLOCKS)
+k_gemv_q4k_q8k(const void* __restrict__ xin, int K, const GemvPlan p, int* __restrict__ err,
+               int32_t* __restrict__ dbg)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* ring = smem + p.off_ring;
+    uint8_t* ring = smem + p.off_ring;                           // [ng][slots][R*row_bytes]
     uint8_t* xq = smem + p.off_xq;                               // [T][n_hb][144]
     float* xds = reinterpret_cast<float*>(smem + p.off_xd);      // [T][nb]
-    float* part = reinterpret_cast<float*>(smem + p.off_part);   // [2][rt][kc][T]
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bar);
-    uint64_t* empty = full + p.stages;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + p.stages);
+    float* part = reinterpret_cast<float*>(smem + p.off_part);   // [ng][2][R][kc][T]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bar);   // [ng*slots]
+    uint64_t* empty = full + p.ng * p.slots;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + p.ng * p.slots);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int n_threads = blockDim.x;
     const bool is_producer = (warp == p.nw);
     const int n_hb = 2 * p.nb;
-    const uint32_t tile_bytes_full = (uint32_t)p.rt * p.row_bytes;
+    const uint32_t tile_bytes_full = (uint32_t)R * p.row_bytes;
+    BPDQ_TRACE(0);
 
     if (tid == 0) {
-        for (int s = 0; s < p.stages; s++) {
+        for (int s = 0; s < p.ng * p.slots; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], p.nw);
+            mbar_init(&empty[s], p.kc);
         }
         *abort_flag = 0;
         mbar_init_fence();
     }
     __syncthreads();
 
-    // Tiles of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
-    const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-
-    // Let the next kernel in the stream start its own weight prefetch as early as possible.
+    // Programmatic dependent launch: the next kernel in the stream may start once every CTA
+    // of this one has got here.  Its CTAs fill their weight rings while we compute and then
+    // block in pdl_wait() until this grid has finished.
     pdl_launch_dependents();
-
-    // Producer: start the first ring fills before anything else so HBM latency overlaps the
-    // activation quantization below.  Weights never depend on the previous kernel.
-    int issued = 0;
-    if (is_producer && lane == 0) {
-        for (; issued < my_tiles && issued < p.stages; issued++) {
-            const int tile = blockIdx.x + issued * gridDim.x;
-            const int row0 = tile * p.rt;
-            const int rows = min(p.rt, M - row0);
-            const uint32_t bytes = (uint32_t)rows * p.row_bytes;
-            mbar_expect_tx(&full[issued], bytes);
-            bulk_g2s(ring + (size_t)issued * tile_bytes_full, W + (size_t)row0 * p.row_bytes, bytes, &full[issued]);
-        }
-    }
-
-    // Activations may be produced by the previous kernel: wait for it here.
-    pdl_wait();
-
-    // ---- stage the quantized activations in shared memory (padded half-block layout)
-    if (XSRC == 0) {
-        const float* x = reinterpret_cast<const float*>(xin);
-        const int n_warps = n_threads >> 5;
-        for (int blk = warp; blk < T * p.nb; blk += n_warps) {
-            const int t = blk / p.nb, b = blk - t * p.nb;
-            const float4* xb = reinterpret_cast<const float4*>(x + (size_t)t * K + (size_t)b * 256);
-            const float4 v0 = __ldg(xb + lane), v1 = __ldg(xb + 32 + lane);
-            uint32_t p0, p1;
-            float d;
-            quantize_block_256(v0, v1, p0, p1, d);
-            uint8_t* dst = xq + ((size_t)t * n_hb + 2 * b) * kXqStride;
-            reinterpret_cast<uint32_t*>(dst)[lane] = p0;
-            reinterpret_cast<uint32_t*>(dst + kXqStride)[lane] = p1;
-            if (lane == 0) xds[t * p.nb + b] = d;
-        }
-    } else {
-        const uint8_t* xb = reinterpret_cast<const uint8_t*>(xin);
-        for (int i = tid; i < T * p.nb * 64; i += n_threads) {
-            const int blk = i >> 6, w = i & 63;  // word w of the 64 qs words of block blk = t*nb + b
-            const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(xb + (size_t)blk * BPDQ_Q8K_BYTES + 4) + w);
-            uint8_t* dst = xq + ((size_t)2 * blk + (w >> 5)) * kXqStride;  // half-block index t*n_hb + 2b + (w>>5)
-            reinterpret_cast<uint32_t*>(dst)[w & 31] = v;
-        }
-        for (int i = tid; i < T * p.nb; i += n_threads)
-            xds[i] = __uint_as_float(__ldg(reinterpret_cast<const uint32_t*>(xb + (size_t)i * BPDQ_Q8K_BYTES)));
-    }
-    __syncthreads();
+    BPDQ_TRACE(1);
 
     if (is_producer) {
-        // ---- producer warp: keep the ring full
-        if (lane == 0) {
-            for (int it = issued; it < my_tiles; it++) {
-                const int s = it % p.stages;
-                const uint32_t parity = ((it / p.stages) - 1) & 1;
-                if (!mbar_wait_bounded(&empty[s], parity, err, 1)) break;
-                const int tile = blockIdx.x + it * gridDim.x;
-                const int row0 = tile * p.rt;
-                const int rows = min(p.rt, M - row0);
-                const uint32_t bytes = (uint32_t)rows * p.row_bytes;
+        if (lane < p.ng) {
+            // Weights never depend on the previous kernel: no pdl_wait on this path.
+            const int g = lane;
+            int slot = 0;
+            uint32_t wait_parity = 0;   // phase of empty[] that frees a slot for its next use
+            bool wrapped = false;       // false during the first pass over the ring: slots are free
+            for (int v = g * (int)gridDim.x + (int)blockIdx.x; v < p.n_tiles; v += p.ng * (int)gridDim.x) {
+                const int s = g * p.slots + slot;
+                if (wrapped && !mbar_wait_bounded(&empty[s], wait_parity, err, 1)) break;
+                const uint8_t* Wj = p.prob[0].W;
+                int Mj = p.prob[0].M, tb = 0;
+#pragma unroll
+                for (int q = 1; q < kMaxProblems; q++)
+                    if (q < p.n_problems && v >= p.prob[q].tile_begin) {
+                        Wj = p.prob[q].W;
+                        Mj = p.prob[q].M;
+                        tb = p.prob[q].tile_begin;
+                    }
+                const int row0 = (v - tb) * R;
+                const uint32_t bytes = (uint32_t)min(R, Mj - row0) * p.row_bytes;
                 mbar_expect_tx(&full[s], bytes);
-                bulk_g2s(ring + (size_t)s * tile_bytes_full, W + (size_t)row0 * p.row_bytes, bytes, &full[s]);
+                bulk_g2s(ring + (size_t)s * tile_bytes_full, Wj + (size_t)row0 * p.row_bytes, bytes, &full[s]);
+                if (++slot == p.slots) {
+                    slot = 0;
+                    if (wrapped) wait_parity ^= 1u;
+                    wrapped = true;
+                }
             }
+            if (lane == 0) BPDQ_TRACE(7);
         }
         return;
     }
 
+    // Activations may be written by the previous kernel: wait for it before the first read.
+    pdl_wait();
+    BPDQ_TRACE(2);
+
     // ---- consumer warps
+    const int g = warp / p.kc;      // group
     const int kc = warp % p.kc;     // K-chunk of this warp (fixed for the whole kernel)
-    const int rwi = warp / p.kc;    // row-warp index
     const int hb = 32 * kc + lane;  // half-super-block of this lane
     const bool active = hb < n_hb;
     const int sb = hb >> 1, half = hb & 1;
+    const int n_consumer_threads = p.nw * 32;
+
+    stage_activations<T, XSRC>(xin, K, p.nb, xq, xds, warp, lane, p.nw);
+    named_bar_sync(2, n_consumer_threads);
+    BPDQ_TRACE(3);
 
     uint32_t xr[T][32];
     int bs[T][4];
@@ -320,39 +424,58 @@ k_gemv_q4k_q8k(const uint8_t* __restrict__ W, const void* __restrict__ xin, floa
             bs[t][j] = s;
         }
     }
+    BPDQ_TRACE(4);
 
-    const int n_consumer_threads = p.nw * 32;
-    for (int it = 0; it < my_tiles; it++) {
-        const int s = it % p.stages;
-        const uint32_t parity = (it / p.stages) & 1;
-        const int tile = blockIdx.x + it * gridDim.x;
-        const int row0 = tile * p.rt;
-        const int rows = min(p.rt, M - row0);
+    constexpr int kLanesPerRow = 32 / R;
+    const int my_row = lane / kLanesPerRow;                  // row whose total this lane ends up holding
+    const bool row_leader = (lane % kLanesPerRow) == 0;
+    float* part_g = part + (size_t)g * 2 * R * p.kc * T;
+
+    int slot = 0;
+    uint32_t parity = 0;
+    int n = 0;
+    for (int v = g * (int)gridDim.x + (int)blockIdx.x; v < p.n_tiles; v += p.ng * (int)gridDim.x, n++) {
+        const int s = g * p.slots + slot;
         const bool ok = mbar_wait_bounded(&full[s], parity, err, 2);
-        if (!ok) *abort_flag = 1;
-        const uint8_t* tile_smem = ring + (size_t)s * tile_bytes_full;
-        float* part_it = part + (size_t)(it & 1) * p.rt * p.kc * T;
+        if (!ok) {
+            // gave up: tell the group mates (they may be past the wait) and meet them once more
+            *abort_flag = 1;
+            if (p.kc > 1) named_bar_sync(3 + g, p.kc * 32);
+            return;
+        }
+        if (n == 0) BPDQ_TRACE(5);
+        if (++slot == p.slots) {
+            slot = 0;
+            parity ^= 1u;
+        }
+        int M = p.prob[0].M, tb = 0;
+        float* __restrict__ out = p.prob[0].out;
+        bool first_matrix = true;
+#pragma unroll
+        for (int q = 1; q < kMaxProblems; q++)
+            if (q < p.n_problems && v >= p.prob[q].tile_begin) {
+                M = p.prob[q].M;
+                tb = p.prob[q].tile_begin;
+                out = p.prob[q].out;
+                first_matrix = false;
+            }
+        const int row0 = (v - tb) * R;
+        const int rows = min(R, M - row0);
+        const uint8_t* tile_smem = ring + (size_t)s * tile_bytes_full + (size_t)sb * BPDQ_Q4K_BYTES;
+        float* part_n = part_g + (size_t)(n & 1) * R * p.kc * T;
 
-        if (ok) {
-            for (int r = rwi; r < rows; r += p.rw) {
-                float acc[T];
+        float acc[R][T];
 #pragma unroll
-                for (int t = 0; t < T; t++) acc[t] = 0.0f;
-                if (active) {
-                    int32_t* d = dbg ? dbg + ((size_t)(row0 + r) * p.nb + sb) * 8 : nullptr;
-                    half_block_fma<T, LAYOUT>(tile_smem + (size_t)r * p.row_bytes + (size_t)sb * BPDQ_Q4K_BYTES, half,
-                                              xr, bs, xd, acc, d);
-                }
+        for (int r = 0; r < R; r++)
 #pragma unroll
-                for (int t = 0; t < T; t++) acc[t] = warp_sum(acc[t]);
-                if (lane == 0) {
-                    if (p.kc == 1) {
+            for (int t = 0; t < T; t++) acc[r][t] = 0.0f;
+        if (active) {
 #pragma unroll
-                        for (int t = 0; t < T; t++) out[(size_t)t * M + row0 + r] = acc[t];
-                    } else {
-#pragma unroll
-                        for (int t = 0; t < T; t++) part_it[((size_t)r * p.kc + kc) * T + t] = acc[t];
-                    }
+            for (int r = 0; r < R; r++) {
+                if (r < rows) {
+                    // sub-block dots are reported for the first matrix of a launch only
+                    int32_t* d = (dbg && first_matrix) ? dbg + ((size_t)(row0 + r) * p.nb + sb) * 8 : nullptr;
+                    half_block_fma<T, LAYOUT>(tile_smem + (size_t)r * p.row_bytes, half, xr, bs, xd, acc[r], d);
                 }
             }
         }
@@ -360,66 +483,99 @@ k_gemv_q4k_q8k(const uint8_t* __restrict__ W, const void* __restrict__ xin, floa
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
 
-        if (p.kc > 1) {
-            // K-chunks of a row live in different warps: combine them in ascending chunk order.
-            named_bar_sync(1, n_consumer_threads);
-            if (*abort_flag) return;  // every consumer warp sees the same value after the barrier
-            for (int i = tid; i < rows * T; i += n_consumer_threads) {
-                const int r = i / T, t = i - r * T;
-                float v = part_it[((size_t)r * p.kc + 0) * T + t];
-                for (int c = 1; c < p.kc; c++) v += part_it[((size_t)r * p.kc + c) * T + t];
-                out[(size_t)t * M + row0 + r] = v;
+#pragma unroll
+        for (int t = 0; t < T; t++) {
+            float vv[R];
+#pragma unroll
+            for (int r = 0; r < R; r++) vv[r] = acc[r][t];
+            const float total = fold_rows<R>(vv, lane);
+            if (row_leader && my_row < rows) {
+                if (p.kc == 1) out[(size_t)t * M + row0 + my_row] = total;
+                else part_n[((size_t)my_row * p.kc + kc) * T + t] = total;
             }
-        } else if (!ok) {
-            return;
+        }
+
+        if (p.kc > 1) {
+            // K-chunks of a row live in the kc warps of this group: add them in ascending order.
+            named_bar_sync(3 + g, p.kc * 32);
+            if (*abort_flag) return;
+            const int gt = kc * 32 + lane;
+            for (int e = gt; e < rows * T; e += p.kc * 32) {
+                const int r = e / T, t = e - r * T;
+                float sum = part_n[((size_t)r * p.kc + 0) * T + t];
+                for (int c = 1; c < p.kc; c++) sum += part_n[((size_t)r * p.kc + c) * T + t];
+                out[(size_t)t * M + row0 + r] = sum;
+            }
         }
     }
+    BPDQ_TRACE(6);
 }
 
 // ---------------------------------------------------------------- host side
 
-constexpr int kSmemLimit = 227 * 1024;
-constexpr int kSmallCtaThreads = 320;   // up to 9 consumer warps + the producer: K <= 36864
+// Timeline capture for tuning: when set, launch k writes 8 stamps per CTA at
+// trace_base + k * trace_stride.
+static unsigned long long* g_trace_base = nullptr;
+static size_t g_trace_stride = 0;
+static int g_trace_left = 0;
 
-// consumer warps for rows of K weights: kc warps cover a row, rw rows run side by side
-static int consumer_warps(int K)
+constexpr int kSmemLimit = 227 * 1024;
+constexpr int kSmallCtaThreads = 288;   // up to 8 consumer warps + the producer
+
+static int rows_per_tile(int row_bytes)
 {
-    const int kc = (K / 256 + 15) / 16;
-    return kc * (kc >= 8 ? 1 : 8 / kc);
+    const int cap = tuning().tile_bytes;
+    if (4 * row_bytes <= cap) return 4;
+    if (2 * row_bytes <= cap) return 2;
+    return 1;
 }
 
 static size_t plan_smem(GemvPlan& p, int T)
 {
     size_t off = 0;
     auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
-    p.off_ring = take((size_t)p.stages * p.rt * p.row_bytes);
+    p.off_ring = take((size_t)p.ng * p.slots * p.rt * p.row_bytes);
     p.off_xq = take((size_t)T * 2 * p.nb * kXqStride);
     p.off_xd = take((size_t)T * p.nb * 4);
-    p.off_part = take((size_t)2 * p.rt * p.kc * T * 4);
-    p.off_bar = take((size_t)2 * p.stages * 8 + 8);
+    p.off_part = take((size_t)p.ng * 2 * p.rt * p.kc * T * 4);
+    p.off_bar = take((size_t)2 * p.ng * p.slots * 8 + 8);
     return off;
 }
 
-static int make_plan(int M, int K, int T, GemvPlan& p)
+// Fills everything but the problem table's pointers.  Ms: rows of each matrix.
+static int make_plan(const int* Ms, int n_problems, int K, int T, GemvPlan& p)
 {
-    if (M < 0 || K <= 0 || (K % 256) != 0 || T < 1 || T > kMaxTokens) return BPDQ_ERR_ARG;
+    if (K <= 0 || (K % 256) != 0 || T < 1 || T > kMaxTokens) return BPDQ_ERR_ARG;
+    if (n_problems < 1 || n_problems > kMaxProblems) return BPDQ_ERR_ARG;
     const Tuning& tu = tuning();
     p.nb = K / 256;
     p.row_bytes = p.nb * BPDQ_Q4K_BYTES;
     p.kc = (p.nb + 15) / 16;
     if (p.kc > 31) return BPDQ_ERR_RANGE;  // K > 126976: one warp per 4096 K, 31 consumer warps at most
-    p.rw = p.kc >= 8 ? 1 : (8 / p.kc);
-    p.nw = p.kc * p.rw;
-    int rows_per_warp = tu.tile_bytes / (p.rw * p.row_bytes);
-    if (rows_per_warp < 1) rows_per_warp = 1;
-    p.rt = p.rw * rows_per_warp;
-    // small matrices: shrink tiles until every SM has at least one
-    while (p.rt > p.rw && (long)((M + p.rt - 1) / p.rt) < (long)sm_count()) p.rt -= p.rw;
-    p.n_tiles = (M + p.rt - 1) / p.rt;
-    p.stages = tu.stages < 2 ? 2 : tu.stages;
+    p.ng = tu.warps / p.kc;
+    if (p.ng < 1) p.ng = 1;
+    if (p.ng > 12) p.ng = 12;              // named barriers 3 .. 3+ng-1
+    p.nw = p.ng * p.kc;
+    p.rt = rows_per_tile(p.row_bytes);
+    p.n_problems = n_problems;
+    p.n_tiles = 0;
+    for (int j = 0; j < kMaxProblems; j++) {
+        p.prob[j].W = nullptr;
+        p.prob[j].out = nullptr;
+        p.prob[j].M = 0;
+        p.prob[j].tile_begin = 0x7FFFFFFF;
+    }
+    for (int j = 0; j < n_problems; j++) {
+        if (Ms[j] < 0) return BPDQ_ERR_ARG;
+        p.prob[j].M = Ms[j];
+        p.prob[j].tile_begin = p.n_tiles;
+        p.n_tiles += (Ms[j] + p.rt - 1) / p.rt;
+    }
+    p.slots = tu.stages < 2 ? 2 : tu.stages;
     p.smem = plan_smem(p, T);
-    while (p.smem > (size_t)kSmemLimit && p.stages > 2) {
-        p.stages--;
+    while (p.smem > (size_t)kSmemLimit && (p.slots > 2 || p.ng > 1)) {
+        if (p.slots > 2) p.slots--;
+        else { p.ng--; p.nw = p.ng * p.kc; }
         p.smem = plan_smem(p, T);
     }
     if (p.smem > (size_t)kSmemLimit) return BPDQ_ERR_RANGE;
@@ -429,16 +585,24 @@ static int make_plan(int M, int K, int T, GemvPlan& p)
     if (per_sm > tu.ctas_per_sm) per_sm = tu.ctas_per_sm;
     if (per_sm < 1) per_sm = 1;
     const long cap = (long)sm_count() * per_sm;
-    p.grid = (int)(p.n_tiles < cap ? p.n_tiles : cap);
-    if (p.grid < 1) p.grid = 1;
+    // one tile per group at least; small launches still spread over all SMs
+    long want = (p.n_tiles + p.ng - 1) / p.ng;
+    if (want < sm_count()) want = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
+    if (want < 1) want = 1;
+    p.grid = (int)(want < cap ? want : cap);
+    p.trace = nullptr;
+    if (g_trace_base && g_trace_left > 0) {
+        p.trace = g_trace_base;
+        g_trace_base += g_trace_stride;
+        g_trace_left--;
+    }
     return 0;
 }
 
-template <int T, int LAYOUT, int XSRC, int MAXTHREADS>
-static int launch_one(const uint8_t* W, const void* x, float* out, int M, int K, const GemvPlan& p, int32_t* dbg,
-                      cudaStream_t s)
+template <int T, int R, int LAYOUT, int XSRC, int MAXTHREADS, int MINBLOCKS>
+static int launch_one(const void* x, int K, const GemvPlan& p, int32_t* dbg, cudaStream_t s)
 {
-    auto kern = k_gemv_q4k_q8k<T, LAYOUT, XSRC, MAXTHREADS>;
+    auto kern = k_gemv_q4k_q8k<T, R, LAYOUT, XSRC, MAXTHREADS, MINBLOCKS>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -457,56 +621,87 @@ static int launch_one(const uint8_t* W, const void* x, float* out, int M, int K,
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = tuning().pdl ? 1 : 0;
-    return check_cuda(cudaLaunchKernelEx(&cfg, kern, W, x, out, M, K, p, device_error_flag(), dbg));
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, x, K, p, device_error_flag(), dbg));
 }
 
-template <int LAYOUT, int XSRC>
-static int launch_T(int T, const uint8_t* W, const void* x, float* out, int M, int K, const GemvPlan& p, int32_t* dbg,
-                    cudaStream_t s)
+template <int T, int LAYOUT, int XSRC>
+static int launch_R(const void* x, int K, const GemvPlan& p, int32_t* dbg, cudaStream_t s)
 {
     if ((p.nw + 1) * 32 > kSmallCtaThreads) {
-        // very long rows: many warps per row, one token per pass
-        if (T != 1) return BPDQ_ERR_ARG;
-        return launch_one<1, LAYOUT, XSRC, 1024>(W, x, out, M, K, p, dbg, s);
+        // very long rows (K > 32768): many warps per row; registers capped by the CTA size
+        if (T != 1 || p.rt != 1) return BPDQ_ERR_RANGE;
+        return launch_one<1, 1, LAYOUT, XSRC, 1024, 1>(x, K, p, dbg, s);
     }
-    switch (T) {
-        case 1: return launch_one<1, LAYOUT, XSRC, kSmallCtaThreads>(W, x, out, M, K, p, dbg, s);
-        case 2: return launch_one<2, LAYOUT, XSRC, kSmallCtaThreads>(W, x, out, M, K, p, dbg, s);
-        case 3: return launch_one<3, LAYOUT, XSRC, kSmallCtaThreads>(W, x, out, M, K, p, dbg, s);
-        case 4: return launch_one<4, LAYOUT, XSRC, kSmallCtaThreads>(W, x, out, M, K, p, dbg, s);
+    constexpr int MB = T == 1 ? 2 : 1;
+    switch (p.rt) {
+        case 4: return launch_one<T, 4, LAYOUT, XSRC, kSmallCtaThreads, MB>(x, K, p, dbg, s);
+        case 2: return launch_one<T, 2, LAYOUT, XSRC, kSmallCtaThreads, MB>(x, K, p, dbg, s);
+        case 1: return launch_one<T, 1, LAYOUT, XSRC, kSmallCtaThreads, MB>(x, K, p, dbg, s);
     }
     return BPDQ_ERR_ARG;
 }
 
-// out is [tokens][M]; x is fp32 [tokens][K] (xsrc 0) or Q8_K blocks [tokens][K/256] (xsrc 1).
-// More than kMaxTokens tokens run as several passes over the weights.
-int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M, int K, int layout, int xsrc,
-                 int32_t* dbg, cudaStream_t s)
+template <int LAYOUT, int XSRC>
+static int launch_T(int T, const void* x, int K, const GemvPlan& p, int32_t* dbg, cudaStream_t s)
 {
-    if (tokens < 0 || M < 0 || K <= 0 || (K % 256) != 0) return latch(BPDQ_ERR_ARG);
-    if (M == 0 || tokens == 0) return 0;
-    if (!W || !x || !out) return latch(BPDQ_ERR_ARG);
-    if (((uintptr_t)W & 15) || ((uintptr_t)x & 15) || ((uintptr_t)out & 3)) return latch(BPDQ_ERR_ALIGN);
+    switch (T) {
+        case 1: return launch_R<1, LAYOUT, XSRC>(x, K, p, dbg, s);
+        case 2: return launch_R<2, LAYOUT, XSRC>(x, K, p, dbg, s);
+        case 3: return launch_R<3, LAYOUT, XSRC>(x, K, p, dbg, s);
+        case 4: return launch_R<4, LAYOUT, XSRC>(x, K, p, dbg, s);
+    }
+    return BPDQ_ERR_ARG;
+}
+
+// n matrices W[j] ([Ms[j]][K], Q4_K) against the same activations.  outs[j] is [tokens][Ms[j]];
+// x is fp32 [tokens][K] (xsrc 0) or Q8_K blocks [tokens][K/256] (xsrc 1).  More than
+// kMaxTokens tokens run as several passes over the weights.
+int gemm_q4k_q8k_multi(int n, const uint8_t* const* Ws, float* const* outs, const int* Ms, const void* x, int tokens,
+                       int K, int layout, int xsrc, int32_t* dbg, cudaStream_t s)
+{
+    if (n < 1 || n > kMaxProblems || tokens < 0 || K <= 0 || (K % 256) != 0) return latch(BPDQ_ERR_ARG);
+    long total_rows = 0;
+    for (int j = 0; j < n; j++) {
+        if (Ms[j] < 0) return latch(BPDQ_ERR_ARG);
+        total_rows += Ms[j];
+    }
+    if (total_rows == 0 || tokens == 0) return 0;
+    if (!x) return latch(BPDQ_ERR_ARG);
+    if ((uintptr_t)x & 15) return latch(BPDQ_ERR_ALIGN);
+    for (int j = 0; j < n; j++) {
+        if (Ms[j] > 0 && (!Ws[j] || !outs[j])) return latch(BPDQ_ERR_ARG);
+        if (((uintptr_t)Ws[j] & 15) || ((uintptr_t)outs[j] & 3)) return latch(BPDQ_ERR_ALIGN);
+    }
     const size_t x_stride = xsrc == 0 ? (size_t)K * 4 : (size_t)(K / 256) * BPDQ_Q8K_BYTES;
-    const bool long_rows = (consumer_warps(K) + 1) * 32 > kSmallCtaThreads;
+    const bool long_rows = ((K / 256 + 15) / 16 + 1) * 32 > kSmallCtaThreads;
     const int per_pass = long_rows ? 1 : kMaxTokens;
     for (int t0 = 0; t0 < tokens; t0 += per_pass) {
         const int T = (tokens - t0) < per_pass ? (tokens - t0) : per_pass;
         GemvPlan p;
-        int rc = make_plan(M, K, T, p);
+        int rc = make_plan(Ms, n, K, T, p);
         if (rc) return latch(rc);
+        for (int j = 0; j < n; j++) {
+            p.prob[j].W = Ws[j];
+            p.prob[j].out = outs[j] + (size_t)t0 * Ms[j];
+        }
         const void* xt = (const uint8_t*)x + (size_t)t0 * x_stride;
-        float* ot = out + (size_t)t0 * M;
         if (layout == BPDQ_LAYOUT_GGML)
-            rc = xsrc == 0 ? launch_T<BPDQ_LAYOUT_GGML, 0>(T, W, xt, ot, M, K, p, dbg, s)
-                           : launch_T<BPDQ_LAYOUT_GGML, 1>(T, W, xt, ot, M, K, p, dbg, s);
+            rc = xsrc == 0 ? launch_T<BPDQ_LAYOUT_GGML, 0>(T, xt, K, p, dbg, s)
+                           : launch_T<BPDQ_LAYOUT_GGML, 1>(T, xt, K, p, dbg, s);
         else
-            rc = xsrc == 0 ? launch_T<BPDQ_LAYOUT_BPD, 0>(T, W, xt, ot, M, K, p, dbg, s)
-                           : launch_T<BPDQ_LAYOUT_BPD, 1>(T, W, xt, ot, M, K, p, dbg, s);
+            rc = xsrc == 0 ? launch_T<BPDQ_LAYOUT_BPD, 0>(T, xt, K, p, dbg, s)
+                           : launch_T<BPDQ_LAYOUT_BPD, 1>(T, xt, K, p, dbg, s);
         if (rc) return latch(rc);
         dbg = nullptr;  // sub-block dots are reported for token 0 only
     }
     return 0;
+}
+
+int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M, int K, int layout, int xsrc,
+                 int32_t* dbg, cudaStream_t s)
+{
+    if (M < 0) return latch(BPDQ_ERR_ARG);
+    return gemm_q4k_q8k_multi(1, &W, &out, &M, x, tokens, K, layout, xsrc, dbg, s);
 }
 
 }  // namespace bpdq
@@ -514,6 +709,15 @@ int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M,
 using namespace bpdq;
 
 extern "C" {
+
+// Debug aid: the next `launches` GEMV launches each write 8 global-timer stamps per CTA
+// (ns) into dev_buf, `stride_u64` 64-bit words apart.  Pass NULL to stop.
+void bpdq_debug_trace(void* dev_buf, size_t stride_u64, int launches)
+{
+    g_trace_base = (unsigned long long*)dev_buf;
+    g_trace_stride = stride_u64;
+    g_trace_left = dev_buf ? launches : 0;
+}
 
 int bpd_quant_q8_K_cuda(const float* x, uint8_t* y, size_t n_elements, void* stream)
 {
@@ -531,6 +735,13 @@ int bpd_quant_q8_K_cuda(const float* x, uint8_t* y, size_t n_elements, void* str
 int bpd_qmatmul_q4k_q8k_cuda(const uint8_t* qweight, const float* x, float* out, int M, int K, void* stream)
 {
     return gemm_q4k_q8k(qweight, x, out, 1, M, K, BPDQ_LAYOUT_BPD, 0, nullptr, (cudaStream_t)stream);
+}
+// Several weight matrices against one activation vector in one launch (the q/k/v and the
+// gate/up projections of a decoder layer): out[j][Ms[j]] = W[j][Ms[j]][K] . quantize_q8_K(x[K]).
+int bpd_qmatmul_q4k_q8k_multi_cuda(int n, const uint8_t* const* qweights, float* const* outs, const int* Ms,
+                                   const float* x, int K, void* stream)
+{
+    return gemm_q4k_q8k_multi(n, qweights, outs, Ms, x, 1, K, BPDQ_LAYOUT_BPD, 0, nullptr, (cudaStream_t)stream);
 }
 // Full-control form: tokens >= 1, layout 0/1, xsrc 0 (fp32) / 1 (pre-quantized Q8_K), optional
 // int32 [M][K/256][8] buffer receiving token 0's exact sub-block dots.

@@ -12,7 +12,7 @@ namespace bpdq {
 
 static std::atomic<cudaStream_t> g_stream{nullptr};
 static std::atomic<int> g_status{0};
-static Tuning g_tuning = {16384, 4, 4, 1};
+static Tuning g_tuning = {16384, 2, 2, 8, 1};
 
 __device__ int g_dev_error = 0;
 
@@ -111,12 +111,13 @@ void bpdq_clear_status(void)
     if (flag) cudaMemset(flag, 0, sizeof(int));
     (void)cudaGetLastError();
 }
-void bpdq_set_tuning(int tile_bytes, int stages, int ctas_per_sm, int pdl)
+void bpdq_set_tuning(int tile_bytes, int stages, int ctas_per_sm, int warps, int pdl)
 {
     Tuning& t = tuning();
     if (tile_bytes > 0) t.tile_bytes = tile_bytes;
     if (stages > 0) t.stages = stages;
     if (ctas_per_sm > 0) t.ctas_per_sm = ctas_per_sm;
+    if (warps > 0) t.warps = warps;
     if (pdl >= 0) t.pdl = pdl;
 }
 int bpdq_sm_count(void) { return sm_count(); }

@@ -41,8 +41,12 @@ void* bpdq_get_stream(void);
 int bpdq_last_status(void);                /* first error since the last clear (synchronizes) */
 int bpdq_device_error_word(void);
 void bpdq_clear_status(void);
-void bpdq_set_tuning(int tile_bytes, int stages, int ctas_per_sm, int pdl); /* <=0 / <0 keeps a field */
+/* GEMV launch tuning: max bytes per weight tile, ring slots per warp group, CTAs per SM,
+ * consumer warps per CTA, programmatic dependent launch on/off.  <=0 (pdl: <0) keeps a field. */
+void bpdq_set_tuning(int tile_bytes, int slots, int ctas_per_sm, int warps, int pdl);
 int bpdq_sm_count(void);
+/* tuning aid: the next `launches` GEMV launches write 8 global-timer stamps (ns) per CTA */
+void bpdq_debug_trace(void* dev_buf, size_t stride_u64, int launches);
 
 /* ---- device memory helpers (additive, size_t) ------------------------------------------ */
 void* bpdq_alloc(size_t bytes);
@@ -126,6 +130,9 @@ void dequant_multi8(const uint8_t* q, float* out, int nb);
 int bpd_quant_q8_K_cuda(const float* x, uint8_t* y, size_t n_elements, void* stream);
 /* out[M] = W[M][K] . q8K(x[K]); W in the nibble order of bench/bpd_quant.c:68-72 */
 int bpd_qmatmul_q4k_q8k_cuda(const uint8_t* qweight, const float* x, float* out, int M, int K, void* stream);
+/* n <= 4 matrices that read the same x in ONE launch (q/k/v, gate/up): outs[j][Ms[j]] */
+int bpd_qmatmul_q4k_q8k_multi_cuda(int n, const uint8_t* const* qweights, float* const* outs, const int* Ms,
+                                   const float* x, int K, void* stream);
 /* out[tokens][M]; layout 0/1 as above; xsrc 0: x is float [tokens][K], 1: x is Q8_K blocks
  * [tokens][K/256]; subdots (may be NULL): int32 [M][K/256][8], token 0's exact sub-block dots */
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,

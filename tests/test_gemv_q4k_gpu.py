@@ -79,3 +79,48 @@ def test_bad_arguments_are_rejected(lib):
     assert lib.bpd_qmatmul_q4k_q8k_cuda(d.ptr + 4, d.ptr, d.ptr, 4, 256, None) == -2  # misaligned weights
     assert lib.bpd_qmatmul_q4k_q8k_cuda(None, d.ptr, d.ptr, 4, 256, None) == -1
     lib.bpdq_clear_status()
+
+
+def test_grouped_matrices_share_one_launch(lib, oracle):
+    """q/k/v-style grouping: three matrices, one activation vector, one launch; every output
+    equals the single-matrix launch bit for bit."""
+    import ctypes as C
+    K = 4096
+    Ms = [96, 24, 37]
+    rng = np.random.default_rng(21)
+    Ws = [synth.q4k_matrix(m, K, rng) for m in Ms]
+    x = synth.activations(K, rng)
+    dWs = [Dev(lib, w) for w in Ws]
+    dOs = [Dev(lib, nbytes=m * 4, fill=0xFF) for m in Ms]
+    dX = Dev(lib, x)
+    wp = (C.c_void_p * 3)(*[d.ptr for d in dWs])
+    op = (C.c_void_p * 3)(*[d.ptr for d in dOs])
+    mp = (C.c_int * 3)(*Ms)
+    assert lib.bpd_qmatmul_q4k_q8k_multi_cuda(3, wp, op, mp, dX.ptr, K, None) == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == 0
+    xq = oracle.quant_q8_K(x)
+    for W, m, dO in zip(Ws, Ms, dOs):
+        single, _ = run_gemm(lib, W, x, 1, m, K)
+        got = dO.read(np.float32)
+        assert np.array_equal(got.view(np.uint32), single[0].view(np.uint32))
+        assert normwise(got, oracle.qmatmul_q4k_q8k(W, xq, m, K)[1]) <= TOL
+
+
+def test_many_launches_leave_scheduler_clean(lib, oracle):
+    """The tile-scheduler words are reused round robin; 200 launches in a row stay correct."""
+    M, K = 333, 4096
+    rng = np.random.default_rng(77)
+    W = synth.q4k_matrix(M, K, rng)
+    x = synth.activations(K, rng)
+    dW, dX, dO = Dev(lib, W), Dev(lib, x), Dev(lib, nbytes=M * 4, fill=0xFF)
+    first = None
+    for i in range(200):
+        assert lib.bpd_qmatmul_q4k_q8k_cuda(dW.ptr, dX.ptr, dO.ptr, M, K, None) == 0
+        if i in (0, 63, 64, 199):
+            lib.bpdq_sync()
+            got = dO.read(np.float32)
+            first = got if first is None else first
+            assert np.array_equal(got.view(np.uint32), first.view(np.uint32))
+    assert lib.bpdq_last_status() == 0
+    assert normwise(first, oracle.qmatmul_q4k_q8k(W, oracle.quant_q8_K(x), M, K)[1]) <= TOL
