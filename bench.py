@@ -199,9 +199,9 @@ def run_gpu(args):
     out_local = None
     if world > 1:
         # NCCL reads this rank's output arena directly: let torch own that allocation
-        o_floats = N_LAYERS * sum(rows for _, rows, _ in synth.MISTRAL_LAYER)
+        o_floats = args.layers * sum(rows for _, rows, _ in synth.MISTRAL_LAYER)
         out_local = torch.empty(o_floats, dtype=torch.float32, device="cuda")
-    ls = LayerSet(synth.MISTRAL_LAYER, N_LAYERS, seed=2000 + rank,
+    ls = LayerSet(synth.MISTRAL_LAYER, args.layers, seed=2000 + rank,
                   d_out=out_local.data_ptr() if out_local is not None else None)
     step_bytes = ls.algorithmic_bytes()
     schedule = args.schedule
@@ -296,7 +296,7 @@ def run_gpu(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers": N_LAYERS, "gemvs_per_step": 7 * N_LAYERS,
+            "config": {"workload": WORKLOAD, "layers": args.layers, "gemvs_per_step": 7 * args.layers,
                        "schedule": schedule, "launches_per_step": launches,
                        "weights_bytes_per_gpu": ls.weight_bytes,
                        "l2": "inputs larger than L2: 3.9 GB of weights stream through once per step",
@@ -332,8 +332,10 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--schedule", default="grouped", choices=["grouped", "separate"])
+    ap.add_argument("--schedule", default="batched", choices=["batched", "grouped", "separate"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=N_LAYERS,
+                    help="layers resident (32 is the benchmark; fewer only for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

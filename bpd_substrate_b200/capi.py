@@ -75,6 +75,9 @@ SIGNATURES = {
     "bpd_quant_q8_K_cuda": (i32, [vp, vp, sz, vp]),
     "bpd_qmatmul_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, vp]),
     "bpd_qmatmul_q4k_q8k_multi_cuda": (i32, [i32, vp, vp, vp, vp, i32, vp]),
+    "bpd_qmatmul_q4k_q8k_batch_cuda": (i32, [i32, vp, vp]),
+    "bpd_qmatmul_q4k_q8k_batch_ws_cuda": (i32, [i32, vp, vp, sz, vp]),
+    "bpdq_batch_workspace_bytes": (sz, [i32, vp]),
     "bpd_qmm_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),
     "gpu_matmul_q4k": (None, [vp, vp, vp, i32, i32, i32]),
@@ -102,6 +105,11 @@ def load(build_if_missing=True):
         fn.argtypes = args
     _LIB = lib
     return lib
+
+
+class GemvDesc(C.Structure):
+    """bpdq_gemv_desc: one product of a batched launch."""
+    _fields_ = [("W", vp), ("x", vp), ("out", vp), ("M", i32), ("K", i32)]
 
 
 class BpdqError(RuntimeError):

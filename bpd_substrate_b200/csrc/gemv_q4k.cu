@@ -521,6 +521,7 @@ static int g_trace_left = 0;
 
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kSmallCtaThreads = 288;   // up to 8 consumer warps + the producer
+constexpr int kMidCtaThreads = 544;     // up to 16 consumer warps + the producer
 
 static int rows_per_tile(int row_bytes)
 {
@@ -554,7 +555,8 @@ static int make_plan(const int* Ms, int n_problems, int K, int T, GemvPlan& p)
     if (p.kc > 31) return BPDQ_ERR_RANGE;  // K > 126976: one warp per 4096 K, 31 consumer warps at most
     p.ng = tu.warps / p.kc;
     if (p.ng < 1) p.ng = 1;
-    if (p.ng > 12) p.ng = 12;              // named barriers 3 .. 3+ng-1
+    if (p.ng > 12 && p.kc > 1) p.ng = 12;  // named barriers 3 .. 3+ng-1 (used only when kc > 1)
+    if (p.ng > 31) p.ng = 31;
     p.nw = p.ng * p.kc;
     p.rt = rows_per_tile(p.row_bytes);
     p.n_problems = n_problems;
@@ -591,11 +593,6 @@ static int make_plan(const int* Ms, int n_problems, int K, int T, GemvPlan& p)
     if (want < 1) want = 1;
     p.grid = (int)(want < cap ? want : cap);
     p.trace = nullptr;
-    if (g_trace_base && g_trace_left > 0) {
-        p.trace = g_trace_base;
-        g_trace_base += g_trace_stride;
-        g_trace_left--;
-    }
     return 0;
 }
 
@@ -624,21 +621,31 @@ static int launch_one(const void* x, int K, const GemvPlan& p, int32_t* dbg, cud
     return check_cuda(cudaLaunchKernelEx(&cfg, kern, x, K, p, device_error_flag(), dbg));
 }
 
+template <int T, int LAYOUT, int XSRC, int MAXTHREADS, int MB>
+static int launch_R2(const void* x, int K, const GemvPlan& p, int32_t* dbg, cudaStream_t s)
+{
+    switch (p.rt) {
+        case 4: return launch_one<T, 4, LAYOUT, XSRC, MAXTHREADS, MB>(x, K, p, dbg, s);
+        case 2: return launch_one<T, 2, LAYOUT, XSRC, MAXTHREADS, MB>(x, K, p, dbg, s);
+        case 1: return launch_one<T, 1, LAYOUT, XSRC, MAXTHREADS, MB>(x, K, p, dbg, s);
+    }
+    return BPDQ_ERR_ARG;
+}
+
 template <int T, int LAYOUT, int XSRC>
 static int launch_R(const void* x, int K, const GemvPlan& p, int32_t* dbg, cudaStream_t s)
 {
-    if ((p.nw + 1) * 32 > kSmallCtaThreads) {
-        // very long rows (K > 32768): many warps per row; registers capped by the CTA size
+    const int threads = (p.nw + 1) * 32;
+    if (threads > kMidCtaThreads) {
+        // very long rows (K > 65536): many warps per row; registers capped by the CTA size
         if (T != 1 || p.rt != 1) return BPDQ_ERR_RANGE;
         return launch_one<1, 1, LAYOUT, XSRC, 1024, 1>(x, K, p, dbg, s);
     }
-    constexpr int MB = T == 1 ? 2 : 1;
-    switch (p.rt) {
-        case 4: return launch_one<T, 4, LAYOUT, XSRC, kSmallCtaThreads, MB>(x, K, p, dbg, s);
-        case 2: return launch_one<T, 2, LAYOUT, XSRC, kSmallCtaThreads, MB>(x, K, p, dbg, s);
-        case 1: return launch_one<T, 1, LAYOUT, XSRC, kSmallCtaThreads, MB>(x, K, p, dbg, s);
+    if (threads > kSmallCtaThreads) {
+        if (T > 2) return BPDQ_ERR_RANGE;
+        return launch_R2<(T > 2 ? 1 : T), LAYOUT, XSRC, kMidCtaThreads, 1>(x, K, p, dbg, s);
     }
-    return BPDQ_ERR_ARG;
+    return launch_R2<T, LAYOUT, XSRC, kSmallCtaThreads, (T == 1 ? 2 : 1)>(x, K, p, dbg, s);
 }
 
 template <int LAYOUT, int XSRC>
@@ -673,13 +680,25 @@ int gemm_q4k_q8k_multi(int n, const uint8_t* const* Ws, float* const* outs, cons
         if (((uintptr_t)Ws[j] & 15) || ((uintptr_t)outs[j] & 3)) return latch(BPDQ_ERR_ALIGN);
     }
     const size_t x_stride = xsrc == 0 ? (size_t)K * 4 : (size_t)(K / 256) * BPDQ_Q8K_BYTES;
-    const bool long_rows = ((K / 256 + 15) / 16 + 1) * 32 > kSmallCtaThreads;
-    const int per_pass = long_rows ? 1 : kMaxTokens;
+    int per_pass = kMaxTokens;
+    {
+        GemvPlan probe;
+        int rc = make_plan(Ms, n, K, 1, probe);
+        if (rc) return latch(rc);
+        const int threads = (probe.nw + 1) * 32;
+        if (threads > kMidCtaThreads) per_pass = 1;
+        else if (threads > kSmallCtaThreads) per_pass = 2;
+    }
     for (int t0 = 0; t0 < tokens; t0 += per_pass) {
         const int T = (tokens - t0) < per_pass ? (tokens - t0) : per_pass;
         GemvPlan p;
         int rc = make_plan(Ms, n, K, T, p);
         if (rc) return latch(rc);
+        if (g_trace_base && g_trace_left > 0) {
+            p.trace = g_trace_base;
+            g_trace_base += g_trace_stride;
+            g_trace_left--;
+        }
         for (int j = 0; j < n; j++) {
             p.prob[j].W = Ws[j];
             p.prob[j].out = outs[j] + (size_t)t0 * Ms[j];
@@ -702,6 +721,455 @@ int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M,
 {
     if (M < 0) return latch(BPDQ_ERR_ARG);
     return gemm_q4k_q8k_multi(1, &W, &out, &M, x, tokens, K, layout, xsrc, dbg, s);
+}
+
+
+// ================================================================ batched independent GEMVs
+//
+// One launch runs up to kMaxBatch independent products out_j = W_j . q8K(x_j), each with its
+// own shape (M_j, K_j); several may name the same x_j.  This is the shape of a decoder layer's
+// seven projections when nothing in between is computed (the benchmark workload), and of any
+// set of matrices that are known to be independent.
+//
+// Differences from the kernel above:
+//  * every consumer warp owns whole tiles and whole rows: a row longer than 4096 weights is
+//    walked in K-chunks of 4096 by the same warp (lane l takes half-super-block 32c + l of
+//    chunk c), so no warp ever waits for another one and the mapping does not depend on K;
+//  * all activation vectors of the launch are quantized once, up front, into shared memory
+//    as 144-byte records per half-super-block: 128 int8, then the four sub-block sums as
+//    int16 and the block scale (the padding of the layout above, put to use).  A lane fetches
+//    its record (nine 16-byte reads, conflict-free) once per tile and K-chunk;
+//  * accumulation order: a lane adds its half-blocks in ascending chunk order with the two
+//    FMAs of half_block_fma, then the rows are folded over the lanes by fold_rows.
+
+constexpr int kMaxBatch = 8;
+
+struct BatchProblem {
+    const uint8_t* W;
+    float* out;
+    int M, nb, row_bytes, rt;     // rows, super-blocks per row, bytes per row, rows per tile
+    int tile_begin;
+    int xq_off;                   // byte offset of this problem's activation records in shared memory
+};
+struct BatchVector {              // one distinct activation vector
+    const float* x;
+    int nb, xq_off;
+};
+struct BatchPlan {
+    int n_problems, n_vectors, n_tiles, total_blocks;
+    int nw, slots, slot_bytes, grid;
+    int off_ring, off_xq, off_bar;
+    size_t smem;
+    unsigned long long* trace;
+    // activation records already quantized by k_quant_records (same layout as the shared-memory
+    // records, xq_bytes in all), or null: quantize inside this kernel
+    const uint8_t* records;
+    int xq_bytes;
+    BatchProblem prob[kMaxBatch];
+    BatchVector vec[kMaxBatch];
+};
+
+
+// Quantizes one 256-block held by a warp (lane l: elements 4l..4l+3 in v0, 128+4l.. in v1) and
+// writes its two 144-byte records: 128 int8, four int16 sub-block sums, the fp32 block scale.
+__device__ __forceinline__ void write_records(const float4& v0, const float4& v1, uint8_t* rec0, int lane)
+{
+    uint32_t p0, p1;
+    float d;
+    quantize_block_256(v0, v1, p0, p1, d);
+    uint8_t* rec1 = rec0 + kXqStride;
+    reinterpret_cast<uint32_t*>(rec0)[lane] = p0;
+    reinterpret_cast<uint32_t*>(rec1)[lane] = p1;
+    int s0 = dp4a_ss(p0, 0x01010101u, 0), s1 = dp4a_ss(p1, 0x01010101u, 0);   // 8 lanes = one sub-block
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, o);
+        s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, o);
+    }
+    if ((lane & 7) == 0) {
+        reinterpret_cast<short*>(rec0 + 128)[lane >> 3] = (short)s0;
+        reinterpret_cast<short*>(rec1 + 128)[lane >> 3] = (short)s1;
+    }
+    if (lane == 0) {
+        reinterpret_cast<float*>(rec0 + 128)[2] = d;
+        reinterpret_cast<float*>(rec0 + 128)[3] = 0.0f;
+        reinterpret_cast<float*>(rec1 + 128)[2] = d;
+        reinterpret_cast<float*>(rec1 + 128)[3] = 0.0f;
+    }
+}
+
+struct QuantVectors {
+    int n_vectors, total_blocks;
+    BatchVector vec[kMaxBatch];
+};
+
+// Activation quantizer of the batched path: one warp per 256-block, records go to global
+// scratch memory in the layout the GEMV kernel keeps in shared memory.  The inputs are not
+// written by the kernel before it in the stream in any way this kernel could know, so it reads
+// them at once and only joins the stream order (pdl_wait) before it ends; the scratch it
+// writes must therefore not be in use by an earlier launch.
+__global__ void __launch_bounds__(256) k_quant_records(const QuantVectors q, uint8_t* __restrict__ records,
+                                                        int wait_first)
+{
+    pdl_launch_dependents();
+    if (wait_first) pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int n_warps = (gridDim.x * blockDim.x) >> 5;
+    for (int b = warp; b < q.total_blocks; b += n_warps) {
+        int blk = b, k = 0;
+        while (k + 1 < q.n_vectors && blk >= q.vec[k].nb) { blk -= q.vec[k].nb; k++; }
+        const float4* xb = reinterpret_cast<const float4*>(q.vec[k].x + (size_t)blk * 256);
+        const float4 v0 = __ldg(xb + lane), v1 = __ldg(xb + 32 + lane);
+        write_records(v0, v1, records + q.vec[k].xq_off + (size_t)(2 * blk) * kXqStride, lane);
+    }
+    if (!wait_first) pdl_wait();
+}
+
+template <int R, int LAYOUT>
+__device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8_t* xq, const BatchProblem& pb, int row0,
+                                           int lane)
+{
+    const int rows = min(R, pb.M - row0);
+    const int n_hb = 2 * pb.nb;
+    float acc[R][1];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r][0] = 0.0f;
+    for (int hb = lane; hb < n_hb; hb += 32) {
+        const uint4* rec = reinterpret_cast<const uint4*>(xq + (size_t)hb * kXqStride);
+        uint32_t xr[1][32];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint4 v = rec[i];
+            xr[0][4 * i + 0] = v.x;
+            xr[0][4 * i + 1] = v.y;
+            xr[0][4 * i + 2] = v.z;
+            xr[0][4 * i + 3] = v.w;
+        }
+        const uint4 tail = rec[8];
+        int bs[1][4];
+        bs[0][0] = (int)(short)(tail.x & 0xFFFFu);
+        bs[0][1] = (int)(short)(tail.x >> 16);
+        bs[0][2] = (int)(short)(tail.y & 0xFFFFu);
+        bs[0][3] = (int)(short)(tail.y >> 16);
+        float xd[1] = {__uint_as_float(tail.z)};
+        const uint8_t* sbp = tile_smem + (size_t)(hb >> 1) * BPDQ_Q4K_BYTES;
+#pragma unroll
+        for (int r = 0; r < R; r++)
+            if (r < rows) half_block_fma<1, LAYOUT>(sbp + (size_t)r * pb.row_bytes, hb & 1, xr, bs, xd, acc[r], nullptr);
+    }
+    float v[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) v[r] = acc[r][0];
+    const float total = fold_rows<R>(v, lane);
+    constexpr int kLanesPerRow = 32 / R;
+    const int my_row = lane / kLanesPerRow;
+    if ((lane % kLanesPerRow) == 0 && my_row < rows) pb.out[row0 + my_row] = total;
+}
+
+template <int LAYOUT, int MAXTHREADS>
+__global__ void __launch_bounds__(MAXTHREADS, 1)
+k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring = smem + p.off_ring;                                 // [nw][slots][slot_bytes]
+    uint8_t* xq = smem + p.off_xq;                                     // activation records
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bar);    // [nw*slots]
+    uint64_t* empty = full + p.nw * p.slots;
+    uint64_t* xbar = empty + p.nw * p.slots;                           // activation records have landed
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool is_producer = (warp == p.nw);
+    BPDQ_TRACE(0);
+    if (tid == 0) {
+        for (int s = 0; s < p.nw * p.slots; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(xbar, 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    BPDQ_TRACE(1);
+
+    if (is_producer) {
+        if (lane < p.nw) {
+            // lane g feeds consumer warp g; weights never depend on the previous kernel
+            const int g = lane;
+            int slot = 0;
+            uint32_t wait_parity = 0;
+            bool wrapped = false;
+            for (int v = g * (int)gridDim.x + (int)blockIdx.x; v < p.n_tiles; v += p.nw * (int)gridDim.x) {
+                const int s = g * p.slots + slot;
+                if (wrapped && !mbar_wait_bounded(&empty[s], wait_parity, err, 1)) break;
+                int j = 0;
+#pragma unroll
+                for (int q = 1; q < kMaxBatch; q++)
+                    if (q < p.n_problems && v >= p.prob[q].tile_begin) j = q;
+                const BatchProblem& pb = p.prob[j];
+                const int row0 = (v - pb.tile_begin) * pb.rt;
+                const uint32_t bytes = (uint32_t)min(pb.rt, pb.M - row0) * pb.row_bytes;
+                mbar_expect_tx(&full[s], bytes);
+                bulk_g2s(ring + (size_t)s * p.slot_bytes, pb.W + (size_t)row0 * pb.row_bytes, bytes, &full[s]);
+                if (++slot == p.slots) {
+                    slot = 0;
+                    if (wrapped) wait_parity ^= 1u;
+                    wrapped = true;
+                }
+            }
+            if (lane == 0) BPDQ_TRACE(7);
+        }
+        return;
+    }
+
+    if (p.records) {
+        // Records were written by the quantizer kernel launched just before this one: one thread
+        // waits for it (and so for everything earlier in the stream) and pulls them in with one
+        // bulk copy; everybody else waits for the bytes.
+        if (tid == 0) {
+            pdl_wait();
+            mbar_expect_tx(xbar, (uint32_t)p.xq_bytes);
+            bulk_g2s(xq, p.records, (uint32_t)p.xq_bytes, xbar);
+        }
+        BPDQ_TRACE(2);
+        if (!mbar_wait_bounded(xbar, 0, err, 3)) return;
+    } else {
+        // Activations may be written by the previous kernel: wait for it before the first read.
+        pdl_wait();
+        BPDQ_TRACE(2);
+        // ---- quantize every activation vector of the launch into shared memory (all consumer warps)
+        constexpr int UNR = 4;
+        for (int blk0 = warp; blk0 < p.total_blocks; blk0 += p.nw * UNR) {
+            float4 v0[UNR], v1[UNR];
+            int vb[UNR], vq[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; u++) {
+                int blk = blk0 + u * p.nw;
+                vb[u] = -1;
+                if (blk < p.total_blocks) {
+                    // every CTA reads the same vectors: start each one at a different block so
+                    // that the SMs do not all ask the same L2 lines at the same moment
+                    blk = (blk + (int)blockIdx.x * 5) % p.total_blocks;
+                    int k = 0;
+                    while (k + 1 < p.n_vectors && blk >= p.vec[k].nb) { blk -= p.vec[k].nb; k++; }
+                    const float4* xb = reinterpret_cast<const float4*>(p.vec[k].x + (size_t)blk * 256);
+                    v0[u] = __ldg(xb + lane);
+                    v1[u] = __ldg(xb + 32 + lane);
+                    vb[u] = blk;
+                    vq[u] = p.vec[k].xq_off;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNR; u++) {
+                if (vb[u] < 0) continue;
+                write_records(v0[u], v1[u], xq + vq[u] + (size_t)(2 * vb[u]) * kXqStride, lane);
+            }
+        }
+        named_bar_sync(2, p.nw * 32);
+    }
+    BPDQ_TRACE(3);
+
+    int slot = 0;
+    uint32_t parity = 0;
+    bool first = true;
+    for (int v = warp * (int)gridDim.x + (int)blockIdx.x; v < p.n_tiles; v += p.nw * (int)gridDim.x) {
+        const int s = warp * p.slots + slot;
+        if (!mbar_wait_bounded(&full[s], parity, err, 2)) return;
+        if (first) { BPDQ_TRACE(5); first = false; }
+        if (++slot == p.slots) {
+            slot = 0;
+            parity ^= 1u;
+        }
+        int j = 0;
+#pragma unroll
+        for (int q = 1; q < kMaxBatch; q++)
+            if (q < p.n_problems && v >= p.prob[q].tile_begin) j = q;
+        const BatchProblem& pb = p.prob[j];
+        const int row0 = (v - pb.tile_begin) * pb.rt;
+        const uint8_t* tile_smem = ring + (size_t)s * p.slot_bytes;
+        if (pb.rt == 4) batch_tile<4, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+        else if (pb.rt == 2) batch_tile<2, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+        else batch_tile<1, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    BPDQ_TRACE(6);
+}
+
+struct BatchDesc {
+    const uint8_t* W;
+    const float* x;
+    float* out;
+    int M, K;
+};
+
+// Builds the launch plan for descs[0..n); returns BPDQ_ERR_RANGE when the set does not fit one
+// launch (too many activations for shared memory, or rows longer than a ring slot).
+static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p)
+{
+    if (n < 1 || n > kMaxBatch) return BPDQ_ERR_RANGE;
+    const Tuning& tu = tuning();
+    const int slot_cap = 32 * 1024;
+    p.n_problems = n;
+    p.n_vectors = 0;
+    p.n_tiles = 0;
+    p.total_blocks = 0;
+    p.slot_bytes = 0;
+    p.trace = nullptr;
+    p.records = nullptr;
+    int xq_bytes = 0;
+    for (int j = 0; j < n; j++) {
+        if (d[j].M <= 0 || d[j].K <= 0 || (d[j].K % 256) != 0) return BPDQ_ERR_ARG;
+        BatchProblem& pb = p.prob[j];
+        pb.W = d[j].W;
+        pb.out = d[j].out;
+        pb.M = d[j].M;
+        pb.nb = d[j].K / 256;
+        pb.row_bytes = pb.nb * BPDQ_Q4K_BYTES;
+        if (pb.row_bytes > slot_cap) return BPDQ_ERR_RANGE;
+        pb.rt = 4 * pb.row_bytes <= tu.tile_bytes ? 4 : (2 * pb.row_bytes <= tu.tile_bytes ? 2 : 1);
+        if (pb.rt * pb.row_bytes > p.slot_bytes) p.slot_bytes = pb.rt * pb.row_bytes;
+        pb.tile_begin = p.n_tiles;
+        p.n_tiles += (pb.M + pb.rt - 1) / pb.rt;
+        int k = 0;
+        for (; k < p.n_vectors; k++)
+            if (p.vec[k].x == d[j].x && p.vec[k].nb == pb.nb) break;
+        if (k == p.n_vectors) {
+            p.vec[k].x = d[j].x;
+            p.vec[k].nb = pb.nb;
+            p.vec[k].xq_off = xq_bytes;
+            xq_bytes += 2 * pb.nb * kXqStride;
+            p.total_blocks += pb.nb;
+            p.n_vectors++;
+        }
+        pb.xq_off = p.vec[k].xq_off;
+    }
+    for (int j = n; j < kMaxBatch; j++) {
+        p.prob[j] = p.prob[0];
+        p.prob[j].tile_begin = 0x7FFFFFFF;
+    }
+    for (int k = p.n_vectors; k < kMaxBatch; k++) p.vec[k] = p.vec[0];
+    p.xq_bytes = xq_bytes;
+    p.slots = tu.stages < 2 ? 2 : tu.stages;
+    p.nw = tu.warps < 1 ? 1 : (tu.warps > 16 ? 16 : tu.warps);
+    for (;;) {
+        size_t off = 0;
+        auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
+        p.off_ring = take((size_t)p.nw * p.slots * p.slot_bytes);
+        p.off_xq = take((size_t)xq_bytes);
+        p.off_bar = take((size_t)2 * p.nw * p.slots * 8 + 8);
+        p.smem = off;
+        if (p.smem <= (size_t)kSmemLimit) break;
+        if (p.slots > 2) p.slots--;
+        else if (p.nw > 4) p.nw--;
+        else return BPDQ_ERR_RANGE;
+    }
+    long want = (p.n_tiles + p.nw - 1) / p.nw;
+    if (want < 1) want = 1;
+    p.grid = (int)(want < sm_count() ? want : sm_count());
+    return 0;
+}
+
+template <int LAYOUT>
+static int launch_batch(const BatchPlan& p, cudaStream_t s)
+{
+    auto kern = k_gemv_batch_q4k_q8k<LAYOUT, kMidCtaThreads>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+        if (rc) return rc;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3((p.nw + 1) * 32);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, p, device_error_flag()));
+}
+
+static int launch_quant_records(const BatchPlan& p, uint8_t* records, int wait_first, cudaStream_t s)
+{
+    QuantVectors q;
+    q.n_vectors = p.n_vectors;
+    q.total_blocks = p.total_blocks;
+    for (int k = 0; k < kMaxBatch; k++) q.vec[k] = p.vec[k];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.total_blocks + 7) / 8);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    return check_cuda(cudaLaunchKernelEx(&cfg, k_quant_records, q, records, wait_first));
+}
+
+// Independent GEMVs: as many launches as needed, each covering as many consecutive
+// descriptors as fit; a product that does not fit the batched kernel at all (K > 58254) runs
+// through the single-matrix kernel.
+//
+// ws / ws_bytes: optional scratch for the quantized activation records (144 bytes per 128
+// activations of every distinct vector of a launch).  With scratch, a small kernel quantizes
+// the activations once and the GEMV kernel bulk-copies the records; without it every CTA of the
+// GEMV kernel quantizes them itself.  ws_private: the caller promises that no earlier launch
+// still reads this scratch, so the quantizer need not wait for the stream before writing it.
+int gemv_q4k_q8k_batch(const BatchDesc* d, int n, int layout, uint8_t* ws, size_t ws_bytes, int ws_private,
+                       cudaStream_t s)
+{
+    if (n < 0 || (n > 0 && !d)) return latch(BPDQ_ERR_ARG);
+    if (ws && ((uintptr_t)ws & 15)) return latch(BPDQ_ERR_ALIGN);
+    for (int j = 0; j < n; j++) {
+        if (d[j].M < 0 || d[j].K <= 0 || (d[j].K % 256) != 0) return latch(BPDQ_ERR_ARG);
+        if (d[j].M > 0 && (!d[j].W || !d[j].x || !d[j].out)) return latch(BPDQ_ERR_ARG);
+        if (((uintptr_t)d[j].W & 15) || ((uintptr_t)d[j].x & 15) || ((uintptr_t)d[j].out & 3)) return latch(BPDQ_ERR_ALIGN);
+    }
+    int i = 0;
+    size_t ws_used = 0;
+    while (i < n) {
+        if (d[i].M == 0) { i++; continue; }
+        // longest run starting at i that fits one launch
+        BatchDesc run[kMaxBatch];
+        BatchPlan plan, good;
+        int len = 0;
+        while (i + len < n && len < kMaxBatch && d[i + len].M > 0) {
+            run[len] = d[i + len];
+            if (make_batch_plan(run, len + 1, plan) != 0) break;
+            good = plan;
+            len++;
+        }
+        if (len == 0) {
+            int rc = gemm_q4k_q8k(d[i].W, d[i].x, d[i].out, 1, d[i].M, d[i].K, layout, 0, nullptr, s);
+            if (rc) return rc;
+            i++;
+            continue;
+        }
+        if (ws && ws_used + (size_t)good.xq_bytes <= ws_bytes) {
+            uint8_t* rec = ws + ws_used;
+            ws_used += ((size_t)good.xq_bytes + 127) / 128 * 128;
+            int rc = launch_quant_records(good, rec, ws_private ? 0 : 1, s);
+            if (rc) return latch(rc);
+            good.records = rec;
+        }
+        if (g_trace_base && g_trace_left > 0) {
+            good.trace = g_trace_base;
+            g_trace_base += g_trace_stride;
+            g_trace_left--;
+        }
+        int rc = layout == BPDQ_LAYOUT_GGML ? launch_batch<BPDQ_LAYOUT_GGML>(good, s) : launch_batch<BPDQ_LAYOUT_BPD>(good, s);
+        if (rc) return latch(rc);
+        i += len;
+    }
+    return 0;
 }
 
 }  // namespace bpdq
@@ -742,6 +1210,30 @@ int bpd_qmatmul_q4k_q8k_multi_cuda(int n, const uint8_t* const* qweights, float*
                                    const float* x, int K, void* stream)
 {
     return gemm_q4k_q8k_multi(n, qweights, outs, Ms, x, 1, K, BPDQ_LAYOUT_BPD, 0, nullptr, (cudaStream_t)stream);
+}
+// n independent products in as few launches as possible (one, for a decoder layer's seven
+// projections).  descs is a HOST array of {W, x, out, M, K}.
+int bpd_qmatmul_q4k_q8k_batch_cuda(int n, const bpdq_gemv_desc* descs, void* stream)
+{
+    static_assert(sizeof(bpdq_gemv_desc) == sizeof(BatchDesc), "descriptor layouts must match");
+    return gemv_q4k_q8k_batch(reinterpret_cast<const BatchDesc*>(descs), n, BPDQ_LAYOUT_BPD, nullptr, 0, 0,
+                              (cudaStream_t)stream);
+}
+// Same, with caller-owned scratch for the quantized activations (bpdq_batch_workspace_bytes
+// says how much).  The scratch must not be in use by an earlier launch that may still run
+// (give every call in flight its own piece).
+int bpd_qmatmul_q4k_q8k_batch_ws_cuda(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes,
+                                      void* stream)
+{
+    return gemv_q4k_q8k_batch(reinterpret_cast<const BatchDesc*>(descs), n, BPDQ_LAYOUT_BPD, (uint8_t*)workspace,
+                              workspace_bytes, 1, (cudaStream_t)stream);
+}
+size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs)
+{
+    // upper bound: every vector distinct, each launch's share rounded up to 128 bytes
+    size_t total = 0;
+    for (int j = 0; j < n; j++) total += (size_t)(descs[j].K / 128) * kXqStride + 128;
+    return total;
 }
 // Full-control form: tokens >= 1, layout 0/1, xsrc 0 (fp32) / 1 (pre-quantized Q8_K), optional
 // int32 [M][K/256][8] buffer receiving token 0's exact sub-block dots.

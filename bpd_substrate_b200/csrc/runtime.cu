@@ -12,7 +12,7 @@ namespace bpdq {
 
 static std::atomic<cudaStream_t> g_stream{nullptr};
 static std::atomic<int> g_status{0};
-static Tuning g_tuning = {16384, 2, 2, 8, 1};
+static Tuning g_tuning = {8192, 2, 1, 16, 1};
 
 __device__ int g_dev_error = 0;
 

@@ -32,7 +32,9 @@ class LayerSet:
 
     * ``"separate"`` -- one launch per matrix (the reference's call sequence);
     * ``"grouped"``  -- matrices that read the same vector in a real decoder (q/k/v, gate/up)
-      share a launch and the first member's activation vector.
+      share a launch and the first member's activation vector;
+    * ``"batched"``  -- the seven independent products of a layer go to the device as ONE
+      launch (``bpd_qmatmul_q4k_q8k_batch_cuda``), each with its own activation vector.
     """
 
     def __init__(self, shapes=synth.MISTRAL_LAYER, n_layers=32, seed=2000, row_shard=(0, 1), lib=None,
@@ -78,6 +80,7 @@ class LayerSet:
         self.stream = lib.bpdq_stream_create()
         self.graph = {}
         self._keep = []
+        self.ws = None             # scratch for quantized activations (batched schedule)
         capi.check(lib.bpdq_last_status(), "LayerSet setup")
 
     # ---- sizes
@@ -86,6 +89,8 @@ class LayerSet:
         return self.n_layers * sum(synth.gemv_bytes_q4k(rows, cols) for _, rows, cols in self.local)
 
     def launches_per_step(self, schedule):
+        if schedule == "batched":
+            return 2 * self.n_layers      # activation quantizer + GEMV kernel per layer
         return self.n_layers * len(GROUPS_DECODE if schedule == "grouped" else GROUPS_NONE)
 
     def host_weight(self, layer, m):
@@ -104,6 +109,21 @@ class LayerSet:
     def enqueue_step(self, schedule="grouped", stream=None):
         """Queues one decode step's GEMVs on ``stream`` (default: this object's stream)."""
         lib, s = self.lib, (stream if stream is not None else self.stream)
+        if schedule == "batched":
+            nm = len(self.local)
+            for layer in range(self.n_layers):
+                descs = (capi.GemvDesc * nm)()
+                for m, (_, rows, cols) in enumerate(self.local):
+                    i = layer * nm + m
+                    descs[m] = capi.GemvDesc(self.weights[layer][m], self.d_x + self.x_off[i],
+                                             self.d_out + self.o_off[i], rows, cols)
+                if self.ws is None:
+                    self.ws_stride = (lib.bpdq_batch_workspace_bytes(nm, descs) + 255) // 256 * 256
+                    self.ws = lib.bpdq_alloc(self.ws_stride * self.n_layers)
+                # every layer has its own scratch: launches of one step never share it
+                capi.check(lib.bpd_qmatmul_q4k_q8k_batch_ws_cuda(nm, descs, self.ws + layer * self.ws_stride,
+                                                                 self.ws_stride, s), "batched GEMV launch")
+            return
         groups = GROUPS_DECODE if schedule == "grouped" else GROUPS_NONE
         for layer in range(self.n_layers):
             for members in groups:
@@ -175,6 +195,8 @@ class LayerSet:
                 lib.bpdq_free(p)
         self.weights = []
         lib.bpdq_free(self.d_x)
+        if self.ws is not None:
+            lib.bpdq_free(self.ws)
         if self._own_out:
             lib.bpdq_free(self.d_out)
         lib.bpdq_stream_destroy(self.stream)

@@ -133,6 +133,21 @@ int bpd_qmatmul_q4k_q8k_cuda(const uint8_t* qweight, const float* x, float* out,
 /* n <= 4 matrices that read the same x in ONE launch (q/k/v, gate/up): outs[j][Ms[j]] */
 int bpd_qmatmul_q4k_q8k_multi_cuda(int n, const uint8_t* const* qweights, float* const* outs, const int* Ms,
                                    const float* x, int K, void* stream);
+/* n independent products out_j[M_j] = W_j[M_j][K_j] . q8K(x_j[K_j]) in as few launches as
+ * possible (shapes may differ; several may share x).  descs is a host array. */
+typedef struct bpdq_gemv_desc {
+    const uint8_t* W;
+    const float* x;
+    float* out;
+    int M, K;
+} bpdq_gemv_desc;
+int bpd_qmatmul_q4k_q8k_batch_cuda(int n, const bpdq_gemv_desc* descs, void* stream);
+/* same with caller-owned device scratch for the quantized activations: a small kernel quantizes
+ * each distinct x once and the GEMV kernel bulk-copies the result, instead of every CTA
+ * quantizing every x.  The scratch must not be in use by a launch that may still be running. */
+int bpd_qmatmul_q4k_q8k_batch_ws_cuda(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes,
+                                      void* stream);
+size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs);
 /* out[tokens][M]; layout 0/1 as above; xsrc 0: x is float [tokens][K], 1: x is Q8_K blocks
  * [tokens][K/256]; subdots (may be NULL): int32 [M][K/256][8], token 0's exact sub-block dots */
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,

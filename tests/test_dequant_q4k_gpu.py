@@ -70,3 +70,21 @@ def test_full_tensor_14336x4096(lib, oracle):
     got = gpu_dequant(lib, q, nb)
     want = oracle.dequant_q4k(q, 0)
     assert hashlib.sha256(got.tobytes()).hexdigest() == hashlib.sha256(want.tobytes()).hexdigest()
+
+
+def test_full_tensor_against_reference_fixture(lib):
+    """Same tensor against the fixture written by the reference's own C code (hash + samples)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "q4k_dequant_14336x4096.npz"))
+    nb = int(g["n_blocks"][0])
+    q = synth.q4k_blocks(nb, int(g["seed"][0]))
+    got = gpu_dequant(lib, q, nb)
+    assert hashlib.sha256(got.tobytes()).hexdigest() == str(g["output_sha256"][0])
+    assert np.array_equal(got[::int(g["sample_stride"][0])].view(np.uint32), g["sample"])
+
+
+def test_small_fixture_from_reference(lib):
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "q4k_small.npz"))
+    got = gpu_dequant(lib, g["q"], g["q"].size // 144)
+    assert np.array_equal(got.view(np.uint32), g["dequant"])
