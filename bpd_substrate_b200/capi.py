@@ -80,6 +80,13 @@ SIGNATURES = {
     "bpdq_batch_workspace_bytes": (sz, [i32, vp]),
     "bpd_qmm_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),
+    # Q8_0
+    "bpd_dequant_q8_0_cuda": (i32, [vp, vp, sz, vp]),
+    "bpd_quant_q8_0_cuda": (i32, [vp, vp, sz, vp]),
+    "bpd_q8_0_block_dots_cuda": (i32, [vp, vp, vp, sz, vp]),
+    "bpd_qmatmul_q8_0_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "bpd_embed_lookup_q8_0_cuda": (i32, [vp, vp, vp, i32, i32, vp]),
+    "gpu_vecmat_q8_0": (None, [vp, vp, vp, i32, i32]),
     "gpu_matmul_q4k": (None, [vp, vp, vp, i32, i32, i32]),
 }
 

@@ -45,6 +45,9 @@ struct Tuning {
 };
 Tuning& tuning();
 
+// gemv_q4k.cu: bulk-copy GEMV for Q8_0 weights (BPDQ_ERR_RANGE when the shape needs the generic kernel)
+int gemv_q8_0_fast(const uint8_t* W, const float* x, float* out, int N, int K, cudaStream_t s);
+
 #ifdef __CUDACC__
 
 // ------------------------------------------------------------------ small device helpers

@@ -798,6 +798,83 @@ __device__ __forceinline__ void write_records(const float4& v0, const float4& v1
     }
 }
 
+// ---- Q8_0 weights (34-byte blocks: fp16 scale + 32 int8; bench/bpd_cpu.c:3886-3890 of the
+// reference) against Q8_0-quantized activations (rule of bench/bpd_cpu.c:4106-4136: stored
+// scale f16(amax/127), multiplier 127/amax, round half to even).  Same kernel skeleton; a lane
+// owns a PAIR of blocks (68 bytes = 17 aligned words of a row) and the activation record of a
+// pair is 80 bytes: 64 int8, the two block scales as fp32 (already widened from fp16), 8 spare.
+constexpr int kQ80PairStride = 80;
+
+// Quantizes 256 consecutive activations held by a warp (v0: elements 4l.., v1: 128+4l..) into
+// the four pair records starting at rec.  Eight lanes share one 32-element block.
+__device__ __forceinline__ void write_records_q80(const float4& v0, const float4& v1, uint8_t* rec, int lane)
+{
+    const float4 v[2] = {v0, v1};
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        float amax = fmaxf(fmaxf(fabsf(v[h].x), fabsf(v[h].y)), fmaxf(fabsf(v[h].z), fabsf(v[h].w)));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const __half d16 = __float2half_rn(__fdiv_rn(amax, 127.0f));
+        const float mul = (amax != 0.0f) ? __fdiv_rn(127.0f, amax) : 0.0f;
+        auto q = [mul](float x) -> uint32_t { return (uint32_t)__float2int_rn(__fmul_rn(x, mul)) & 0xFFu; };
+        const uint32_t packed = q(v[h].x) | (q(v[h].y) << 8) | (q(v[h].z) << 16) | (q(v[h].w) << 24);
+        const int blk = 4 * h + (lane >> 3);          // block 0..7 of the 256
+        uint8_t* pr = rec + (size_t)(blk >> 1) * kQ80PairStride;
+        reinterpret_cast<uint32_t*>(pr + 32 * (blk & 1))[lane & 7] = packed;
+        if ((lane & 7) == 0) reinterpret_cast<float*>(pr + 64)[blk & 1] = __half2float(d16);
+    }
+}
+
+template <int R>
+__device__ __forceinline__ void batch_tile_q80(const uint8_t* tile_smem, const uint8_t* xq, const BatchProblem& pb,
+                                               int row0, int lane)
+{
+    const int rows = min(R, pb.M - row0);
+    const int n_pairs = 4 * pb.nb;
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = 0.0f;
+    for (int pp = lane; pp < n_pairs; pp += 32) {
+        const uint4* rec = reinterpret_cast<const uint4*>(xq + (size_t)pp * kQ80PairStride);
+        uint32_t xr[16];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint4 t = rec[i];
+            xr[4 * i + 0] = t.x;
+            xr[4 * i + 1] = t.y;
+            xr[4 * i + 2] = t.z;
+            xr[4 * i + 3] = t.w;
+        }
+        const uint4 sc = rec[4];
+        const float ad0 = __uint_as_float(sc.x), ad1 = __uint_as_float(sc.y);
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            if (r < rows) {
+                const uint32_t* w = reinterpret_cast<const uint32_t*>(tile_smem + (size_t)r * pb.row_bytes) + 17 * pp;
+                uint32_t ww[17];
+#pragma unroll
+                for (int i = 0; i < 17; i++) ww[i] = w[i];
+                // block 0: scale = low half of word 0, quants = bytes 2..33 (realign by 16 bits)
+                int s0 = 0, s1 = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    s0 = dp4a_ss(__funnelshift_r(ww[i], ww[i + 1], 16), xr[i], s0);
+                    s1 = dp4a_ss(ww[9 + i], xr[8 + i], s1);   // block 1: quants are words 9..16
+                }
+                const float wd0 = f16_bits_to_f32(ww[0] & 0xFFFFu), wd1 = f16_bits_to_f32(ww[8] >> 16);
+                acc[r] = fmaf((float)s0, wd0 * ad0, acc[r]);
+                acc[r] = fmaf((float)s1, wd1 * ad1, acc[r]);
+            }
+        }
+    }
+    const float total = fold_rows<R>(acc, lane);
+    constexpr int kLanesPerRow = 32 / R;
+    const int my_row = lane / kLanesPerRow;
+    if ((lane % kLanesPerRow) == 0 && my_row < rows) pb.out[row0 + my_row] = total;
+}
+
+
 struct QuantVectors {
     int n_vectors, total_blocks;
     BatchVector vec[kMaxBatch];
@@ -808,6 +885,7 @@ struct QuantVectors {
 // written by the kernel before it in the stream in any way this kernel could know, so it reads
 // them at once and only joins the stream order (pdl_wait) before it ends; the scratch it
 // writes must therefore not be in use by an earlier launch.
+template <int FMT>
 __global__ void __launch_bounds__(256) k_quant_records(const QuantVectors q, uint8_t* __restrict__ records,
                                                         int wait_first)
 {
@@ -821,10 +899,12 @@ __global__ void __launch_bounds__(256) k_quant_records(const QuantVectors q, uin
         while (k + 1 < q.n_vectors && blk >= q.vec[k].nb) { blk -= q.vec[k].nb; k++; }
         const float4* xb = reinterpret_cast<const float4*>(q.vec[k].x + (size_t)blk * 256);
         const float4 v0 = __ldg(xb + lane), v1 = __ldg(xb + 32 + lane);
-        write_records(v0, v1, records + q.vec[k].xq_off + (size_t)(2 * blk) * kXqStride, lane);
+        if (FMT == 0) write_records(v0, v1, records + q.vec[k].xq_off + (size_t)(2 * blk) * kXqStride, lane);
+        else write_records_q80(v0, v1, records + q.vec[k].xq_off + (size_t)(4 * blk) * kQ80PairStride, lane);
     }
     if (!wait_first) pdl_wait();
 }
+
 
 template <int R, int LAYOUT>
 __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8_t* xq, const BatchProblem& pb, int row0,
@@ -867,7 +947,7 @@ __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8
     if ((lane % kLanesPerRow) == 0 && my_row < rows) pb.out[row0 + my_row] = total;
 }
 
-template <int LAYOUT, int MAXTHREADS>
+template <int FMT, int LAYOUT, int MAXTHREADS>
 __global__ void __launch_bounds__(MAXTHREADS, 1)
 k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
 {
@@ -963,7 +1043,8 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
 #pragma unroll
             for (int u = 0; u < UNR; u++) {
                 if (vb[u] < 0) continue;
-                write_records(v0[u], v1[u], xq + vq[u] + (size_t)(2 * vb[u]) * kXqStride, lane);
+                if (FMT == 0) write_records(v0[u], v1[u], xq + vq[u] + (size_t)(2 * vb[u]) * kXqStride, lane);
+                else write_records_q80(v0[u], v1[u], xq + vq[u] + (size_t)(4 * vb[u]) * kQ80PairStride, lane);
             }
         }
         named_bar_sync(2, p.nw * 32);
@@ -988,9 +1069,15 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
         const BatchProblem& pb = p.prob[j];
         const int row0 = (v - pb.tile_begin) * pb.rt;
         const uint8_t* tile_smem = ring + (size_t)s * p.slot_bytes;
-        if (pb.rt == 4) batch_tile<4, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-        else if (pb.rt == 2) batch_tile<2, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-        else batch_tile<1, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+        if (FMT == 0) {
+            if (pb.rt == 4) batch_tile<4, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+            else if (pb.rt == 2) batch_tile<2, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+            else batch_tile<1, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+        } else {
+            if (pb.rt == 4) batch_tile_q80<4>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+            else if (pb.rt == 2) batch_tile_q80<2>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+            else batch_tile_q80<1>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
@@ -1006,7 +1093,7 @@ struct BatchDesc {
 
 // Builds the launch plan for descs[0..n); returns BPDQ_ERR_RANGE when the set does not fit one
 // launch (too many activations for shared memory, or rows longer than a ring slot).
-static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p)
+static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt = 0)
 {
     if (n < 1 || n > kMaxBatch) return BPDQ_ERR_RANGE;
     const Tuning& tu = tuning();
@@ -1026,7 +1113,7 @@ static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p)
         pb.out = d[j].out;
         pb.M = d[j].M;
         pb.nb = d[j].K / 256;
-        pb.row_bytes = pb.nb * BPDQ_Q4K_BYTES;
+        pb.row_bytes = fmt == 0 ? pb.nb * BPDQ_Q4K_BYTES : pb.nb * 8 * BPDQ_Q80_BYTES;
         if (pb.row_bytes > slot_cap) return BPDQ_ERR_RANGE;
         pb.rt = 4 * pb.row_bytes <= tu.tile_bytes ? 4 : (2 * pb.row_bytes <= tu.tile_bytes ? 2 : 1);
         if (pb.rt * pb.row_bytes > p.slot_bytes) p.slot_bytes = pb.rt * pb.row_bytes;
@@ -1039,7 +1126,7 @@ static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p)
             p.vec[k].x = d[j].x;
             p.vec[k].nb = pb.nb;
             p.vec[k].xq_off = xq_bytes;
-            xq_bytes += 2 * pb.nb * kXqStride;
+            xq_bytes += fmt == 0 ? 2 * pb.nb * kXqStride : 4 * pb.nb * kQ80PairStride;
             p.total_blocks += pb.nb;
             p.n_vectors++;
         }
@@ -1071,10 +1158,10 @@ static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p)
     return 0;
 }
 
-template <int LAYOUT>
+template <int FMT, int LAYOUT>
 static int launch_batch(const BatchPlan& p, cudaStream_t s)
 {
-    auto kern = k_gemv_batch_q4k_q8k<LAYOUT, kMidCtaThreads>;
+    auto kern = k_gemv_batch_q4k_q8k<FMT, LAYOUT, kMidCtaThreads>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1111,7 +1198,7 @@ static int launch_quant_records(const BatchPlan& p, uint8_t* records, int wait_f
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = tuning().pdl ? 1 : 0;
-    return check_cuda(cudaLaunchKernelEx(&cfg, k_quant_records, q, records, wait_first));
+    return check_cuda(cudaLaunchKernelEx(&cfg, k_quant_records<0>, q, records, wait_first));
 }
 
 // Independent GEMVs: as many launches as needed, each covering as many consecutive
@@ -1165,11 +1252,24 @@ int gemv_q4k_q8k_batch(const BatchDesc* d, int n, int layout, uint8_t* ws, size_
             g_trace_base += g_trace_stride;
             g_trace_left--;
         }
-        int rc = layout == BPDQ_LAYOUT_GGML ? launch_batch<BPDQ_LAYOUT_GGML>(good, s) : launch_batch<BPDQ_LAYOUT_BPD>(good, s);
+        int rc = layout == BPDQ_LAYOUT_GGML ? launch_batch<0, BPDQ_LAYOUT_GGML>(good, s) : launch_batch<0, BPDQ_LAYOUT_BPD>(good, s);
         if (rc) return latch(rc);
         i += len;
     }
     return 0;
+}
+
+// Q8_0 weights [N][K/32][34] times one activation vector, activations quantized to Q8_0 inside
+// the kernel.  Fast path only: K a multiple of 256 (rows are then 16-byte multiples and can be
+// bulk-copied); returns BPDQ_ERR_RANGE otherwise so that the caller can take the generic kernel.
+int gemv_q8_0_fast(const uint8_t* W, const float* x, float* out, int N, int K, cudaStream_t s)
+{
+    if ((K % 256) != 0 || ((uintptr_t)W & 15) || ((uintptr_t)x & 15)) return BPDQ_ERR_RANGE;
+    BatchDesc d = {W, x, out, N, K};
+    BatchPlan plan;
+    int rc = make_batch_plan(&d, 1, plan, 1);
+    if (rc) return rc;
+    return launch_batch<1, BPDQ_LAYOUT_BPD>(plan, s);
 }
 
 }  // namespace bpdq

@@ -158,6 +158,21 @@ int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int 
 void gpu_vecmat_q4k(const float* a, const uint8_t* wq, float* c, int k, int n);
 void gpu_matmul_q4k(const float* A, const uint8_t* wq, float* C, int M, int N, int K);
 
+/* ---- Q8_0 (34-byte blocks: fp16 scale + 32 int8), device-pointer twins of the CPU entries --- */
+/* bench/bpd_cpu.c:3960-3973  bpd_dequant_q8_0_cpu */
+int bpd_dequant_q8_0_cuda(const uint8_t* raw, float* out, size_t n_blocks, void* stream);
+/* bench/bpd_cpu.c:4106-4136  bpd_quant_q8_0_cpu (byte-identical blocks) */
+int bpd_quant_q8_0_cuda(const float* x, uint8_t* y, size_t n_elements, void* stream);
+/* the exact int32 core of bench/bpd_cpu.c:4263-4280 bpd_qdot_q8_0_q8_0_cpu, per block */
+int bpd_q8_0_block_dots_cuda(const uint8_t* w, const uint8_t* a, int32_t* dots, size_t n_blocks, void* stream);
+/* bench/bpd_cpu.c:4295-4315  bpd_qmatmul_q8_0_cpu: out[m*N+n] = W row n . q8_0(X row m) */
+int bpd_qmatmul_q8_0_cuda(const uint8_t* W, const float* X, float* out, int M, int N, int K, void* stream);
+/* bench/bpd_cpu.c:4002-4013  bpd_embed_lookup_q8_0_cpu */
+int bpd_embed_lookup_q8_0_cuda(const uint8_t* table, const int32_t* ids, float* out, int n_tokens, int embed_dim,
+                               void* stream);
+/* gpu_vecmat's argument order (lib/kernel_templates_llama.pl:147-158) with Q8_0 rows [n][k/32][34] */
+void gpu_vecmat_q8_0(const float* a, const uint8_t* wq, float* c, int k, int n);
+
 #ifdef __cplusplus
 }
 #endif
