@@ -78,6 +78,8 @@ SIGNATURES = {
     "bpd_qmatmul_q4k_q8k_batch_cuda": (i32, [i32, vp, vp]),
     "bpd_qmatmul_q4k_q8k_batch_ws_cuda": (i32, [i32, vp, vp, sz, vp]),
     "bpdq_batch_workspace_bytes": (sz, [i32, vp]),
+    "bpd_qmatmul_q4k_q8k_batch_static_cuda": (i32, [i32, vp, vp]),
+    "bpdq_batch_static_capacity": (sz, []),
     "bpd_qmm_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),
     # Q8_0

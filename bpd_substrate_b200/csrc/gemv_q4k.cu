@@ -1272,6 +1272,38 @@ int gemv_q8_0_fast(const uint8_t* W, const float* x, float* out, int N, int K, c
     return launch_batch<1, BPDQ_LAYOUT_BPD>(plan, s);
 }
 
+// ---------------------------------------------------------------- scratch without an allocator
+//
+// Scratch for the quantized activation records of bpd_qmatmul_q4k_q8k_batch_static_cuda: a
+// fixed array inside the library image.  Every GPU that loads the library carries these bytes
+// until the process exits.
+constexpr size_t kStaticRecordBytes = 256 * 1024;   // room for 233,016 activations per call
+static __device__ __align__(256) uint8_t g_static_records[kStaticRecordBytes];
+
+// In host code the name g_static_records is only a handle for the runtime, not a device
+// address: it must be translated once per device, with that device current.
+static uint8_t* static_records_address(int* status)
+{
+    static uint8_t* cached[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        *status = e != cudaSuccess ? check_cuda(e) : latch(BPDQ_ERR_RANGE);
+        return nullptr;
+    }
+    if (!cached[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_records);
+        if (e != cudaSuccess || !p) {
+            *status = e != cudaSuccess ? check_cuda(e) : latch(BPDQ_ERR_CUDA);
+            return nullptr;
+        }
+        cached[dev] = (uint8_t*)p;
+    }
+    *status = 0;
+    return cached[dev];
+}
+
 }  // namespace bpdq
 
 using namespace bpdq;
@@ -1335,6 +1367,22 @@ size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs)
     for (int j = 0; j < n; j++) total += (size_t)(descs[j].K / 128) * kXqStride + 128;
     return total;
 }
+// Batched GEMVs for callers that must not allocate device memory (see include/bpdq.h).
+int bpd_qmatmul_q4k_q8k_batch_static_cuda(int n, const bpdq_gemv_desc* descs, void* stream)
+{
+    if (n < 0 || (n > 0 && !descs)) return latch(BPDQ_ERR_ARG);
+    // the records of all launches of this call sit side by side in the fixed array
+    if (bpdq_batch_workspace_bytes(n, descs) > kStaticRecordBytes) return latch(BPDQ_ERR_RANGE);
+    int rc = 0;
+    uint8_t* records = static_records_address(&rc);
+    if (!records) return rc;
+    // ws_private = 0: the quantizer waits for everything earlier in the stream before it writes,
+    // because the previous call on this stream may still be reading the same array
+    return gemv_q4k_q8k_batch(reinterpret_cast<const BatchDesc*>(descs), n, BPDQ_LAYOUT_BPD, records,
+                              kStaticRecordBytes, 0, (cudaStream_t)stream);
+}
+size_t bpdq_batch_static_capacity(void) { return kStaticRecordBytes; }
+
 // Full-control form: tokens >= 1, layout 0/1, xsrc 0 (fp32) / 1 (pre-quantized Q8_K), optional
 // int32 [M][K/256][8] buffer receiving token 0's exact sub-block dots.
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,

@@ -148,6 +148,24 @@ int bpd_qmatmul_q4k_q8k_batch_cuda(int n, const bpdq_gemv_desc* descs, void* str
 int bpd_qmatmul_q4k_q8k_batch_ws_cuda(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes,
                                       void* stream);
 size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs);
+/* No counterpart in the reference.  The same batched product for callers that cannot allocate
+ * device memory at the time of the call: plugins of a host application that owns every byte of
+ * the GPU and hands out none, code in a region where the CUDA allocator must not be entered
+ * (cudaMalloc and cudaFree synchronize the whole device), and latency-bound loops that may not
+ * pay for an allocation.  The scratch for the quantized activations
+ * is a fixed 256 KiB array inside the library (bpdq_batch_static_capacity(); every GPU that
+ * loads the library holds it until the process ends), so this entry point allocates nothing
+ * and frees nothing; inputs and outputs are still the caller's.
+ *  - Limit: bpdq_batch_workspace_bytes(n, descs) must not exceed the capacity (about 233,000
+ *    activations over the call's vectors); a larger call returns -3 and launches nothing.
+ *  - The first call on a device looks up the array's device address and sets kernel
+ *    attributes; make that first call before any stream capture begins.
+ *  - Every call uses the same array and overwrites what the previous call left there (nothing
+ *    in it needs to start at zero).  Calls on ONE stream are ordered by the library; calls that
+ *    can overlap on the GPU (different streams, different host threads) race on the array and
+ *    must be serialized by the caller. */
+int bpd_qmatmul_q4k_q8k_batch_static_cuda(int n, const bpdq_gemv_desc* descs, void* stream);
+size_t bpdq_batch_static_capacity(void);
 /* out[tokens][M]; layout 0/1 as above; xsrc 0: x is float [tokens][K], 1: x is Q8_K blocks
  * [tokens][K/256]; subdots (may be NULL): int32 [M][K/256][8], token 0's exact sub-block dots */
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,
