@@ -82,6 +82,18 @@ SIGNATURES = {
     "bpdq_batch_static_capacity": (sz, []),
     "bpd_qmm_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),
+    # fp32 decode operators
+    "gpu_vecmat": (None, [vp, vp, vp, i32, i32]),
+    "gpu_rms_norm": (None, [vp, vp, vp, i32, i32, f32]),
+    "gpu_add": (None, [vp, vp, vp, i32]),
+    "gpu_mul": (None, [vp, vp, vp, i32]),
+    "gpu_silu": (None, [vp, vp, i32]),
+    "gpu_matmul": (None, [vp, vp, vp, i32, i32, i32]),
+    "gpu_matmul_opt": (None, [vp, vp, vp, i32, i32, i32]),
+    # Q4_K x fp32
+    "bpd_qmatmul_q4k_gpu": (None, [vp, vp, vp, i32, i32]),
+    "bpd_qmatmul_q4k_gpu_st": (i32, [vp, vp, vp, i32, i32, vp]),
+    "bpd_qmm_q4k_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     # Q8_0
     "bpd_dequant_q8_0_cuda": (i32, [vp, vp, sz, vp]),
     "bpd_quant_q8_0_cuda": (i32, [vp, vp, sz, vp]),

@@ -176,6 +176,13 @@ int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int 
 void gpu_vecmat_q4k(const float* a, const uint8_t* wq, float* c, int k, int n);
 void gpu_matmul_q4k(const float* A, const uint8_t* wq, float* C, int M, int N, int K);
 
+/* ---- Q4_K weights x fp32 activations (no activation quantization) --------------------------- */
+/* bench/bpd_quant_gpu.cu:166-169  output[M] = dequant(qweight[M][K]) . x[K] */
+void bpd_qmatmul_q4k_gpu(const uint8_t* qweight, const float* x, float* output, int M, int K);
+int bpd_qmatmul_q4k_gpu_st(const uint8_t* qweight, const float* x, float* output, int M, int K, void* stream);
+/* bench/bpd_quant.c:114-137 (bpd_qmm_q4k) on device pointers: C[M][N] = dequant(qA[M][K]) @ B[K][N] */
+int bpd_qmm_q4k_cuda(const uint8_t* qA, const float* B, float* C, int M, int N, int K, void* stream);
+
 /* ---- Q8_0 (34-byte blocks: fp16 scale + 32 int8), device-pointer twins of the CPU entries --- */
 /* bench/bpd_cpu.c:3960-3973  bpd_dequant_q8_0_cpu */
 int bpd_dequant_q8_0_cuda(const uint8_t* raw, float* out, size_t n_blocks, void* stream);
@@ -190,6 +197,19 @@ int bpd_embed_lookup_q8_0_cuda(const uint8_t* table, const int32_t* ids, float* 
                                void* stream);
 /* gpu_vecmat's argument order (lib/kernel_templates_llama.pl:147-158) with Q8_0 rows [n][k/32][34] */
 void gpu_vecmat_q8_0(const float* a, const uint8_t* wq, float* c, int k, int n);
+
+/* ---- fp32 operators of the decode dispatch (inference/llamatov_gpu_llama.py:15-31) ----------- */
+/* lib/kernel_templates_llama.pl:147-158  c[n] = a[k] . b[k][n] */
+void gpu_vecmat(const float* a, const float* b, float* c, int k, int n);
+/* lib/kernel_templates_llama.pl:583-593 */
+void gpu_rms_norm(const float* in, const float* w, float* out, int rows, int cols, float eps);
+/* lib/kernel_templates_llama.pl:600-830 (binary elementwise; silu = x / (1 + expf(-x)), :668) */
+void gpu_add(const float* a, const float* b, float* out, int n);
+void gpu_mul(const float* a, const float* b, float* out, int n);
+void gpu_silu(const float* in, float* out, int n);
+/* lib/kernel_templates_llama.pl:1104-1290, lib/kernel_templates_blas.pl:2146-2153  C[M][N] = A[M][K] @ B[K][N] */
+void gpu_matmul(const float* A, const float* B, float* C, int M, int N, int K);
+void gpu_matmul_opt(const float* A, const float* B, float* C, int M, int N, int K);
 
 #ifdef __cplusplus
 }
