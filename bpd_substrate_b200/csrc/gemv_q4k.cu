@@ -720,6 +720,10 @@ int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M,
                  int32_t* dbg, cudaStream_t s)
 {
     if (M < 0) return latch(BPDQ_ERR_ARG);
+    // many tokens: the weights would be streamed once per four tokens here; the tensor-core
+    // kernel reads them once per 64
+    if (tokens > 8 && layout == BPDQ_LAYOUT_BPD && xsrc == 0 && !dbg)
+        return gemm_q4k_q8k_mma(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s);
     return gemm_q4k_q8k_multi(1, &W, &out, &M, x, tokens, K, layout, xsrc, dbg, s);
 }
 
@@ -1390,6 +1394,12 @@ int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int 
 {
     if ((layout != 0 && layout != 1) || (xsrc != 0 && xsrc != 1)) return latch(BPDQ_ERR_ARG);
     return gemm_q4k_q8k(qweight, x, out, tokens, M, K, layout, xsrc, subdots, (cudaStream_t)stream);
+}
+
+// The tensor-core kernel at any token count (the dispatcher above picks it for more than 8).
+int bpd_qmm_q4k_q8k_mma_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream)
+{
+    return gemm_q4k_q8k_mma(qweight, X, out, tokens, M, K, (cudaStream_t)stream);
 }
 
 // Dispatch-shaped entries (argument order of gpu_vecmat / gpu_matmul,

@@ -1,0 +1,117 @@
+"""Timings of the secondary configurations (the benchmark line itself comes from bench.py).
+
+    python -m bpd_substrate_b200.measure            # prints one JSON object per configuration
+
+Cold-HBM protocol: every timed launch reads a different copy of its weights, with enough
+copies that the working set is several times the L2 size, so no launch finds its inputs
+cached.  Times are CUDA events on the launching stream around `iters` launches.
+"""
+import json
+import sys
+
+import numpy as np
+
+from . import capi, synth
+
+PEAK_FALLBACK = 6650.0
+
+
+def _peak():
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["hbm_gbs"])
+    except Exception:
+        return PEAK_FALLBACK
+
+
+class Timer:
+    def __init__(self, lib):
+        self.lib = lib
+        self.stream = lib.bpdq_stream_create()
+        self.e0, self.e1 = lib.bpdq_event_create(), lib.bpdq_event_create()
+
+    def run(self, fn, iters, warm=3):
+        lib = self.lib
+        for i in range(warm):
+            fn(i)
+        lib.bpdq_stream_sync(self.stream)
+        lib.bpdq_event_record(self.e0, self.stream)
+        for i in range(iters):
+            fn(i)
+        lib.bpdq_event_record(self.e1, self.stream)
+        return lib.bpdq_event_elapsed_ms(self.e0, self.e1) / iters * 1e3   # microseconds
+
+
+def _dev(lib, arr):
+    p = lib.bpdq_alloc(arr.nbytes)
+    lib.bpdq_h2d(p, arr.ctypes.data, arr.nbytes)
+    return p
+
+
+def _copies(nbytes, target=600e6):
+    return max(2, int(target // nbytes) + 1)
+
+
+def main():
+    lib = capi.load()
+    lib.bpdq_clear_status()
+    peak = _peak()
+    tm = Timer(lib)
+    s = tm.stream
+    out = []
+
+    def report(name, us, nbytes, **extra):
+        gbs = nbytes / us / 1e3
+        rec = dict(config=name, us=round(us, 2), algorithmic_bytes=nbytes, gbs=round(gbs, 1),
+                   pct_of_measured_peak=round(100 * gbs / peak, 1), **extra)
+        out.append(rec)
+        print(json.dumps(rec), flush=True)
+
+    # ---- config 0: Q4_K dequant of a 14336 x 4096 tensor
+    nb = 14336 * 16
+    q = synth.q4k_blocks(nb, 1000)
+    qs = [_dev(lib, q) for _ in range(4)]
+    os_ = [lib.bpdq_alloc(nb * 1024) for _ in range(3)]
+    us = tm.run(lambda i: lib.bpd_dequant_q4k_gpu_st(qs[i % 4], os_[i % 3], nb, 0, s), 30)
+    report("0: Q4_K dequant 14336x4096", us, nb * (144 + 1024), elements_per_s=nb * 256 / us * 1e6)
+    for p in qs + os_:
+        lib.bpdq_free(p)
+
+    # ---- config 1: Q8_0 GEMV 4096 x 4096 with in-kernel activation quantization
+    N = K = 4096
+    W = synth.q8_0_matrix(N, K, 1001)
+    n = _copies(W.nbytes)
+    ws = [_dev(lib, W) for _ in range(n)]
+    x, o = _dev(lib, synth.activations(K, 1002)), lib.bpdq_alloc(N * 4)
+    us = tm.run(lambda i: lib.bpd_qmatmul_q8_0_cuda(ws[i % n], x, o, 1, N, K, s), 100)
+    report("1: Q8_0 GEMV 4096x4096 (single launches back to back)", us, synth.gemv_bytes_q8_0(N, K))
+    for p in ws + [x, o]:
+        lib.bpdq_free(p)
+
+    # ---- config 3: Q4_K x Q8_K GEMM, N=14336, K=4096, M tokens
+    N, K = 14336, 4096
+    W = synth.q4k_matrix(N, K, 1003)
+    n = _copies(W.nbytes)
+    ws = [_dev(lib, W) for _ in range(n)]
+    for M in (1, 4, 16, 64):
+        X = _dev(lib, synth.activations(K, 1004, rows=M))
+        o = lib.bpdq_alloc(M * N * 4)
+        us = tm.run(lambda i: lib.bpd_qmm_q4k_q8k_cuda(ws[i % n], X, o, M, N, K, 0, 0, None, s), 50)
+        report(f"3: Q4_K x Q8_K GEMM M={M} N=14336 K=4096", us, synth.gemv_bytes_q4k(N, K, M),
+               tflops=round(2.0 * M * N * K / us / 1e6, 2))
+        lib.bpdq_free(X)
+        lib.bpdq_free(o)
+    # ---- W4A32 drop-in on the same matrix
+    x, o = _dev(lib, synth.activations(K, 1005)), lib.bpdq_alloc(N * 4)
+    us = tm.run(lambda i: lib.bpd_qmatmul_q4k_gpu_st(ws[i % n], x, o, N, K, s), 20)
+    report("W4A32 GEMV 14336x4096 (bpd_qmatmul_q4k_gpu)", us, synth.gemv_bytes_q4k(N, K))
+    for p in ws + [x, o]:
+        lib.bpdq_free(p)
+    status = lib.bpdq_last_status()
+    print(json.dumps({"status": status}))
+    return 0 if status == 0 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -170,6 +170,9 @@ size_t bpdq_batch_static_capacity(void);
  * [tokens][K/256]; subdots (may be NULL): int32 [M][K/256][8], token 0's exact sub-block dots */
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,
                          int xsrc, int32_t* subdots, void* stream);
+/* the int8 tensor-core kernel behind bpd_qmm_q4k_q8k_cuda for more than 8 tokens, callable at any
+ * token count: out[tokens][M], X float [tokens][K], nibble order of bench/bpd_quant.c:68-72 */
+int bpd_qmm_q4k_q8k_mma_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream);
 /* dispatch-shaped forms: argument order of gpu_vecmat (lib/kernel_templates_llama.pl:147-158)
  * and gpu_matmul (lib/kernel_templates_llama.pl:1104-1112) with the fp32 [K][N] weight
  * replaced by Q4_K rows [N][K/256][144] */

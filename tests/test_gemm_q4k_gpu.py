@@ -1,0 +1,56 @@
+"""Batched Q4_K x Q8_K product (many tokens): the int8 tensor-core kernel against the checker."""
+import numpy as np
+import pytest
+
+from bpd_substrate_b200 import synth
+from tests.util import Dev, normwise
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def run(lib, entry, W, X, T, N, K):
+    dW, dX, dO = Dev(lib, W), Dev(lib, X), Dev(lib, nbytes=T * N * 4, fill=0xFF)
+    if entry == "mma":
+        rc = lib.bpd_qmm_q4k_q8k_mma_cuda(dW.ptr, dX.ptr, dO.ptr, T, N, K, None)
+    else:
+        rc = lib.bpd_qmm_q4k_q8k_cuda(dW.ptr, dX.ptr, dO.ptr, T, N, K, 0, 0, None, None)
+    assert rc == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == 0
+    return dO.read(np.float32).reshape(T, N)
+
+
+@pytest.mark.parametrize("T,N,K", [(16, 128, 256), (16, 300, 1024), (9, 64, 4096), (33, 112, 512), (64, 260, 4096),
+                                   (1, 40, 256), (70, 100, 768), (130, 48, 256)])
+def test_mma_kernel_matches_checker(lib, oracle, T, N, K):
+    rng = np.random.default_rng(T * 7 + N + K)
+    W = synth.q4k_matrix(N, K, rng)
+    X = synth.activations(K, rng, rows=T)
+    got = run(lib, "mma", W, X, T, N, K)
+    ref32, ref64 = oracle.qmm_q4k_q8k(W, X, T, N, K)
+    assert normwise(got, ref64) <= TOL
+
+
+def test_dispatcher_agrees_across_token_counts(lib, oracle):
+    """1..4 tokens (dp4a kernel), 16 and 64 tokens (tensor cores): each token's row equals the
+    checker, whatever kernel produced it."""
+    N, K = 96, 2048
+    rng = np.random.default_rng(5)
+    W = synth.q4k_matrix(N, K, rng)
+    X = synth.activations(K, rng, rows=64)
+    _, ref64 = oracle.qmm_q4k_q8k(W, X, 64, N, K)
+    for T in (1, 4, 16, 64):
+        got = run(lib, "dispatch", W, X[:T], T, N, K)
+        assert normwise(got, ref64[:T]) <= TOL, T
+
+
+def test_gpu_matmul_q4k_entry(lib, oracle):
+    T, N, K = 24, 80, 1024
+    rng = np.random.default_rng(6)
+    W, X = synth.q4k_matrix(N, K, rng), synth.activations(K, rng, rows=T)
+    dW, dX, dO = Dev(lib, W), Dev(lib, X), Dev(lib, nbytes=T * N * 4)
+    lib.gpu_matmul_q4k(dX.ptr, dW.ptr, dO.ptr, T, N, K)
+    lib.gpu_sync()
+    assert lib.bpdq_last_status() == 0
+    assert normwise(dO.read(np.float32).reshape(T, N), oracle.qmm_q4k_q8k(W, X, T, N, K)[1]) <= TOL
