@@ -1,53 +1,58 @@
-// Batched Q4_K x Q8_K product for 8 < tokens: int8 tensor-core MMA on raw nibbles.
+// Batched Q4_K x Q8_K product for many tokens: int8 tensor-core MMA on raw nibbles.
 //
-// out[t][n] = sum_b [ (d_nb * dA_tb) * isum - (dmin_nb * dA_tb) * msum ],
-//   isum = sum_j sc_j * sum_{k in sub-block j} q_k * x_k,   msum = sum_j mn_j * sum_{k in j} x_k
-// (the definition of gemv_q4k.cu, exact integers inside a super-block).  The integer sums run
-// on the tensor cores without ever leaving the integer domain:
-//   * a 6-bit scale is split sc = 8*sh + sl; the byte-wise products q*sl and q*sh are < 128, so
-//     (w & 0x0F0F0F0F) * sl is four int8 operands from ONE 32-bit multiply;
-//   * isum = 8 * acc_hi + acc_lo with two int32 accumulators that run over the eight
-//     sub-blocks of a super-block; msum comes from a third accumulator whose A operand is mn_j
-//     replicated over the sub-block;
-//   * the fp32 scales are applied once per super-block.
-// MMA shape: mma.sync.m16n8k32 s8 x s8 -> s32.  A warp owns 16 weight rows (A fragments are built
-// in registers straight from the packed nibbles: thread (g,t) needs word t of the 16-byte
-// sub-block of rows g and g+8), and all tokens (NT n-tiles of 8).
+// out[t][n] = sum_b dA_tb * ( d_nb * isum - dmin_nb * msum ),
+//   isum = sum_j sc_j * sum_{k in sub-block j} q_k * x_k,   msum = sum_j mn_j * bsum_tj
+// (the definition of gemv_q4k.cu; every integer is exact).  A sub-block is exactly the K depth
+// of one mma.sync.m16n8k32 (s8 x s8 -> s32): the raw nibbles 0..15 are the A operand, built in
+// registers straight from the packed bytes (thread (g,t) needs word t of the 16-byte
+// sub-block of rows g and g+8: low nibbles are k = 4t..4t+3, high nibbles k = 16+4t..), the
+// int8 activations the B operand; the 6-bit scale multiplies the int32 result (4 IMAD per
+// MMA), and the min term uses the activations' sub-block sums with dp2a.  A warp owns 16
+// weight rows and all tokens (NT n-tiles of 8).
 //
 // Data movement: activations are quantized once by k_quant_gemm_acts into global scratch laid
-// out [K/256][tokens_padded][272 B] (256 int8, fp32 scale, pad: the 272-byte pitch makes the
-// B-fragment reads conflict-free); a CTA of W warps (16*W rows) walks K in stages of two
-// super-blocks: the producer warp bulk-copies each row's 288-byte piece (pitch 304 B in shared
-// memory, conflict-free A reads) and the stage's activation chunk into a ring with full/empty
-// mbarriers.  Accumulation order: super-blocks in ascending order, one fp32 accumulator per
-// output, acc += dA * (d * float(isum) - dmin * float(msum)).
+// out [K/256][tokens_padded][288 B]: 256 int8 (words permuted so that a thread's two B words
+// are adjacent: one 8-byte read, conflict-free at this pitch), fp32 scale, eight int16
+// sub-block sums.  A CTA of W warps (16*W rows) walks K in stages of two super-blocks; per
+// stage the producer issues TWO requests: a tiled TMA copy (cp.async.bulk.tensor.2d, box
+// 288 bytes x 16*W rows of the [N][K/256*144] byte matrix; rows past the end are zero-filled)
+// and one bulk copy of the stage's activations, into a ring with full/empty mbarriers.
+// Accumulation order: super-blocks ascending, one fp32 accumulator per output,
+// acc = fma(dA, d * float(isum) - dmin * float(msum), acc).
 #include "bpdq_common.cuh"
 #include "../../include/bpdq.h"
 
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
 namespace bpdq {
 
-constexpr int kActPitch = 272;     // bytes per (super-block, token) in scratch and in shared memory
-constexpr int kRowPitch = 304;     // shared-memory pitch of a row's two-super-block piece (288 B + 16)
+constexpr int kActPitch = 288;     // bytes per (super-block, token) in scratch and in shared memory
 constexpr int kSbPerStage = 2;
 
 struct GemmPlan {
     int N, K, nb, tokens, tok_pad;   // weight rows, K, super-blocks per row, valid tokens, padded tokens (8*NT)
-    int warps;                       // consumer warps per CTA (16 rows each)
+    int warps;                       // consumer warps per CTA = row groups (16 rows each) x ts
+    int ts;                          // warps that share a row group, each taking NT n-tiles of the tokens
     int stages, n_tiles, grid;
     int stage_bytes, act_bytes;      // bytes per ring slot, of which activations
+    int row_pitch, box_rows;         // TMA box: bytes per row piece (144 or 288), rows (<= N)
     size_t smem;
 };
 
-__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+// D = A x B (no accumulator input: the C operand is the zero register)
+__device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
     asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
 
 // Activation quantizer for the GEMM path: one warp per (token, super-block); writes the
-// 272-byte record at [b][t] (tokens >= `tokens` up to tok_pad are written as zeros).
+// 288-byte record at [b][t] (tokens >= `tokens` up to tok_pad are written as zeros).  Word w of
+// the 64 quant words (elements 4w..4w+3) is stored at position 8*(w/8) + 2*(w%4) + (w%8)/4, so
+// that words 8j+t and 8j+4+t (one thread's B fragment of sub-block j) sit side by side.
 __global__ void __launch_bounds__(256) k_quant_gemm_acts(const float* __restrict__ X, uint8_t* __restrict__ scratch,
                                                          int tokens, int tok_pad, int K)
 {
@@ -61,7 +66,7 @@ __global__ void __launch_bounds__(256) k_quant_gemm_acts(const float* __restrict
         if (t >= tokens) {
             rec[lane] = 0;
             rec[32 + lane] = 0;
-            if (lane < 4) rec[64 + lane] = 0;
+            if (lane < 8) rec[64 + lane] = 0;
             continue;
         }
         const float4* xb = reinterpret_cast<const float4*>(X + (size_t)t * K + (size_t)b * 256);
@@ -72,16 +77,52 @@ __global__ void __launch_bounds__(256) k_quant_gemm_acts(const float* __restrict
         const float d = __fdiv_rn(amax, 127.0f);
         const float mul = (amax != 0.0f) ? __fdiv_rn(127.0f, amax) : 0.0f;
         auto q = [mul](float x) -> uint32_t { return (uint32_t)__float2int_rn(__fmul_rn(x, mul)) & 0xFFu; };
-        rec[lane] = q(v0.x) | (q(v0.y) << 8) | (q(v0.z) << 16) | (q(v0.w) << 24);
-        rec[32 + lane] = q(v1.x) | (q(v1.y) << 8) | (q(v1.z) << 16) | (q(v1.w) << 24);
+        const uint32_t p0 = q(v0.x) | (q(v0.y) << 8) | (q(v0.z) << 16) | (q(v0.w) << 24);   // word lane
+        const uint32_t p1 = q(v1.x) | (q(v1.y) << 8) | (q(v1.z) << 16) | (q(v1.w) << 24);   // word 32 + lane
+        const int pos = 8 * (lane >> 3) + 2 * (lane & 3) + ((lane & 7) >> 2);
+        rec[pos] = p0;
+        rec[32 + pos] = p1;
+        // sub-block sums: sub-block j = words 8j..8j+7 = 8 consecutive lanes
+        int s0 = dp4a_ss(p0, 0x01010101u, 0), s1 = dp4a_ss(p1, 0x01010101u, 0);
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, o);
+            s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, o);
+        }
+        short* bs = reinterpret_cast<short*>(rec + 68);           // bytes 272..287
+        if ((lane & 7) == 0) {
+            bs[lane >> 3] = (short)s0;                            // sub-blocks 0..3
+            bs[4 + (lane >> 3)] = (short)s1;                      // sub-blocks 4..7
+        }
         if (lane == 0) rec[64] = __float_as_uint(d);
         if (lane > 0 && lane < 4) rec[64 + lane] = 0;
     }
 }
 
+__device__ __forceinline__ int dp2a_lo(uint32_t a16x2, uint32_t b8x4, int c)
+{
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a16x2), "r"(b8x4), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi(uint32_t a16x2, uint32_t b8x4, int c)
+{
+    int d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a16x2), "r"(b8x4), "r"(c));
+    return d;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_addr(dst_smem)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+        : "memory");
+}
+
 template <int NT>
-__global__ void __launch_bounds__(288, 1)
-k_gemm_q4k_q8k_mma(const uint8_t* __restrict__ W, const uint8_t* __restrict__ acts, float* __restrict__ out,
+__global__ void __launch_bounds__(544, 1)
+k_gemm_q4k_q8k_mma(const __grid_constant__ CUtensorMap wmap, const uint8_t* __restrict__ acts, float* __restrict__ out,
                    const GemmPlan p, int* __restrict__ err)
 {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -92,13 +133,14 @@ k_gemm_q4k_q8k_mma(const uint8_t* __restrict__ W, const uint8_t* __restrict__ ac
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const bool is_producer = warp == p.warps;
-    const int rows_per_cta = 16 * p.warps;
-    const int row_bytes = p.nb * BPDQ_Q4K_BYTES;
+    const int rows_per_cta = 16 * (p.warps / p.ts);
+    const int rg = warp / p.ts;                 // row group of this warp
+    const int tok0 = (warp % p.ts) * 8 * NT;    // first token of this warp
     const int n_stage_steps = (p.nb + kSbPerStage - 1) / kSbPerStage;   // stages per row tile
 
     if (tid == 0) {
         for (int s = 0; s < p.stages; s++) {
-            mbar_init(&full[s], 32);          // every producer lane arrives (with its own byte count)
+            mbar_init(&full[s], 1);
             mbar_init(&empty[s], p.warps);
         }
         mbar_init_fence();
@@ -108,30 +150,23 @@ k_gemm_q4k_q8k_mma(const uint8_t* __restrict__ W, const uint8_t* __restrict__ ac
     pdl_wait();   // activations in scratch come from the quantizer launched just before
 
     if (is_producer) {
-        int it = 0;
-        for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
-            const int row0 = tile * rows_per_cta;
-            const int rows = min(rows_per_cta, p.N - row0);
-            for (int st = 0; st < n_stage_steps; st++, it++) {
-                const int s = it % p.stages;
-                if (it >= p.stages) {
-                    if (!mbar_wait_bounded(&empty[s], ((it / p.stages) - 1) & 1, err, 1)) return;
+        if (lane == 0) {
+            int it = 0;
+            for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
+                const int row0 = tile * rows_per_cta;
+                for (int st = 0; st < n_stage_steps; st++, it++) {
+                    const int s = it % p.stages;
+                    if (it >= p.stages && !mbar_wait_bounded(&empty[s], ((it / p.stages) - 1) & 1, err, 1)) return;
+                    const int sb0 = st * kSbPerStage;
+                    const int nsb = min(kSbPerStage, p.nb - sb0);
+                    uint8_t* slot = ring + (size_t)s * p.stage_bytes;
+                    const uint32_t act_bytes = (uint32_t)nsb * p.tok_pad * kActPitch;
+                    // the box is always whole: columns past the row end and rows past N arrive as zeros
+                    mbar_expect_tx(&full[s], act_bytes + (uint32_t)p.box_rows * p.row_pitch);
+                    bulk_g2s(slot, acts + (size_t)sb0 * p.tok_pad * kActPitch, act_bytes, &full[s]);
+                    // x coordinate in 4-byte elements: 36 words per super-block (a multiple of 16 bytes)
+                    tma_load_2d(slot + p.act_bytes, &wmap, sb0 * (BPDQ_Q4K_BYTES / 4), row0, &full[s]);
                 }
-                const int sb0 = st * kSbPerStage;
-                const int nsb = min(kSbPerStage, p.nb - sb0);
-                uint8_t* slot = ring + (size_t)s * p.stage_bytes;
-                uint32_t my_bytes = 0;
-                // lane 0 also brings this stage's activations: [nsb][tok_pad][272] is contiguous
-                if (lane == 0) my_bytes += (uint32_t)nsb * p.tok_pad * kActPitch;
-                for (int r = lane; r < rows; r += 32) my_bytes += (uint32_t)nsb * BPDQ_Q4K_BYTES;
-                mbar_expect_tx(&full[s], my_bytes);
-                if (lane == 0)
-                    bulk_g2s(slot, acts + (size_t)sb0 * p.tok_pad * kActPitch, (uint32_t)nsb * p.tok_pad * kActPitch,
-                             &full[s]);
-                for (int r = lane; r < rows; r += 32)
-                    bulk_g2s(slot + p.act_bytes + (size_t)r * kRowPitch,
-                             W + (size_t)(row0 + r) * row_bytes + (size_t)sb0 * BPDQ_Q4K_BYTES,
-                             (uint32_t)nsb * BPDQ_Q4K_BYTES, &full[s]);
             }
         }
         return;
@@ -139,7 +174,7 @@ k_gemm_q4k_q8k_mma(const uint8_t* __restrict__ W, const uint8_t* __restrict__ ac
 
     int it = 0;
     for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
-        const int row0 = tile * rows_per_cta + 16 * warp;
+        const int row0 = tile * rows_per_cta + 16 * rg;
         float facc[NT][4];
 #pragma unroll
         for (int n = 0; n < NT; n++)
@@ -150,42 +185,42 @@ k_gemm_q4k_q8k_mma(const uint8_t* __restrict__ W, const uint8_t* __restrict__ ac
             const int s = it % p.stages;
             if (!mbar_wait_bounded(&full[s], (it / p.stages) & 1, err, 2)) return;
             const uint8_t* slot = ring + (size_t)s * p.stage_bytes;
-            const int sb0 = st * kSbPerStage;
-            const int nsb = min(kSbPerStage, p.nb - sb0);
+            const int nsb = min(kSbPerStage, p.nb - st * kSbPerStage);
             if (row0 < p.N) {   // warps past the end of the matrix only keep the ring moving
                 for (int sb = 0; sb < nsb; sb++) {
                     const uint8_t* xa = slot + (size_t)sb * p.tok_pad * kActPitch;
-                    const uint8_t* w0 = slot + p.act_bytes + (size_t)(16 * warp + g) * kRowPitch + sb * BPDQ_Q4K_BYTES;
-                    const uint8_t* w1 = w0 + 8 * kRowPitch;
+                    const uint8_t* w0 = slot + p.act_bytes + (size_t)(16 * rg + g) * p.row_pitch + sb * BPDQ_Q4K_BYTES;
+                    const uint8_t* w1 = w0 + 8 * p.row_pitch;
                     const uint4 h0 = *reinterpret_cast<const uint4*>(w0);
                     const uint4 h1 = *reinterpret_cast<const uint4*>(w1);
-                    int lo[NT][4], hi[NT][4], mm[NT][4];
+                    uint32_t sca[2], mna[2], scb[2], mnb[2];   // packed scales/mins of rows g and g+8, halves 0/1
+                    q4k_scales4(h0.y, h0.z, h0.w, 0, sca[0], mna[0]);
+                    q4k_scales4(h0.y, h0.z, h0.w, 1, sca[1], mna[1]);
+                    q4k_scales4(h1.y, h1.z, h1.w, 0, scb[0], mnb[0]);
+                    q4k_scales4(h1.y, h1.z, h1.w, 1, scb[1], mnb[1]);
+                    int isum[NT][4];
 #pragma unroll
                     for (int n = 0; n < NT; n++)
 #pragma unroll
-                        for (int i = 0; i < 4; i++) lo[n][i] = hi[n][i] = mm[n][i] = 0;
+                        for (int i = 0; i < 4; i++) isum[n][i] = 0;
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
-                        uint32_t sc4a, mn4a, sc4b, mn4b;
-                        q4k_scales4(h0.y, h0.z, h0.w, j >> 2, sc4a, mn4a);
-                        q4k_scales4(h1.y, h1.z, h1.w, j >> 2, sc4b, mn4b);
-                        const uint32_t sca = byte_of(sc4a, j & 3), scb = byte_of(sc4b, j & 3);
-                        const uint32_t mna = byte_of(mn4a, j & 3) * 0x01010101u, mnb = byte_of(mn4b, j & 3) * 0x01010101u;
+                        const int sa = (int)byte_of(sca[j >> 2], j & 3), sb_ = (int)byte_of(scb[j >> 2], j & 3);
                         const uint32_t wa = *reinterpret_cast<const uint32_t*>(w0 + 16 + 16 * j + 4 * t);
                         const uint32_t wb = *reinterpret_cast<const uint32_t*>(w1 + 16 + 16 * j + 4 * t);
-                        const uint32_t qa_lo = wa & 0x0F0F0F0Fu, qa_hi = (wa >> 4) & 0x0F0F0F0Fu;
-                        const uint32_t qb_lo = wb & 0x0F0F0F0Fu, qb_hi = (wb >> 4) & 0x0F0F0F0Fu;
                         // fragment order: {row g k 0-15, row g+8 k 0-15, row g k 16-31, row g+8 k 16-31}
-                        const uint32_t a_lo[4] = {qa_lo * (sca & 7u), qb_lo * (scb & 7u), qa_hi * (sca & 7u), qb_hi * (scb & 7u)};
-                        const uint32_t a_hi[4] = {qa_lo * (sca >> 3), qb_lo * (scb >> 3), qa_hi * (sca >> 3), qb_hi * (scb >> 3)};
-                        const uint32_t a_mn[4] = {mna, mnb, mna, mnb};
+                        const uint32_t af[4] = {wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, (wa >> 4) & 0x0F0F0F0Fu,
+                                                (wb >> 4) & 0x0F0F0F0Fu};
 #pragma unroll
                         for (int n = 0; n < NT; n++) {
-                            const uint32_t* xr = reinterpret_cast<const uint32_t*>(xa + (size_t)(8 * n + g) * kActPitch);
-                            const uint32_t b0 = xr[8 * j + t], b1 = xr[8 * j + 4 + t];
-                            mma_s8(lo[n], a_lo, b0, b1);
-                            mma_s8(hi[n], a_hi, b0, b1);
-                            mma_s8(mm[n], a_mn, b0, b1);
+                            const uint2 bf =
+                                *reinterpret_cast<const uint2*>(xa + (size_t)(tok0 + 8 * n + g) * kActPitch + 32 * j + 8 * t);
+                            int c[4];
+                            mma_s8(c, af, bf.x, bf.y);
+                            isum[n][0] += sa * c[0];
+                            isum[n][1] += sa * c[1];
+                            isum[n][2] += sb_ * c[2];
+                            isum[n][3] += sb_ * c[3];
                         }
                     }
                     const float d0 = f16_bits_to_f32(h0.x & 0xFFFFu), m0 = f16_bits_to_f32(h0.x >> 16);
@@ -193,12 +228,22 @@ k_gemm_q4k_q8k_mma(const uint8_t* __restrict__ W, const uint8_t* __restrict__ ac
 #pragma unroll
                     for (int n = 0; n < NT; n++) {
                         // accumulator i: row g (i<2) or g+8, token 8n + 2t + (i&1)
-                        const float dA0 = *reinterpret_cast<const float*>(xa + (size_t)(8 * n + 2 * t) * kActPitch + 256);
-                        const float dA1 = *reinterpret_cast<const float*>(xa + (size_t)(8 * n + 2 * t + 1) * kActPitch + 256);
-                        const float v0 = d0 * (float)(8 * hi[n][0] + lo[n][0]) - m0 * (float)mm[n][0];
-                        const float v1 = d0 * (float)(8 * hi[n][1] + lo[n][1]) - m0 * (float)mm[n][1];
-                        const float v2 = d1 * (float)(8 * hi[n][2] + lo[n][2]) - m1 * (float)mm[n][2];
-                        const float v3 = d1 * (float)(8 * hi[n][3] + lo[n][3]) - m1 * (float)mm[n][3];
+                        const uint8_t* r0 = xa + (size_t)(tok0 + 8 * n + 2 * t) * kActPitch;
+                        const uint8_t* r1 = r0 + kActPitch;
+                        const float dA0 = *reinterpret_cast<const float*>(r0 + 256);
+                        const float dA1 = *reinterpret_cast<const float*>(r1 + 256);
+                        const uint4 bs0 = *reinterpret_cast<const uint4*>(r0 + 272);   // eight int16 sub-block sums
+                        const uint4 bs1 = *reinterpret_cast<const uint4*>(r1 + 272);
+                        auto msum = [](const uint4& bs, uint32_t mlo, uint32_t mhi) {
+                            int v = dp2a_lo(bs.x, mlo, 0);
+                            v = dp2a_hi(bs.y, mlo, v);
+                            v = dp2a_lo(bs.z, mhi, v);
+                            return dp2a_hi(bs.w, mhi, v);
+                        };
+                        const float v0 = d0 * (float)isum[n][0] - m0 * (float)msum(bs0, mna[0], mna[1]);
+                        const float v1 = d0 * (float)isum[n][1] - m0 * (float)msum(bs1, mna[0], mna[1]);
+                        const float v2 = d1 * (float)isum[n][2] - m1 * (float)msum(bs0, mnb[0], mnb[1]);
+                        const float v3 = d1 * (float)isum[n][3] - m1 * (float)msum(bs1, mnb[0], mnb[1]);
                         facc[n][0] = fmaf(dA0, v0, facc[n][0]);
                         facc[n][1] = fmaf(dA1, v1, facc[n][1]);
                         facc[n][2] = fmaf(dA0, v2, facc[n][2]);
@@ -214,10 +259,31 @@ k_gemm_q4k_q8k_mma(const uint8_t* __restrict__ W, const uint8_t* __restrict__ ac
         for (int n = 0; n < NT; n++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const int row = row0 + g + (i >> 1) * 8, tok = 8 * n + 2 * t + (i & 1);
+                const int row = row0 + g + (i >> 1) * 8, tok = tok0 + 8 * n + 2 * t + (i & 1);
                 if (row < p.N && tok < p.tokens) out[(size_t)tok * p.N + row] = facc[n][i];
             }
     }
+}
+
+// The weight matrix as a 2-D tensor of 4-byte elements [N][K/256*36] for the tiled copy.
+static int make_weight_map(CUtensorMap* map, const uint8_t* W, int N, int nb, int box_rows, int row_pitch)
+{
+    static PFN_cuTensorMapEncodeTiled encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return latch(BPDQ_ERR_CUDA);
+        encode = (PFN_cuTensorMapEncodeTiled)fn;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)nb * (BPDQ_Q4K_BYTES / 4), (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)nb * BPDQ_Q4K_BYTES};
+    const cuuint32_t box[2] = {(cuuint32_t)(row_pitch / 4), (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(W), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : latch(BPDQ_ERR_CUDA - 900 - (int)r);
 }
 
 // Scratch for the quantized activations of the GEMM path: grown on demand, kept per device.
@@ -246,6 +312,9 @@ static uint8_t* gemm_scratch(size_t bytes)
 template <int NT>
 static int launch_gemm(const uint8_t* W, const uint8_t* acts, float* out, const GemmPlan& p, cudaStream_t s)
 {
+    CUtensorMap wmap;
+    int mrc = make_weight_map(&wmap, W, p.N, p.nb, p.box_rows, p.row_pitch);
+    if (mrc) return mrc;
     auto kern = k_gemm_q4k_q8k_mma<NT>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -265,7 +334,7 @@ static int launch_gemm(const uint8_t* W, const uint8_t* acts, float* out, const 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = tuning().pdl ? 1 : 0;
-    return check_cuda(cudaLaunchKernelEx(&cfg, kern, W, acts, out, p, device_error_flag()));
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, wmap, acts, out, p, device_error_flag()));
 }
 
 // out[tokens][N] for up to 64 tokens per pass.  C-ABI nibble order only.
@@ -282,9 +351,11 @@ int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, i
         p.K = K;
         p.nb = K / 256;
         p.tokens = T;
-        const int nt = T <= 16 ? 2 : (T <= 32 ? 4 : 8);
-        p.tok_pad = 8 * nt;
-        // rows per CTA: 16 * warps, chosen so that the tiles fill the SMs in as few equal rounds as possible
+        // tokens are split over `ts` warps per row group, NT n-tiles of 8 tokens each
+        const int nt = T <= 8 ? 1 : (T <= 32 ? 2 : 4);
+        p.ts = T <= 16 ? 1 : 2;
+        p.tok_pad = 8 * nt * p.ts;
+        // rows per CTA: 16 * groups, chosen so that the tiles fill the SMs in as few equal rounds as possible
         int best_w = 8;
         long best_cost = -1;
         for (int w = 4; w <= 8; w++) {
@@ -293,11 +364,14 @@ int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, i
             const long cost = rounds * w;
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_w = w; }
         }
-        p.warps = best_w;
-        p.n_tiles = (N + 16 * p.warps - 1) / (16 * p.warps);
+        p.warps = best_w * p.ts;
+        p.n_tiles = (N + 16 * best_w - 1) / (16 * best_w);
         p.grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
         p.act_bytes = kSbPerStage * p.tok_pad * kActPitch;
-        p.stage_bytes = (p.act_bytes + 16 * p.warps * kRowPitch + 127) / 128 * 128;
+        p.act_bytes = (p.act_bytes + 127) / 128 * 128;   // the weight box must start on a 128-byte boundary
+        p.row_pitch = (p.nb < kSbPerStage ? p.nb : kSbPerStage) * BPDQ_Q4K_BYTES;
+        p.box_rows = 16 * best_w < N ? 16 * best_w : N;
+        p.stage_bytes = (p.act_bytes + 16 * best_w * p.row_pitch + 127) / 128 * 128;
         p.stages = (227 * 1024 - 128) / p.stage_bytes;
         if (p.stages > 6) p.stages = 6;
         if (p.stages < 2) return latch(BPDQ_ERR_RANGE);
@@ -311,7 +385,7 @@ int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, i
         int rc = check_cuda(cudaGetLastError());
         if (rc) return rc;
         float* o = out + (size_t)t0 * N;
-        rc = nt == 2 ? launch_gemm<2>(W, acts, o, p, s) : (nt == 4 ? launch_gemm<4>(W, acts, o, p, s) : launch_gemm<8>(W, acts, o, p, s));
+        rc = nt == 1 ? launch_gemm<1>(W, acts, o, p, s) : (nt == 2 ? launch_gemm<2>(W, acts, o, p, s) : launch_gemm<4>(W, acts, o, p, s));
         if (rc) return latch(rc);
     }
     return 0;

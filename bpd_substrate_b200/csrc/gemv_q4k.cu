@@ -553,7 +553,7 @@ static int make_plan(const int* Ms, int n_problems, int K, int T, GemvPlan& p)
     p.row_bytes = p.nb * BPDQ_Q4K_BYTES;
     p.kc = (p.nb + 15) / 16;
     if (p.kc > 31) return BPDQ_ERR_RANGE;  // K > 126976: one warp per 4096 K, 31 consumer warps at most
-    p.ng = tu.warps / p.kc;
+    p.ng = (T > 2 && tu.warps > 8 ? 8 : tu.warps) / p.kc;   // 3-4 tokens need the registers of a small CTA
     if (p.ng < 1) p.ng = 1;
     if (p.ng > 12 && p.kc > 1) p.ng = 12;  // named barriers 3 .. 3+ng-1 (used only when kc > 1)
     if (p.ng > 31) p.ng = 31;
@@ -683,7 +683,7 @@ int gemm_q4k_q8k_multi(int n, const uint8_t* const* Ws, float* const* outs, cons
     int per_pass = kMaxTokens;
     {
         GemvPlan probe;
-        int rc = make_plan(Ms, n, K, 1, probe);
+        int rc = make_plan(Ms, n, K, tokens < kMaxTokens ? tokens : kMaxTokens, probe);
         if (rc) return latch(rc);
         const int threads = (probe.nw + 1) * 32;
         if (threads > kMidCtaThreads) per_pass = 1;
@@ -722,7 +722,7 @@ int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M,
     if (M < 0) return latch(BPDQ_ERR_ARG);
     // many tokens: the weights would be streamed once per four tokens here; the tensor-core
     // kernel reads them once per 64
-    if (tokens > 8 && layout == BPDQ_LAYOUT_BPD && xsrc == 0 && !dbg)
+    if (tokens > 4 && layout == BPDQ_LAYOUT_BPD && xsrc == 0 && !dbg)
         return gemm_q4k_q8k_mma(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s);
     return gemm_q4k_q8k_multi(1, &W, &out, &M, x, tokens, K, layout, xsrc, dbg, s);
 }
