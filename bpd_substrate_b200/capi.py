@@ -26,6 +26,7 @@ SIGNATURES = {
     "bpdq_clear_status": (None, []),
     "bpdq_set_tuning": (None, [i32, i32, i32, i32, i32]),
     "bpdq_sm_count": (i32, []),
+    "bpdq_set_dequant_tuning": (None, [i32, i32]),
     "bpdq_debug_trace": (None, [vp, sz, i32]),
     # memory (size_t)
     "bpdq_alloc": (vp, [sz]),

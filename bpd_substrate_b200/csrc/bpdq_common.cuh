@@ -42,6 +42,8 @@ struct Tuning {
     int ctas_per_sm;    // persistent CTAs per SM (upper bound)
     int warps;          // consumer warps per CTA (target)
     int pdl;            // launch GEMVs with programmatic dependent launch
+    int dequant_variant;   // 0: four outputs per thread, 1: eight outputs per thread
+    int dequant_ctas;      // CTAs per SM of the dequant grid
 };
 Tuning& tuning();
 

@@ -12,7 +12,7 @@ namespace bpdq {
 
 static std::atomic<cudaStream_t> g_stream{nullptr};
 static std::atomic<int> g_status{0};
-static Tuning g_tuning = {8192, 2, 1, 16, 1};
+static Tuning g_tuning = {8192, 2, 1, 16, 1, 1, 32};
 
 __device__ int g_dev_error = 0;
 
@@ -119,6 +119,11 @@ void bpdq_set_tuning(int tile_bytes, int stages, int ctas_per_sm, int warps, int
     if (ctas_per_sm > 0) t.ctas_per_sm = ctas_per_sm;
     if (warps > 0) t.warps = warps;
     if (pdl >= 0) t.pdl = pdl;
+}
+void bpdq_set_dequant_tuning(int variant, int ctas_per_sm)
+{
+    if (variant == 0 || variant == 1) tuning().dequant_variant = variant;
+    if (ctas_per_sm > 0) tuning().dequant_ctas = ctas_per_sm;
 }
 int bpdq_sm_count(void) { return sm_count(); }
 

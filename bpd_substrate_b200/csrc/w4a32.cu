@@ -70,6 +70,78 @@ __global__ void __launch_bounds__(256) k_w4a32(const uint8_t* __restrict__ W, co
     }
 }
 
+// GEMV fast path (contiguous x): a warp owns R consecutive rows; lane l takes half-super-blocks
+// l, l+32, ...  The activations of a sub-block are loaded once and used by all R rows; a nibble
+// becomes a float with one byte-permute (0x4B0000qq = 2^23 + q) and one subtraction.  Per
+// sub-block the lane forms S1 = sum q*x and S0 = sum x, then acc += (d*sc)*S1 - (dmin*mn)*S0,
+// half-blocks ascending; lanes are added by a butterfly (xor 16 .. 1).
+template <int R>
+__global__ void __launch_bounds__(256) k_w4a32_gemv(const uint8_t* __restrict__ W, const float* __restrict__ x,
+                                                    float* __restrict__ out, int M, int nb)
+{
+    const int lane = threadIdx.x & 31;
+    const int row0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * R;
+    if (row0 >= M) return;
+    const size_t row_bytes = (size_t)nb * BPDQ_Q4K_BYTES;
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r] = 0.0f;
+    for (int hb = lane; hb < 2 * nb; hb += 32) {
+        const int half = hb & 1;
+        const uint8_t* blk0 = W + (size_t)row0 * row_bytes + (size_t)(hb >> 1) * BPDQ_Q4K_BYTES;
+        uint4 hdr[R];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+            hdr[r] = (row0 + r < M) ? __ldg(reinterpret_cast<const uint4*>(blk0 + r * row_bytes)) : make_uint4(0, 0, 0, 0);
+        const float4* xs = reinterpret_cast<const float4*>(x + (size_t)hb * 128);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float xv[32];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float4 v = __ldg(xs + 8 * j + i);
+                xv[4 * i + 0] = v.x;
+                xv[4 * i + 1] = v.y;
+                xv[4 * i + 2] = v.z;
+                xv[4 * i + 3] = v.w;
+            }
+            float s0 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 32; i++) s0 += xv[i];
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                if (row0 + r >= M) continue;
+                const uint4 qv = __ldg(reinterpret_cast<const uint4*>(blk0 + r * row_bytes + 16 + 64 * half) + j);
+                const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+                float s1 = 0.0f;
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const uint32_t lo = qw[w] & 0x0F0F0F0Fu, hi = (qw[w] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                    for (int b = 0; b < 4; b++) {
+                        // bytes {q, 0, 0, 0x4B}: selector picks byte b of the nibble word, then 0x4B000000's bytes
+                        const uint32_t sel = 0x7440u | (uint32_t)b;
+                        const float fl = __uint_as_float(__byte_perm(lo, 0x4B000000u, sel)) - 8388608.0f;
+                        const float fh = __uint_as_float(__byte_perm(hi, 0x4B000000u, sel)) - 8388608.0f;
+                        s1 = fmaf(fl, xv[4 * w + b], s1);
+                        s1 = fmaf(fh, xv[16 + 4 * w + b], s1);
+                    }
+                }
+                uint32_t sc4, mn4;
+                q4k_scales4(hdr[r].y, hdr[r].z, hdr[r].w, half, sc4, mn4);
+                const float d = f16_bits_to_f32(hdr[r].x & 0xFFFFu), dmin = f16_bits_to_f32(hdr[r].x >> 16);
+                acc[r] = fmaf(d * (float)byte_of(sc4, j), s1, acc[r]);
+                acc[r] = fmaf(-(dmin * (float)byte_of(mn4, j)), s0, acc[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && row0 + r < M) out[row0 + r] = v;
+    }
+}
+
 // Generic driver: n_cols activation vectors; element (k, c) at xs[k*ldx + c*cstride]; result
 // (row, c) at out[row*ldo + c*ostride].
 static int w4a32(const uint8_t* W, const float* xs, long ldx, long cstride, float* out, long ldo, long ostride, int M,
@@ -79,6 +151,12 @@ static int w4a32(const uint8_t* W, const float* xs, long ldx, long cstride, floa
     if (M == 0 || n_cols == 0) return 0;
     if (!W || !xs || !out) return latch(BPDQ_ERR_ARG);
     if (((uintptr_t)W & 15) || ((uintptr_t)xs & 3) || ((uintptr_t)out & 3)) return latch(BPDQ_ERR_ALIGN);
+    if (n_cols == 1 && ldx == 1 && !((uintptr_t)xs & 15)) {
+        constexpr int R = 4;
+        const int warps = (M + R - 1) / R;
+        k_w4a32_gemv<R><<<(warps + 7) / 8, 256, 0, s>>>(W, xs, out, M, K / 256);
+        return check_cuda(cudaGetLastError());
+    }
     const int grid = (M + 7) / 8;
     for (int c0 = 0; c0 < n_cols; c0 += 4) {
         const int nc = n_cols - c0 < 4 ? n_cols - c0 : 4;

@@ -44,6 +44,8 @@ void bpdq_clear_status(void);
 /* GEMV launch tuning: max bytes per weight tile, ring slots per warp group, CTAs per SM,
  * consumer warps per CTA, programmatic dependent launch on/off.  <=0 (pdl: <0) keeps a field. */
 void bpdq_set_tuning(int tile_bytes, int slots, int ctas_per_sm, int warps, int pdl);
+/* dequant launch tuning: variant 0 = four outputs per thread, 1 = eight; CTAs per SM of the grid */
+void bpdq_set_dequant_tuning(int variant, int ctas_per_sm);
 int bpdq_sm_count(void);
 /* tuning aid: the next `launches` GEMV launches write 8 global-timer stamps (ns) per CTA */
 void bpdq_debug_trace(void* dev_buf, size_t stride_u64, int launches);
