@@ -200,12 +200,18 @@ def run_gpu(args):
 
     # Every rank holds a full-size layer set: its row shard of a `world`-times larger model.
     out_local = None
+    if args.workload == "llama70b":
+        # one model for all ranks: rank r owns rows [r*N/world, (r+1)*N/world) of every matrix; the
+        # output head rides along as an eighth matrix of every 80th layer's worth of work
+        shapes, shard = synth.LLAMA70B_LAYER, (rank, world)
+    else:
+        shapes, shard = synth.MISTRAL_LAYER, (0, 1)
     if world > 1:
         # NCCL reads this rank's output arena directly: let torch own that allocation
-        o_floats = args.layers * sum(rows for _, rows, _ in synth.MISTRAL_LAYER)
+        o_floats = args.tokens * args.layers * sum(rows // shard[1] for _, rows, _ in shapes)
         out_local = torch.empty(o_floats, dtype=torch.float32, device="cuda")
-    ls = LayerSet(synth.MISTRAL_LAYER, args.layers, seed=2000 + rank,
-                  d_out=out_local.data_ptr() if out_local is not None else None)
+    ls = LayerSet(shapes, args.layers, seed=2000 + (rank if args.workload == "mistral7b" else 0), row_shard=shard,
+                  d_out=out_local.data_ptr() if out_local is not None else None, tokens=args.tokens)
     step_bytes = ls.algorithmic_bytes()
     schedule = args.schedule
     launches = ls.launches_per_step(schedule)
@@ -300,9 +306,12 @@ def run_gpu(args):
                              f"split over {threads} host threads, {dt:.2f} s wall"}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak" if args.workload == "mistral7b" else "strong",
             "vs_baseline": None, "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers": args.layers, "gemvs_per_step": 7 * args.layers,
+            "config": {"workload": WORKLOAD if args.workload == "mistral7b" else
+                       f"llama70b_layer_set_x{args.layers}_q4k_decode_batch{args.tokens}_rowshard{world}",
+                       "layers": args.layers, "gemvs_per_step": 7 * args.layers, "tokens": args.tokens,
                        "schedule": schedule, "launches_per_step": launches,
                        "weights_bytes_per_gpu": ls.weight_bytes,
                        "l2": "inputs larger than L2: 3.9 GB of weights stream through once per step",
@@ -343,9 +352,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--schedule", default="batched", choices=["batched", "grouped", "separate"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--layers", type=int, default=N_LAYERS,
+    ap.add_argument("--workload", default="mistral7b", choices=["mistral7b", "llama70b"],
+                    help="mistral7b: the benchmark (every rank a full layer set, weak scaling); llama70b: the "
+                         "70B-shaped model row-sharded over the ranks (80 layers + output head, strong scaling)")
+    ap.add_argument("--tokens", type=int, default=1, help="activation rows per product (llama70b sweep: 1 and 8)")
+    ap.add_argument("--layers", type=int, default=None,
                     help="layers resident (32 is the benchmark; fewer only for profiler captures)")
     args = ap.parse_args()
+    if args.layers is None:
+        args.layers = N_LAYERS if args.workload == "mistral7b" else 80
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -1235,6 +1235,8 @@ int gemv_q4k_q8k_batch(const BatchDesc* d, int n, int layout, uint8_t* ws, size_
         while (i + len < n && len < kMaxBatch && d[i + len].M > 0) {
             run[len] = d[i + len];
             if (make_batch_plan(run, len + 1, plan) != 0) break;
+            // do not let a long run squeeze the consumer warps out of shared memory: split instead
+            if (len > 0 && plan.nw < (tuning().warps < 8 ? tuning().warps : 8)) break;
             good = plan;
             len++;
         }

@@ -38,10 +38,11 @@ class LayerSet:
     """
 
     def __init__(self, shapes=synth.MISTRAL_LAYER, n_layers=32, seed=2000, row_shard=(0, 1), lib=None,
-                 d_out=None):
+                 d_out=None, tokens=1):
         self.lib = lib or capi.load()
         self.shapes = tuple(shapes)
         self.n_layers = n_layers
+        self.tokens = tokens       # activation rows per product (1 = decode; more: schedule "separate" only)
         rank, world = row_shard
         self.rank, self.world = rank, world
         lib = self.lib
@@ -57,8 +58,8 @@ class LayerSet:
             for _, rows, cols in self.local:
                 self.x_off.append(xo)
                 self.o_off.append(oo)
-                xo += cols * 4
-                oo += rows * 4
+                xo += tokens * cols * 4
+                oo += tokens * rows * 4
         self.x_bytes, self.o_bytes = xo, oo
         self.d_x = lib.bpdq_alloc(xo)
         self._own_out = d_out is None      # an output arena may be lent by the caller (e.g. for NCCL)
@@ -86,9 +87,11 @@ class LayerSet:
     # ---- sizes
     def algorithmic_bytes(self):
         """Quantized weights + fp32 activations in + fp32 outputs out, per step."""
-        return self.n_layers * sum(synth.gemv_bytes_q4k(rows, cols) for _, rows, cols in self.local)
+        return self.n_layers * sum(synth.gemv_bytes_q4k(rows, cols, self.tokens) for _, rows, cols in self.local)
 
     def launches_per_step(self, schedule):
+        if self.tokens > 1:
+            return 2 * self.n_layers * len(self.local)   # activation quantizer + GEMM kernel per matrix
         if schedule == "batched":
             return 2 * self.n_layers      # activation quantizer + GEMV kernel per layer
         return self.n_layers * len(GROUPS_DECODE if schedule == "grouped" else GROUPS_NONE)
@@ -109,6 +112,16 @@ class LayerSet:
     def enqueue_step(self, schedule="grouped", stream=None):
         """Queues one decode step's GEMVs on ``stream`` (default: this object's stream)."""
         lib, s = self.lib, (stream if stream is not None else self.stream)
+        if self.tokens > 1:
+            # several tokens per product: one launch per matrix (tensor-core kernel above 4 tokens)
+            nm = len(self.local)
+            for layer in range(self.n_layers):
+                for m, (_, rows, cols) in enumerate(self.local):
+                    i = layer * nm + m
+                    capi.check(lib.bpd_qmm_q4k_q8k_cuda(self.weights[layer][m], self.d_x + self.x_off[i],
+                                                        self.d_out + self.o_off[i], self.tokens, rows, cols, 0, 0,
+                                                        None, s), "GEMM launch")
+            return
         if schedule == "batched":
             nm = len(self.local)
             for layer in range(self.n_layers):
