@@ -191,6 +191,8 @@ def run_gpu(args):
     lib = capi.load()
     dist = torch = None
     if world > 1:
+        # keep stdout to the one JSON line (NCCL announces its version there at the default level)
+        os.environ.setdefault("NCCL_DEBUG", "WARN")
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)

@@ -356,12 +356,13 @@ int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, i
         p.ts = T <= 16 ? 1 : 2;
         p.tok_pad = 8 * nt * p.ts;
         // rows per CTA: 16 * groups, chosen so that the tiles fill the SMs in as few equal rounds as possible
+        // (warps of a CTA run side by side, so a tile's time grows slowly with its height: model it as 4 + w)
         int best_w = 8;
         long best_cost = -1;
-        for (int w = 4; w <= 8; w++) {
+        for (int w = 8; w >= 1; w--) {
             const long tiles = (N + 16 * w - 1) / (16 * w);
             const long rounds = (tiles + sm_count() - 1) / sm_count();
-            const long cost = rounds * w;
+            const long cost = rounds * (4 + w);
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_w = w; }
         }
         p.warps = best_w * p.ts;
