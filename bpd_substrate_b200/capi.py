@@ -83,6 +83,7 @@ SIGNATURES = {
     "bpdq_batch_static_capacity": (sz, []),
     "bpd_qmm_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
     "bpd_qmm_q4k_q8k_mma_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "bpd_qmm_q4k_q8k_tc5_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),
     # fp32 decode operators
     "gpu_vecmat": (None, [vp, vp, vp, i32, i32]),

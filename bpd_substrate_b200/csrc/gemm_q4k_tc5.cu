@@ -1,0 +1,462 @@
+// Many-token Q4_K x Q8_K product on the fifth-generation tensor cores (tcgen05, accumulators in
+// tensor memory).  Same arithmetic as gemm_q4k_mma.cu and gemv_q4k.cu, every integer exact:
+//
+//   out[t][n] = sum_b dA_tb * ( d_nb * isum - dmin_nb * msum )
+//   isum = sum_j sc_j * dot_j = 8 * sum_k (q_k * sh_j(k)) * x_k + sum_k (q_k * sl_j(k)) * x_k,   sc = 8*sh + sl
+//   msum = sum_j mn_j * bsum_j = 64 * sum_j mn_j * bh_j + sum_j mn_j * bl_j,                     bsum = 64*bh + bl
+//
+// q*sl and q*sh are below 128, mn, bl, bh fit a signed byte, so all four sums are kind::i8 MMAs
+// (int8 x int8 -> int32 in TMEM) that accumulate over a whole super-block: D_lo, D_hi over its
+// eight K=32 steps, D_ml, D_mh in one step each.  The fp32 scales are applied once per
+// super-block by the epilogue warps after tcgen05.ld.
+//
+// One CTA = 128 weight rows (the MMA M) x all tokens (the MMA N, 16..64), ten warps:
+//   warps 0-3  transform: thread r turns row r's packed nibbles into the two int8 A planes in
+//              the canonical K-major core-matrix layout (8 rows x 16 bytes per 128-byte core
+//              matrix; chunk stride 2048 B, row-group stride 128 B), half a super-block at a time
+//   warps 4-7  epilogue: thread r owns TMEM lane r: tcgen05.ld 16 columns of the four
+//              accumulators at a time, scale, accumulate 64 fp32 outputs in registers
+//   warp 8     producer: per super-block one tiled TMA request for the 128 x 144-byte block of
+//              raw rows and one bulk copy of the activations' block (already in canonical B
+//              layout, written by k_quant_tc5_acts), ring of two stages
+//   warp 9     allocates tensor memory; one lane issues the MMAs and commits to mbarriers
+// Rings: raw (2 stages) -> operands (3 half-super-block stages) -> TMEM (2 accumulator sets).
+// All mbarrier waits are bounded; on a timeout the role records an error code and leaves, the
+// others time out in turn, and warp 9 frees the tensor memory before it returns.
+#include "bpdq_common.cuh"
+#include "../../include/bpdq.h"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace bpdq {
+
+constexpr int kRows = 128;
+constexpr int kRawStages = 2, kOpStages = 3, kSideSlots = 6;
+constexpr int kPlaneBytes = 16384;                 // one A plane of half a super-block: 8 chunks x 2048 B
+constexpr int kOpBytes = 2 * kPlaneBytes + 4096;   // lo, hi, and the 4 KB mins operand
+constexpr int kRowsBytes = kRows * BPDQ_Q4K_BYTES; // 18432
+
+struct Tc5Plan {
+    int N, nb, tokens, npad;      // weight rows, super-blocks per row, valid / padded tokens (16, 32 or 64)
+    int n_tiles, grid;
+    int act_bytes;                // scratch bytes per super-block: 324 * npad
+    int raw_bytes;                // ring slot: rows + activations
+    int off_raw, off_op, off_side, off_bar;
+    size_t smem;
+};
+
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo)
+{
+    // K-major, no swizzle: start address, leading (K-chunk) and stride (8-row group) byte offsets
+    // in 16-byte units, descriptor version 1
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(0)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tma_rows_2d(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_addr(dst_smem)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+        : "memory");
+}
+
+// Activation quantizer: warp per (super-block, token).  Scratch per super-block:
+//   [256*npad] int8 B operand, canonical: element (tok,k) at (k/16)*16*npad + (tok/8)*128 + (tok%8)*16 + k%16
+//   [32*npad]  bl plane, [32*npad] bh plane (K = 32 bytes per token, bytes 0..7 = sub-blocks 0..7, rest 0)
+//   [4*npad]   fp32 block scales
+__global__ void __launch_bounds__(256) k_quant_tc5_acts(const float* __restrict__ X, uint8_t* __restrict__ scratch,
+                                                        int tokens, int npad, int K)
+{
+    const int nb = K / 256;
+    const int lane = threadIdx.x & 31;
+    const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long n_warps = ((long)gridDim.x * blockDim.x) >> 5;
+    const int chunk_stride = 16 * npad;
+    for (long u = warp; u < (long)nb * npad; u += n_warps) {
+        const int b = (int)(u / npad), t = (int)(u - (long)b * npad);
+        uint8_t* base = scratch + (size_t)b * 324 * npad;
+        uint8_t* rowp = base + (t >> 3) * 128 + (t & 7) * 16;
+        uint32_t p0 = 0, p1 = 0;
+        float d = 0.0f;
+        if (t < tokens) {
+            const float4* xb = reinterpret_cast<const float4*>(X + (size_t)t * K + (size_t)b * 256);
+            const float4 v0 = __ldg(xb + lane), v1 = __ldg(xb + 32 + lane);
+            float amax = fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w)));
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+            amax = warp_max(amax);
+            d = __fdiv_rn(amax, 127.0f);
+            const float mul = (amax != 0.0f) ? __fdiv_rn(127.0f, amax) : 0.0f;
+            auto q = [mul](float x) -> uint32_t { return (uint32_t)__float2int_rn(__fmul_rn(x, mul)) & 0xFFu; };
+            p0 = q(v0.x) | (q(v0.y) << 8) | (q(v0.z) << 16) | (q(v0.w) << 24);
+            p1 = q(v1.x) | (q(v1.y) << 8) | (q(v1.z) << 16) | (q(v1.w) << 24);
+        }
+        // word `lane` = elements 4*lane.. -> K-chunk lane/4, byte 4*(lane%4); word 32+lane -> chunk 8 + lane/4
+        *reinterpret_cast<uint32_t*>(rowp + (lane >> 2) * chunk_stride + 4 * (lane & 3)) = p0;
+        *reinterpret_cast<uint32_t*>(rowp + (8 + (lane >> 2)) * chunk_stride + 4 * (lane & 3)) = p1;
+        int s0 = dp4a_ss(p0, 0x01010101u, 0), s1 = dp4a_ss(p1, 0x01010101u, 0);
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, o);
+            s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, o);
+        }
+        // gather the eight sub-block sums into every lane, then lane 0 writes the two planes
+        uint32_t bl_lo = 0, bl_hi = 0, bh_lo = 0, bh_hi = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int a = __shfl_sync(0xFFFFFFFFu, s0, 8 * j), c = __shfl_sync(0xFFFFFFFFu, s1, 8 * j);
+            bl_lo |= (uint32_t)(a & 63) << (8 * j);
+            bh_lo |= ((uint32_t)(a >> 6) & 0xFFu) << (8 * j);
+            bl_hi |= (uint32_t)(c & 63) << (8 * j);
+            bh_hi |= ((uint32_t)(c >> 6) & 0xFFu) << (8 * j);
+        }
+        uint8_t* blp = base + 256 * npad + (t >> 3) * 128 + (t & 7) * 16;
+        uint8_t* bhp = blp + 32 * npad;
+        if (lane == 0) {
+            *reinterpret_cast<uint4*>(blp) = make_uint4(bl_lo, bl_hi, 0, 0);
+            *reinterpret_cast<uint4*>(blp + chunk_stride) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(bhp) = make_uint4(bh_lo, bh_hi, 0, 0);
+            *reinterpret_cast<uint4*>(bhp + chunk_stride) = make_uint4(0, 0, 0, 0);
+            reinterpret_cast<float*>(base + 320 * npad)[t] = d;
+        }
+    }
+}
+
+template <int NPAD>
+__global__ void __launch_bounds__(320, 1)
+k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __restrict__ acts, float* __restrict__ out,
+                   const Tc5Plan p, int* __restrict__ err)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* raw = smem + p.off_raw;
+    uint8_t* ops = smem + p.off_op;
+    float* side = reinterpret_cast<float*>(smem + p.off_side);   // [kSideSlots][256 hdr floats + NPAD dA floats]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);
+    uint64_t* raw_full = bars;                   // [kRawStages]
+    uint64_t* raw_empty = raw_full + kRawStages; // transform warps (4) + MMA commit (1)
+    uint64_t* op_full = raw_empty + kRawStages;  // [kOpStages] transform warps (4)
+    uint64_t* op_empty = op_full + kOpStages;    // MMA commit (1)
+    uint64_t* acc_full = op_empty + kOpStages;   // [2] MMA commit (1)
+    uint64_t* acc_empty = acc_full + 2;          // epilogue warps (4)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    constexpr int kSideFloats = 256 + NPAD;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < kRawStages; s++) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 5); }
+        for (int s = 0; s < kOpStages; s++) { mbar_init(&op_full[s], 4); mbar_init(&op_empty[s], 1); }
+        for (int s = 0; s < 2; s++) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+        mbar_init_fence();
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();   // the activations in scratch come from the quantizer launched just before
+
+    const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total_sb = my_tiles * p.nb;       // super-blocks this CTA walks, over all its tiles
+
+    if (warp == 8) {
+        // ---------------- producer
+        if (lane == 0) {
+            for (int i = 0; i < total_sb; i++) {
+                const int s = i % kRawStages;
+                if (i >= kRawStages && !mbar_wait_bounded(&raw_empty[s], ((i / kRawStages) - 1) & 1, err, 11)) break;
+                const int tile = blockIdx.x + (i / p.nb) * gridDim.x, b = i % p.nb;
+                uint8_t* slot = raw + (size_t)s * p.raw_bytes;
+                mbar_expect_tx(&raw_full[s], (uint32_t)(kRowsBytes + p.act_bytes));
+                tma_rows_2d(slot, &wmap, b * (BPDQ_Q4K_BYTES / 4), tile * kRows, &raw_full[s]);
+                bulk_g2s(slot + kRowsBytes, acts + (size_t)b * p.act_bytes, (uint32_t)p.act_bytes, &raw_full[s]);
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+            for (int i = 0; i < total_sb; i++) {
+                const int s = i % kRawStages, a = i & 1;
+                if (!mbar_wait_bounded(&raw_full[s], (i / kRawStages) & 1, err, 12)) break;
+                if (i >= 2 && !mbar_wait_bounded(&acc_empty[a], ((i >> 1) - 1) & 1, err, 13)) break;
+                const uint32_t acts_s = smem_addr(raw + (size_t)s * p.raw_bytes + kRowsBytes);
+                const uint32_t d_lo = tmem_base + (uint32_t)(a * 4 + 0) * NPAD, d_hi = d_lo + NPAD;
+                const uint32_t d_ml = d_lo + 2 * NPAD, d_mh = d_lo + 3 * NPAD;
+                bool gave_up = false;
+                for (int half = 0; half < 2; half++) {
+                    const int h = 2 * i + half, o = h % kOpStages;
+                    if (!mbar_wait_bounded(&op_full[o], (h / kOpStages) & 1, err, 14)) { gave_up = true; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t op_s = smem_addr(ops + (size_t)o * kOpBytes);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int j = 4 * half + k;   // sub-block: K-chunks 2j, 2j+1 of the B operand
+                        const uint64_t bdesc = umma_desc(acts_s + (uint32_t)(2 * j) * 16 * NPAD, 16 * NPAD, 128);
+                        const uint32_t accum = (half | k) ? 1u : 0u;
+                        umma_i8(d_lo, umma_desc(op_s + (uint32_t)(2 * k) * 2048, 2048, 128), bdesc, idesc, accum);
+                        umma_i8(d_hi, umma_desc(op_s + kPlaneBytes + (uint32_t)(2 * k) * 2048, 2048, 128), bdesc, idesc, accum);
+                    }
+                    if (half == 1) {
+                        const uint64_t mdesc = umma_desc(op_s + 2 * kPlaneBytes, 2048, 128);
+                        umma_i8(d_ml, mdesc, umma_desc(acts_s + 256 * NPAD, 16 * NPAD, 128), idesc, 0u);
+                        umma_i8(d_mh, mdesc, umma_desc(acts_s + 288 * NPAD, 16 * NPAD, 128), idesc, 0u);
+                    }
+                    umma_commit(&op_empty[o]);
+                }
+                if (gave_up) break;
+                umma_commit(&raw_empty[s]);
+                umma_commit(&acc_full[a]);
+            }
+        }
+    } else if (warp < 4) {
+        // ---------------- transform: thread r = row r of the tile
+        const int r = tid;
+        for (int i = 0; i < total_sb; i++) {
+            const int s = i % kRawStages;
+            if (!mbar_wait_bounded(&raw_full[s], (i / kRawStages) & 1, err, 15)) break;
+            const uint8_t* slot = raw + (size_t)s * p.raw_bytes;
+            const uint8_t* row = slot + (size_t)r * BPDQ_Q4K_BYTES;
+            const uint4 hdr = *reinterpret_cast<const uint4*>(row);
+            float* sd = side + (size_t)(i % kSideSlots) * kSideFloats;
+            sd[2 * r] = f16_bits_to_f32(hdr.x & 0xFFFFu);
+            sd[2 * r + 1] = f16_bits_to_f32(hdr.x >> 16);
+            if (r < NPAD) sd[256 + r] = reinterpret_cast<const float*>(slot + kRowsBytes + 320 * NPAD)[r];
+            bool gave_up = false;
+            for (int half = 0; half < 2; half++) {
+                const int h = 2 * i + half, o = h % kOpStages;
+                if (h >= kOpStages && !mbar_wait_bounded(&op_empty[o], ((h / kOpStages) - 1) & 1, err, 16)) { gave_up = true; break; }
+                uint8_t* op = ops + (size_t)o * kOpBytes;
+                uint8_t* dst = op + (r >> 3) * 128 + (r & 7) * 16;     // this row's 16 bytes inside every core matrix
+                uint32_t sc4, mn4;
+                q4k_scales4(hdr.y, hdr.z, hdr.w, half, sc4, mn4);
+                const uint4* qs = reinterpret_cast<const uint4*>(row + 16 + 64 * half);
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const uint4 qv = qs[k];
+                    const uint32_t sc = byte_of(sc4, k), sl = sc & 7u, sh = sc >> 3;
+                    const uint32_t l0 = qv.x & 0x0F0F0F0Fu, l1 = qv.y & 0x0F0F0F0Fu, l2 = qv.z & 0x0F0F0F0Fu, l3 = qv.w & 0x0F0F0F0Fu;
+                    const uint32_t h0 = (qv.x >> 4) & 0x0F0F0F0Fu, h1 = (qv.y >> 4) & 0x0F0F0F0Fu, h2 = (qv.z >> 4) & 0x0F0F0F0Fu,
+                                   h3 = (qv.w >> 4) & 0x0F0F0F0Fu;
+                    // K-chunk 2k = elements 0..15 of the sub-block (low nibbles), 2k+1 = elements 16..31 (high)
+                    *reinterpret_cast<uint4*>(dst + (2 * k) * 2048) = make_uint4(l0 * sl, l1 * sl, l2 * sl, l3 * sl);
+                    *reinterpret_cast<uint4*>(dst + (2 * k + 1) * 2048) = make_uint4(h0 * sl, h1 * sl, h2 * sl, h3 * sl);
+                    *reinterpret_cast<uint4*>(dst + kPlaneBytes + (2 * k) * 2048) = make_uint4(l0 * sh, l1 * sh, l2 * sh, l3 * sh);
+                    *reinterpret_cast<uint4*>(dst + kPlaneBytes + (2 * k + 1) * 2048) = make_uint4(h0 * sh, h1 * sh, h2 * sh, h3 * sh);
+                }
+                if (half == 1) {
+                    uint32_t sca, mna;
+                    q4k_scales4(hdr.y, hdr.z, hdr.w, 0, sca, mna);
+                    *reinterpret_cast<uint4*>(dst + 2 * kPlaneBytes) = make_uint4(mna, mn4, 0, 0);    // mins of sub-blocks 0..7
+                    *reinterpret_cast<uint4*>(dst + 2 * kPlaneBytes + 2048) = make_uint4(0, 0, 0, 0);
+                }
+                // make the generic-proxy writes visible to the tensor core's reads, then publish
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&op_full[o]);
+            }
+            if (gave_up) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_empty[s]);
+        }
+    } else {
+        // ---------------- epilogue: thread r owns TMEM lane r and output row tile*128 + r
+        const int r = tid - 128;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp - 4)) << 16);
+        float facc[NPAD];
+        int i = 0;
+        for (int tl = 0; tl < my_tiles; tl++) {
+#pragma unroll
+            for (int t = 0; t < NPAD; t++) facc[t] = 0.0f;
+            bool gave_up = false;
+            for (int b = 0; b < p.nb; b++, i++) {
+                const int a = i & 1;
+                if (!mbar_wait_bounded(&acc_full[a], (i >> 1) & 1, err, 17)) { gave_up = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float* sd = side + (size_t)(i % kSideSlots) * kSideFloats;
+                const float d = sd[2 * r], dmin = sd[2 * r + 1];
+                const uint32_t col0 = lane_base + (uint32_t)(a * 4) * NPAD;
+#pragma unroll
+                for (int c = 0; c < NPAD / 16; c++) {
+                    int lo[16], hi[16], ml[16], mh[16];
+                    tmem_ld16(col0 + 16 * c, lo);
+                    tmem_ld16(col0 + NPAD + 16 * c, hi);
+                    tmem_ld16(col0 + 2 * NPAD + 16 * c, ml);
+                    tmem_ld16(col0 + 3 * NPAD + 16 * c, mh);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int t = 0; t < 16; t++) {
+                        const float v = d * (float)(8 * hi[t] + lo[t]) - dmin * (float)(64 * mh[t] + ml[t]);
+                        facc[16 * c + t] = fmaf(sd[256 + 16 * c + t], v, facc[16 * c + t]);
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[a]);
+            }
+            if (gave_up) break;
+            const int rowg = (blockIdx.x + tl * gridDim.x) * kRows + r;
+            if (rowg < p.N) {
+#pragma unroll
+                for (int t = 0; t < NPAD; t++)
+                    if (t < p.tokens) out[(size_t)t * p.N + rowg] = facc[t];
+            }
+        }
+    }
+    // ---------------- teardown: everybody meets, then the allocating warp frees tensor memory
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 9) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+static uint8_t* tc5_scratch(size_t bytes)
+{
+    static uint8_t* buf[64] = {nullptr};
+    static size_t cap[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cap[dev] < bytes) {
+        if (buf[dev]) {
+            cudaDeviceSynchronize();
+            cudaFree(buf[dev]);
+            buf[dev] = nullptr;
+            cap[dev] = 0;
+        }
+        void* ptr = nullptr;
+        const size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+        if (check_cuda(cudaMalloc(&ptr, want)) != 0) return nullptr;
+        buf[dev] = (uint8_t*)ptr;
+        cap[dev] = want;
+    }
+    return buf[dev];
+}
+
+static int tc5_weight_map(CUtensorMap* map, const uint8_t* W, int N, int nb)
+{
+    static PFN_cuTensorMapEncodeTiled encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return latch(BPDQ_ERR_CUDA);
+        encode = (PFN_cuTensorMapEncodeTiled)fn;
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)nb * (BPDQ_Q4K_BYTES / 4), (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)nb * BPDQ_Q4K_BYTES};
+    const cuuint32_t box[2] = {(cuuint32_t)(BPDQ_Q4K_BYTES / 4), (cuuint32_t)kRows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(W), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : latch(BPDQ_ERR_CUDA - 900 - (int)r);
+}
+
+template <int NPAD>
+static int launch_tc5(const CUtensorMap& wmap, const uint8_t* acts, float* out, const Tc5Plan& p, cudaStream_t s)
+{
+    auto kern = k_gemm_q4k_q8k_tc5<NPAD>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        if (rc) return rc;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(320);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, wmap, acts, out, p, device_error_flag()));
+}
+
+// out[tokens][N], X fp32 [tokens][K], C-ABI nibble order; N >= 128 rows (the TMA box), up to 64 tokens per pass.
+int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s)
+{
+    if (tokens < 0 || N < 0 || K <= 0 || (K % 256) != 0) return latch(BPDQ_ERR_ARG);
+    if (tokens == 0 || N == 0) return 0;
+    if (!W || !X || !out) return latch(BPDQ_ERR_ARG);
+    if (((uintptr_t)W & 15) || ((uintptr_t)X & 15) || ((uintptr_t)out & 3)) return latch(BPDQ_ERR_ALIGN);
+    if (N < kRows) return latch(BPDQ_ERR_RANGE);
+    CUtensorMap wmap;
+    int rc = tc5_weight_map(&wmap, W, N, K / 256);
+    if (rc) return rc;
+    for (int t0 = 0; t0 < tokens; t0 += 64) {
+        const int T = tokens - t0 < 64 ? tokens - t0 : 64;
+        Tc5Plan p;
+        p.N = N;
+        p.nb = K / 256;
+        p.tokens = T;
+        p.npad = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
+        p.n_tiles = (N + kRows - 1) / kRows;
+        p.grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
+        p.act_bytes = 324 * p.npad;
+        p.raw_bytes = (kRowsBytes + p.act_bytes + 127) / 128 * 128;
+        size_t off = 0;
+        auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
+        p.off_raw = take((size_t)kRawStages * p.raw_bytes);
+        p.off_op = take((size_t)kOpStages * kOpBytes);
+        p.off_side = take((size_t)kSideSlots * (256 + p.npad) * 4);
+        p.off_bar = take(256);
+        p.smem = off;
+        if (p.smem > 227 * 1024) return latch(BPDQ_ERR_RANGE);
+        uint8_t* acts = tc5_scratch((size_t)p.nb * p.act_bytes);
+        if (!acts) return latch(BPDQ_ERR_CUDA);
+        const long units = (long)p.nb * p.npad;
+        long want = (units + 7) / 8, cap = (long)sm_count() * 8;
+        k_quant_tc5_acts<<<(int)(want < cap ? want : cap), 256, 0, s>>>(X + (size_t)t0 * K, acts, T, p.npad, K);
+        rc = check_cuda(cudaGetLastError());
+        if (rc) return rc;
+        float* o = out + (size_t)t0 * N;
+        rc = p.npad == 16 ? launch_tc5<16>(wmap, acts, o, p, s) : (p.npad == 32 ? launch_tc5<32>(wmap, acts, o, p, s) : launch_tc5<64>(wmap, acts, o, p, s));
+        if (rc) return latch(rc);
+    }
+    return 0;
+}
+
+}  // namespace bpdq
+
+using namespace bpdq;
+
+extern "C" {
+// The tcgen05 kernel directly (bpd_qmm_q4k_q8k_cuda's dispatcher decides when to use it).
+int bpd_qmm_q4k_q8k_tc5_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream)
+{
+    return gemm_q4k_q8k_tc5(qweight, X, out, tokens, M, K, (cudaStream_t)stream);
+}
+}

@@ -100,6 +100,13 @@ def main():
         us = tm.run(lambda i: lib.bpd_qmm_q4k_q8k_cuda(ws[i % n], X, o, M, N, K, 0, 0, None, s), 50)
         report(f"3: Q4_K x Q8_K GEMM M={M} N=14336 K=4096", us, synth.gemv_bytes_q4k(N, K, M),
                tflops=round(2.0 * M * N * K / us / 1e6, 2))
+        if M >= 16:
+            us = tm.run(lambda i: lib.bpd_qmm_q4k_q8k_tc5_cuda(ws[i % n], X, o, M, N, K, s), 50)
+            report(f"3: same, tcgen05 kernel, M={M}", us, synth.gemv_bytes_q4k(N, K, M),
+                   tflops=round(2.0 * M * N * K / us / 1e6, 2))
+            us = tm.run(lambda i: lib.bpd_qmm_q4k_q8k_mma_cuda(ws[i % n], X, o, M, N, K, s), 50)
+            report(f"3: same, mma.sync kernel, M={M}", us, synth.gemv_bytes_q4k(N, K, M),
+                   tflops=round(2.0 * M * N * K / us / 1e6, 2))
         lib.bpdq_free(X)
         lib.bpdq_free(o)
     # ---- W4A32 drop-in on the same matrix

@@ -175,6 +175,8 @@ int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int 
 /* the int8 tensor-core kernel behind bpd_qmm_q4k_q8k_cuda for more than 8 tokens, callable at any
  * token count: out[tokens][M], X float [tokens][K], nibble order of bench/bpd_quant.c:68-72 */
 int bpd_qmm_q4k_q8k_mma_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream);
+/* the same product on tcgen05 tensor cores with TMEM accumulators (M >= 128 weight rows) */
+int bpd_qmm_q4k_q8k_tc5_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream);
 /* dispatch-shaped forms: argument order of gpu_vecmat (lib/kernel_templates_llama.pl:147-158)
  * and gpu_matmul (lib/kernel_templates_llama.pl:1104-1112) with the fp32 [K][N] weight
  * replaced by Q4_K rows [N][K/256][144] */

@@ -13,6 +13,8 @@ def run(lib, entry, W, X, T, N, K):
     dW, dX, dO = Dev(lib, W), Dev(lib, X), Dev(lib, nbytes=T * N * 4, fill=0xFF)
     if entry == "mma":
         rc = lib.bpd_qmm_q4k_q8k_mma_cuda(dW.ptr, dX.ptr, dO.ptr, T, N, K, None)
+    elif entry == "tc5":
+        rc = lib.bpd_qmm_q4k_q8k_tc5_cuda(dW.ptr, dX.ptr, dO.ptr, T, N, K, None)
     else:
         rc = lib.bpd_qmm_q4k_q8k_cuda(dW.ptr, dX.ptr, dO.ptr, T, N, K, 0, 0, None, None)
     assert rc == 0
@@ -30,6 +32,24 @@ def test_mma_kernel_matches_checker(lib, oracle, T, N, K):
     got = run(lib, "mma", W, X, T, N, K)
     ref32, ref64 = oracle.qmm_q4k_q8k(W, X, T, N, K)
     assert normwise(got, ref64) <= TOL
+
+
+@pytest.mark.parametrize("T,N,K", [(16, 128, 256), (9, 300, 768), (32, 384, 1024), (64, 512, 4096), (40, 1000, 2048),
+                                   (100, 256, 512), (1, 128, 256), (64, 14336 // 8, 4096)])
+def test_tcgen05_kernel_matches_checker(lib, oracle, T, N, K):
+    """The TMEM-accumulator kernel: same integers, same tolerance; partial last row tile included."""
+    rng = np.random.default_rng(T * 11 + N + K)
+    W = synth.q4k_matrix(N, K, rng)
+    X = synth.activations(K, rng, rows=T)
+    got = run(lib, "tc5", W, X, T, N, K)
+    _, ref64 = oracle.qmm_q4k_q8k(W, X, T, N, K)
+    assert normwise(got, ref64) <= TOL
+
+
+def test_tcgen05_kernel_rejects_short_matrices(lib):
+    d = Dev(lib, nbytes=64 * 144 + 4096)
+    assert lib.bpd_qmm_q4k_q8k_tc5_cuda(d.ptr, d.ptr, d.ptr, 16, 64, 256, None) == -3
+    lib.bpdq_clear_status()
 
 
 def test_dispatcher_agrees_across_token_counts(lib, oracle):
