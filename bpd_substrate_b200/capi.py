@@ -28,6 +28,7 @@ SIGNATURES = {
     "bpdq_sm_count": (i32, []),
     "bpdq_set_dequant_tuning": (None, [i32, i32]),
     "bpdq_debug_trace": (None, [vp, sz, i32]),
+    "bpdq_debug_trace_tc5": (None, [vp]),
     # memory (size_t)
     "bpdq_alloc": (vp, [sz]),
     "bpdq_free": (None, [vp]),

@@ -10,19 +10,19 @@
 // eight K=32 steps, D_ml, D_mh in one step each.  The fp32 scales are applied once per
 // super-block by the epilogue warps after tcgen05.ld.
 //
-// One CTA = 128 weight rows (the MMA M) x all tokens (the MMA N, 16..64), ten warps:
-//   warps 0-3  transform: thread r turns row r's packed nibbles into the two int8 A planes in
-//              the canonical K-major core-matrix layout (8 rows x 16 bytes per 128-byte core
-//              matrix; chunk stride 2048 B, row-group stride 128 B), half a super-block at a time
-//   warps 4-7  epilogue: thread r owns TMEM lane r: tcgen05.ld 16 columns of the four
-//              accumulators at a time, scale, accumulate 64 fp32 outputs in registers
-//   warp 8     producer: per super-block one tiled TMA request for the 128 x 144-byte block of
-//              raw rows and one bulk copy of the activations' block (already in canonical B
-//              layout, written by k_quant_tc5_acts), ring of two stages
-//   warp 9     allocates tensor memory; one lane issues the MMAs and commits to mbarriers
-// Rings: raw (2 stages) -> operands (3 half-super-block stages) -> TMEM (2 accumulator sets).
+// One CTA = 128 weight rows (the MMA M) x all tokens (the MMA N, 16..64), fourteen warps:
+//   warps 0-7   transform: two threads per row turn its packed nibbles into the two int8 A planes
+//               in the canonical K-major core-matrix layout (8 rows x 16 bytes per 128-byte core
+//               matrix; chunk stride 2048 B, row-group stride 128 B), half a super-block at a time
+//   warps 8-11  epilogue: thread r owns TMEM lane r: tcgen05.ld 16 columns of the four
+//               accumulators at a time, scale, accumulate up to 64 fp32 outputs in registers
+//   warp 12     producer: per super-block one tiled TMA request for the 128 x 144-byte block of
+//               raw rows and one bulk copy of the activations' block (already in canonical B
+//               layout, written by k_quant_tc5_acts), ring of 2-4 stages
+//   warp 13     allocates tensor memory; one lane issues the MMAs and commits to mbarriers
+// Rings: raw (2-4 stages) -> operands (3 half-super-block stages) -> TMEM (2 accumulator sets).
 // All mbarrier waits are bounded; on a timeout the role records an error code and leaves, the
-// others time out in turn, and warp 9 frees the tensor memory before it returns.
+// others time out in turn, and warp 13 frees the tensor memory before it returns.
 #include "bpdq_common.cuh"
 #include "../../include/bpdq.h"
 
@@ -32,19 +32,41 @@
 namespace bpdq {
 
 constexpr int kRows = 128;
-constexpr int kRawStages = 2, kOpStages = 3, kSideSlots = 6;
+constexpr int kMaxRawStages = 4, kOpStages = 3, kSideSlots = 8;
+constexpr int kTransformWarps = 8;   // two threads per weight row, two sub-blocks each per half super-block
 constexpr int kPlaneBytes = 16384;                 // one A plane of half a super-block: 8 chunks x 2048 B
 constexpr int kOpBytes = 2 * kPlaneBytes + 4096;   // lo, hi, and the 4 KB mins operand
 constexpr int kRowsBytes = kRows * BPDQ_Q4K_BYTES; // 18432
 
 struct Tc5Plan {
     int N, nb, tokens, npad;      // weight rows, super-blocks per row, valid / padded tokens (16, 32 or 64)
-    int n_tiles, grid;
+    int n_tiles, grid, raw_stages;
     int act_bytes;                // scratch bytes per super-block: 324 * npad
     int raw_bytes;                // ring slot: rows + activations
     int off_raw, off_op, off_side, off_bar;
     size_t smem;
+    unsigned long long* trace;    // tuning aid: global-timer stamps of CTA 0, [role 0..4][super-block 0..31], or null
 };
+
+__device__ __forceinline__ unsigned long long tc5_timer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TC5_TRACE(role, i) do { if (p.trace && blockIdx.x == 0 && (i) < 32) p.trace[(role) * 32 + (i)] = tc5_timer(); } while (0)
+
+// Bounded wait with a short sleep between polls: the roles that only consume leave the issue
+// slots to the single thread that feeds the tensor core.
+__device__ __forceinline__ bool mbar_wait_sleepy(uint64_t* bar, uint32_t parity, int* err, int code)
+{
+    for (uint32_t i = 0; i < (1u << 22); i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(40);
+    }
+    if (err) atomicCAS(err, 0, code);
+    return false;
+}
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo)
 {
@@ -145,7 +167,7 @@ __global__ void __launch_bounds__(256) k_quant_tc5_acts(const float* __restrict_
 }
 
 template <int NPAD>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(448, 1)
 k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __restrict__ acts, float* __restrict__ out,
                    const Tc5Plan p, int* __restrict__ err)
 {
@@ -154,9 +176,10 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     uint8_t* ops = smem + p.off_op;
     float* side = reinterpret_cast<float*>(smem + p.off_side);   // [kSideSlots][256 hdr floats + NPAD dA floats]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);
-    uint64_t* raw_full = bars;                   // [kRawStages]
-    uint64_t* raw_empty = raw_full + kRawStages; // transform warps (4) + MMA commit (1)
-    uint64_t* op_full = raw_empty + kRawStages;  // [kOpStages] transform warps (4)
+    const int kRawStages = p.raw_stages;
+    uint64_t* raw_full = bars;                      // [raw_stages]
+    uint64_t* raw_empty = raw_full + kMaxRawStages; // transform warps (8) + MMA commit (1)
+    uint64_t* op_full = raw_empty + kMaxRawStages;  // [kOpStages] transform warps (8)
     uint64_t* op_empty = op_full + kOpStages;    // MMA commit (1)
     uint64_t* acc_full = op_empty + kOpStages;   // [2] MMA commit (1)
     uint64_t* acc_empty = acc_full + 2;          // epilogue warps (4)
@@ -165,12 +188,12 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
-        for (int s = 0; s < kRawStages; s++) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 5); }
-        for (int s = 0; s < kOpStages; s++) { mbar_init(&op_full[s], 4); mbar_init(&op_empty[s], 1); }
+        for (int s = 0; s < kMaxRawStages; s++) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kTransformWarps + 1); }
+        for (int s = 0; s < kOpStages; s++) { mbar_init(&op_full[s], kTransformWarps); mbar_init(&op_empty[s], 1); }
         for (int s = 0; s < 2; s++) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
         mbar_init_fence();
     }
-    if (warp == 9) {
+    if (warp == 13) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -185,20 +208,21 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int total_sb = my_tiles * p.nb;       // super-blocks this CTA walks, over all its tiles
 
-    if (warp == 8) {
+    if (warp == 12) {
         // ---------------- producer
         if (lane == 0) {
             for (int i = 0; i < total_sb; i++) {
                 const int s = i % kRawStages;
-                if (i >= kRawStages && !mbar_wait_bounded(&raw_empty[s], ((i / kRawStages) - 1) & 1, err, 11)) break;
+                if (i >= kRawStages && !mbar_wait_sleepy(&raw_empty[s], ((i / kRawStages) - 1) & 1, err, 11)) break;
                 const int tile = blockIdx.x + (i / p.nb) * gridDim.x, b = i % p.nb;
                 uint8_t* slot = raw + (size_t)s * p.raw_bytes;
                 mbar_expect_tx(&raw_full[s], (uint32_t)(kRowsBytes + p.act_bytes));
                 tma_rows_2d(slot, &wmap, b * (BPDQ_Q4K_BYTES / 4), tile * kRows, &raw_full[s]);
                 bulk_g2s(slot + kRowsBytes, acts + (size_t)b * p.act_bytes, (uint32_t)p.act_bytes, &raw_full[s]);
+                TC5_TRACE(0, i);
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 13) {
         // ---------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
@@ -206,59 +230,72 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                 const int s = i % kRawStages, a = i & 1;
                 if (!mbar_wait_bounded(&raw_full[s], (i / kRawStages) & 1, err, 12)) break;
                 if (i >= 2 && !mbar_wait_bounded(&acc_empty[a], ((i >> 1) - 1) & 1, err, 13)) break;
+                TC5_TRACE(9, i);
+                // descriptors differ only in their 14-bit start-address field (bytes >> 4): build one
+                // per operand and step it with an add
                 const uint32_t acts_s = smem_addr(raw + (size_t)s * p.raw_bytes + kRowsBytes);
+                const uint64_t b_base = umma_desc(acts_s, 16 * NPAD, 128);
                 const uint32_t d_lo = tmem_base + (uint32_t)(a * 4 + 0) * NPAD, d_hi = d_lo + NPAD;
                 const uint32_t d_ml = d_lo + 2 * NPAD, d_mh = d_lo + 3 * NPAD;
                 bool gave_up = false;
+#pragma unroll
                 for (int half = 0; half < 2; half++) {
                     const int h = 2 * i + half, o = h % kOpStages;
                     if (!mbar_wait_bounded(&op_full[o], (h / kOpStages) & 1, err, 14)) { gave_up = true; break; }
+                    TC5_TRACE(5 + 2 * half, i);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t op_s = smem_addr(ops + (size_t)o * kOpBytes);
+                    const uint64_t a_base = umma_desc(smem_addr(ops + (size_t)o * kOpBytes), 2048, 128);
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const int j = 4 * half + k;   // sub-block: K-chunks 2j, 2j+1 of the B operand
-                        const uint64_t bdesc = umma_desc(acts_s + (uint32_t)(2 * j) * 16 * NPAD, 16 * NPAD, 128);
+                        const uint64_t bdesc = b_base + (uint64_t)((2 * j * 16 * NPAD) >> 4);
                         const uint32_t accum = (half | k) ? 1u : 0u;
-                        umma_i8(d_lo, umma_desc(op_s + (uint32_t)(2 * k) * 2048, 2048, 128), bdesc, idesc, accum);
-                        umma_i8(d_hi, umma_desc(op_s + kPlaneBytes + (uint32_t)(2 * k) * 2048, 2048, 128), bdesc, idesc, accum);
+                        umma_i8(d_lo, a_base + (uint64_t)((2 * k * 2048) >> 4), bdesc, idesc, accum);
+                        umma_i8(d_hi, a_base + (uint64_t)((kPlaneBytes + 2 * k * 2048) >> 4), bdesc, idesc, accum);
                     }
                     if (half == 1) {
-                        const uint64_t mdesc = umma_desc(op_s + 2 * kPlaneBytes, 2048, 128);
-                        umma_i8(d_ml, mdesc, umma_desc(acts_s + 256 * NPAD, 16 * NPAD, 128), idesc, 0u);
-                        umma_i8(d_mh, mdesc, umma_desc(acts_s + 288 * NPAD, 16 * NPAD, 128), idesc, 0u);
+                        const uint64_t mdesc = a_base + (uint64_t)((2 * kPlaneBytes) >> 4);
+                        umma_i8(d_ml, mdesc, b_base + (uint64_t)((256 * NPAD) >> 4), idesc, 0u);
+                        umma_i8(d_mh, mdesc, b_base + (uint64_t)((288 * NPAD) >> 4), idesc, 0u);
                     }
                     umma_commit(&op_empty[o]);
+                    TC5_TRACE(6 + 2 * half, i);
                 }
                 if (gave_up) break;
                 umma_commit(&raw_empty[s]);
                 umma_commit(&acc_full[a]);
+                TC5_TRACE(2, i);
             }
         }
-    } else if (warp < 4) {
-        // ---------------- transform: thread r = row r of the tile
-        const int r = tid;
+    } else if (warp < kTransformWarps) {
+        // ---------------- transform: threads r and 128 + r share row r of the tile (sub-blocks 2*part, 2*part+1 of each half)
+        const int r = tid & 127, part = tid >> 7;
         for (int i = 0; i < total_sb; i++) {
             const int s = i % kRawStages;
-            if (!mbar_wait_bounded(&raw_full[s], (i / kRawStages) & 1, err, 15)) break;
+            if (!mbar_wait_sleepy(&raw_full[s], (i / kRawStages) & 1, err, 15)) break;
+            if (tid == 0) TC5_TRACE(1, i);
             const uint8_t* slot = raw + (size_t)s * p.raw_bytes;
             const uint8_t* row = slot + (size_t)r * BPDQ_Q4K_BYTES;
             const uint4 hdr = *reinterpret_cast<const uint4*>(row);
             float* sd = side + (size_t)(i % kSideSlots) * kSideFloats;
-            sd[2 * r] = f16_bits_to_f32(hdr.x & 0xFFFFu);
-            sd[2 * r + 1] = f16_bits_to_f32(hdr.x >> 16);
-            if (r < NPAD) sd[256 + r] = reinterpret_cast<const float*>(slot + kRowsBytes + 320 * NPAD)[r];
+            if (part == 0) {
+                sd[2 * r] = f16_bits_to_f32(hdr.x & 0xFFFFu);
+                sd[2 * r + 1] = f16_bits_to_f32(hdr.x >> 16);
+            } else if (r < NPAD) {
+                sd[256 + r] = reinterpret_cast<const float*>(slot + kRowsBytes + 320 * NPAD)[r];
+            }
             bool gave_up = false;
             for (int half = 0; half < 2; half++) {
                 const int h = 2 * i + half, o = h % kOpStages;
-                if (h >= kOpStages && !mbar_wait_bounded(&op_empty[o], ((h / kOpStages) - 1) & 1, err, 16)) { gave_up = true; break; }
+                if (h >= kOpStages && !mbar_wait_sleepy(&op_empty[o], ((h / kOpStages) - 1) & 1, err, 16)) { gave_up = true; break; }
                 uint8_t* op = ops + (size_t)o * kOpBytes;
                 uint8_t* dst = op + (r >> 3) * 128 + (r & 7) * 16;     // this row's 16 bytes inside every core matrix
                 uint32_t sc4, mn4;
                 q4k_scales4(hdr.y, hdr.z, hdr.w, half, sc4, mn4);
                 const uint4* qs = reinterpret_cast<const uint4*>(row + 16 + 64 * half);
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
+                for (int kk = 0; kk < 2; kk++) {
+                    const int k = 2 * part + kk;
                     const uint4 qv = qs[k];
                     const uint32_t sc = byte_of(sc4, k), sl = sc & 7u, sh = sc >> 3;
                     const uint32_t l0 = qv.x & 0x0F0F0F0Fu, l1 = qv.y & 0x0F0F0F0Fu, l2 = qv.z & 0x0F0F0F0Fu, l3 = qv.w & 0x0F0F0F0Fu;
@@ -270,7 +307,7 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                     *reinterpret_cast<uint4*>(dst + kPlaneBytes + (2 * k) * 2048) = make_uint4(l0 * sh, l1 * sh, l2 * sh, l3 * sh);
                     *reinterpret_cast<uint4*>(dst + kPlaneBytes + (2 * k + 1) * 2048) = make_uint4(h0 * sh, h1 * sh, h2 * sh, h3 * sh);
                 }
-                if (half == 1) {
+                if (half == 1 && part == 1) {
                     uint32_t sca, mna;
                     q4k_scales4(hdr.y, hdr.z, hdr.w, 0, sca, mna);
                     *reinterpret_cast<uint4*>(dst + 2 * kPlaneBytes) = make_uint4(mna, mn4, 0, 0);    // mins of sub-blocks 0..7
@@ -284,11 +321,12 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
             if (gave_up) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[s]);
+            if (tid == 0) TC5_TRACE(3, i);
         }
     } else {
         // ---------------- epilogue: thread r owns TMEM lane r and output row tile*128 + r
-        const int r = tid - 128;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp - 4)) << 16);
+        const int r = tid - 32 * kTransformWarps;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp - kTransformWarps)) << 16);
         float facc[NPAD];
         int i = 0;
         for (int tl = 0; tl < my_tiles; tl++) {
@@ -297,7 +335,7 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
             bool gave_up = false;
             for (int b = 0; b < p.nb; b++, i++) {
                 const int a = i & 1;
-                if (!mbar_wait_bounded(&acc_full[a], (i >> 1) & 1, err, 17)) { gave_up = true; break; }
+                if (!mbar_wait_sleepy(&acc_full[a], (i >> 1) & 1, err, 17)) { gave_up = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float* sd = side + (size_t)(i % kSideSlots) * kSideFloats;
                 const float d = sd[2 * r], dmin = sd[2 * r + 1];
@@ -319,6 +357,7 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[a]);
+                if (r == 0) TC5_TRACE(4, i);
             }
             if (gave_up) break;
             const int rowg = (blockIdx.x + tl * gridDim.x) * kRows + r;
@@ -332,11 +371,13 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     // ---------------- teardown: everybody meets, then the allocating warp frees tensor memory
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 13) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
 }
+
+static unsigned long long* g_tc5_trace = nullptr;
 
 static uint8_t* tc5_scratch(size_t bytes)
 {
@@ -394,7 +435,7 @@ static int launch_tc5(const CUtensorMap& wmap, const uint8_t* acts, float* out, 
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.grid);
-    cfg.blockDim = dim3(320);
+    cfg.blockDim = dim3(448);
     cfg.dynamicSmemBytes = p.smem;
     cfg.stream = s;
     cudaLaunchAttribute at[1];
@@ -422,6 +463,7 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
         p.N = N;
         p.nb = K / 256;
         p.tokens = T;
+        p.trace = g_tc5_trace;
         p.npad = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
         p.n_tiles = (N + kRows - 1) / kRows;
         p.grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
@@ -429,7 +471,11 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
         p.raw_bytes = (kRowsBytes + p.act_bytes + 127) / 128 * 128;
         size_t off = 0;
         auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
-        p.off_raw = take((size_t)kRawStages * p.raw_bytes);
+        const size_t fixed = (size_t)kOpStages * kOpBytes + ((size_t)kSideSlots * (256 + p.npad) * 4 + 127) / 128 * 128 + 256;
+        p.raw_stages = (int)((227 * 1024 - fixed) / p.raw_bytes);
+        if (p.raw_stages > kMaxRawStages) p.raw_stages = kMaxRawStages;
+        if (p.raw_stages < 2) return latch(BPDQ_ERR_RANGE);
+        p.off_raw = take((size_t)p.raw_stages * p.raw_bytes);
         p.off_op = take((size_t)kOpStages * kOpBytes);
         p.off_side = take((size_t)kSideSlots * (256 + p.npad) * 4);
         p.off_bar = take(256);
@@ -454,6 +500,8 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
 using namespace bpdq;
 
 extern "C" {
+// Tuning aid: CTA 0 of later tcgen05 launches writes 5 x 32 global-timer stamps (ns) to dev_buf; NULL stops.
+void bpdq_debug_trace_tc5(void* dev_buf) { g_tc5_trace = (unsigned long long*)dev_buf; }
 // The tcgen05 kernel directly (bpd_qmm_q4k_q8k_cuda's dispatcher decides when to use it).
 int bpd_qmm_q4k_q8k_tc5_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream)
 {

@@ -49,6 +49,7 @@ void bpdq_set_dequant_tuning(int variant, int ctas_per_sm);
 int bpdq_sm_count(void);
 /* tuning aid: the next `launches` GEMV launches write 8 global-timer stamps (ns) per CTA */
 void bpdq_debug_trace(void* dev_buf, size_t stride_u64, int launches);
+void bpdq_debug_trace_tc5(void* dev_buf);   /* 5 x 32 stamps of CTA 0 of the tcgen05 kernel */
 
 /* ---- device memory helpers (additive, size_t) ------------------------------------------ */
 void* bpdq_alloc(size_t bytes);
