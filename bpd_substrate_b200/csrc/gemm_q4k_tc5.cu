@@ -12,15 +12,20 @@
 //
 // One CTA = 128 weight rows (the MMA M) x all tokens (the MMA N, 16..64), fourteen warps:
 //   warps 0-7   transform: two threads per row turn its packed nibbles into the two int8 A planes
-//               in the canonical K-major core-matrix layout (8 rows x 16 bytes per 128-byte core
-//               matrix; chunk stride 2048 B, row-group stride 128 B), half a super-block at a time
+//               and store them straight into tensor memory (tcgen05.st: lane = row, one 32-bit
+//               column = four K elements), half a super-block at a time.  The A operand never
+//               touches shared memory: expanded to two bytes per weight it would cost four times
+//               the shared-memory traffic of the packed rows and bound the kernel there.
 //   warps 8-11  epilogue: thread r owns TMEM lane r: tcgen05.ld 16 columns of the four
 //               accumulators at a time, scale, accumulate up to 64 fp32 outputs in registers
 //   warp 12     producer: per super-block one tiled TMA request for the 128 x 144-byte block of
-//               raw rows and one bulk copy of the activations' block (already in canonical B
-//               layout, written by k_quant_tc5_acts), ring of 2-4 stages
+//               raw rows and one bulk copy of the activations' block (the B operand, already in the
+//               canonical K-major core-matrix layout: 8 tokens x 16 bytes per 128-byte core matrix,
+//               written by k_quant_tc5_acts)
 //   warp 13     allocates tensor memory; one lane issues the MMAs and commits to mbarriers
-// Rings: raw (2-4 stages) -> operands (3 half-super-block stages) -> TMEM (2 accumulator sets).
+// Rings: raw rows + activations in shared memory (2-6 stages) -> A planes in TMEM (3-4 half-
+// super-block stages of 64 columns, plus two 8-column stages for the mins) -> accumulators in
+// TMEM (two sets of 4 x tokens columns; one set at 64 tokens, where two would not fit 512 columns).
 // All mbarrier waits are bounded; on a timeout the role records an error code and leaves, the
 // others time out in turn, and warp 13 frees the tensor memory before it returns.
 #include "bpdq_common.cuh"
@@ -32,10 +37,9 @@
 namespace bpdq {
 
 constexpr int kRows = 128;
-constexpr int kMaxRawStages = 4, kOpStages = 3, kSideSlots = 8;
-constexpr int kTransformWarps = 8;   // two threads per weight row, two sub-blocks each per half super-block
-constexpr int kPlaneBytes = 16384;                 // one A plane of half a super-block: 8 chunks x 2048 B
-constexpr int kOpBytes = 2 * kPlaneBytes + 4096;   // lo, hi, and the 4 KB mins operand
+constexpr int kMaxRawStages = 6, kMaxOpStages = 4, kSideSlots = 8;
+constexpr int kOpCols = 64;                        // TMEM columns of one A stage: lo plane 32 (4 sub-blocks x K=32 bytes), hi plane 32
+constexpr int kMinCols = 8;                        // one K=32 step: columns 0,1 = the eight mins, rest zero
 constexpr int kRowsBytes = kRows * BPDQ_Q4K_BYTES; // 18432
 
 struct Tc5Plan {
@@ -43,7 +47,7 @@ struct Tc5Plan {
     int n_tiles, grid, raw_stages;
     int act_bytes;                // scratch bytes per super-block: 324 * npad
     int raw_bytes;                // ring slot: rows + activations
-    int off_raw, off_op, off_side, off_bar;
+    int off_raw, off_side, off_bar;
     size_t smem;
     unsigned long long* trace;    // tuning aid: global-timer stamps of CTA 0, [role 0..4][super-block 0..31], or null
 };
@@ -51,10 +55,14 @@ struct Tc5Plan {
 __device__ __forceinline__ unsigned long long tc5_timer()
 {
     unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
     return t;
 }
+#ifdef BPDQ_TC5_TRACE
 #define TC5_TRACE(role, i) do { if (p.trace && blockIdx.x == 0 && (i) < 32) p.trace[(role) * 32 + (i)] = tc5_timer(); } while (0)
+#else
+#define TC5_TRACE(role, i) do { } while (0)
+#endif
 
 // Bounded wait with a short sleep between polls: the roles that only consume leave the issue
 // slots to the single thread that feeds the tensor core.
@@ -75,26 +83,46 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo, uint
     return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) |
            ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
 }
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum)
+// A operand in tensor memory (lane = row, column = four consecutive K bytes), B through a descriptor.
+template <int ACCUM>
+__device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc)
 {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(0)
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "n"(ACCUM)
         : "memory");
+}
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const uint32_t (&v)[8])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]),
+                 "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16])
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, int (&v)[8])
 {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr));
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr));
 }
 __device__ __forceinline__ void tma_rows_2d(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar)
 {
@@ -166,34 +194,66 @@ __global__ void __launch_bounds__(256) k_quant_tc5_acts(const float* __restrict_
     }
 }
 
+// Warp roles per padded token count.  Sixteen transform warps (four threads per weight row) hide the
+// shared-memory and tcgen05.st latencies; at 64 tokens the epilogue is the heavier side and gets
+// eight warps (two per TMEM lane quadrant, half of the columns each) while the transform keeps eight.
+template <int NPAD> struct Tc5Shape {
+    static constexpr int kTransformWarps = NPAD == 64 ? 8 : 16;
+    static constexpr int kEpilogueWarps = NPAD == 64 ? 8 : 4;
+    static constexpr int kThreads = (kTransformWarps + kEpilogueWarps + 2) * 32;
+};
+
 template <int NPAD>
-__global__ void __launch_bounds__(448, 1)
+__global__ void __launch_bounds__(Tc5Shape<NPAD>::kThreads, 1)
 k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __restrict__ acts, float* __restrict__ out,
                    const Tc5Plan p, int* __restrict__ err)
 {
+    constexpr int kTransformWarps = Tc5Shape<NPAD>::kTransformWarps;
+    constexpr int kEpilogueWarps = Tc5Shape<NPAD>::kEpilogueWarps;
+    constexpr int kProducerWarp = kTransformWarps + kEpilogueWarps, kMmaWarp = kProducerWarp + 1;
+    // transform warps work in groups of eight (two threads per weight row, two sub-blocks each per half
+    // super-block); with two groups they take alternate super-blocks, so that one group's chain of
+    // waits, loads, stores and arrivals overlaps the other's
+    constexpr int kGroups = kTransformWarps / 8;
+    constexpr int kParts = 2, kSubs = 2;
+    // Two accumulator sets of four (lo, hi, ml, mh) x kAccCols columns.  Up to 32 tokens they alternate by
+    // super-block; at 64 tokens two such pairs would not fit 512 columns, so the sets are the two token halves:
+    // each super-block is issued as two passes of N = 32 over the same A operand, and the epilogue of one
+    // half runs while the other half's MMAs execute.
+    constexpr int kPasses = NPAD == 64 ? 2 : 1;
+    constexpr int kAccCols = NPAD / kPasses;                // MMA N = token columns per accumulator
+    constexpr int kEpiCols = kAccCols;                      // token columns per epilogue warp
+    static_assert(kEpilogueWarps == 4 * kPasses, "one epilogue warp per TMEM lane quadrant and pass");
+    // tensor-memory columns: accumulator sets, then the A stages, then the two mins stages
+    constexpr int kAccSets = 2;
+    constexpr int kOpStages = NPAD == 16 ? 4 : 3;
+    constexpr uint32_t kColOps = kAccSets * 4 * kAccCols;
+    constexpr uint32_t kColMins = kColOps + kOpStages * kOpCols;
+    static_assert(kColMins + 2 * kMinCols <= 512, "tensor memory has 512 columns");
+    static_assert(kOpStages <= kMaxOpStages && kOpStages <= 4, "a mins stage is reused two super-blocks later");
+
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* raw = smem + p.off_raw;
-    uint8_t* ops = smem + p.off_op;
     float* side = reinterpret_cast<float*>(smem + p.off_side);   // [kSideSlots][256 hdr floats + NPAD dA floats]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);
     const int kRawStages = p.raw_stages;
-    uint64_t* raw_full = bars;                      // [raw_stages]
-    uint64_t* raw_empty = raw_full + kMaxRawStages; // transform warps (8) + MMA commit (1)
-    uint64_t* op_full = raw_empty + kMaxRawStages;  // [kOpStages] transform warps (8)
-    uint64_t* op_empty = op_full + kOpStages;    // MMA commit (1)
-    uint64_t* acc_full = op_empty + kOpStages;   // [2] MMA commit (1)
-    uint64_t* acc_empty = acc_full + 2;          // epilogue warps (4)
+    uint64_t* raw_full = bars;                       // [raw_stages] producer's expect_tx + bytes
+    uint64_t* raw_empty = raw_full + kMaxRawStages;  // MMA commit (its MMAs follow the transform's reads of the slot)
+    uint64_t* xf_full = raw_empty + kMaxRawStages;   // [2] by super-block parity: the eight warps of a transform group
+    uint64_t* op_empty = xf_full + 2;                // [kOpStages] MMA commit
+    uint64_t* acc_full = op_empty + kMaxOpStages;    // [kAccSets] MMA commit
+    uint64_t* acc_empty = acc_full + 2;              // epilogue warps
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     constexpr int kSideFloats = 256 + NPAD;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
-        for (int s = 0; s < kMaxRawStages; s++) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kTransformWarps + 1); }
-        for (int s = 0; s < kOpStages; s++) { mbar_init(&op_full[s], kTransformWarps); mbar_init(&op_empty[s], 1); }
-        for (int s = 0; s < 2; s++) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+        for (int s = 0; s < kMaxRawStages; s++) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 1); }
+        for (int s = 0; s < kMaxOpStages; s++) mbar_init(&op_empty[s], 1);
+        for (int s = 0; s < 2; s++) { mbar_init(&xf_full[s], 8); mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
         mbar_init_fence();
     }
-    if (warp == 13) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_slot)), "r"(512)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -208,170 +268,224 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int total_sb = my_tiles * p.nb;       // super-blocks this CTA walks, over all its tiles
 
-    if (warp == 12) {
+    if (warp == kProducerWarp) {
         // ---------------- producer
         if (lane == 0) {
+            int s = 0, b = 0, tile = blockIdx.x;
+            uint32_t par = 1;   // parity of the consumers' release one round of stages back
             for (int i = 0; i < total_sb; i++) {
-                const int s = i % kRawStages;
-                if (i >= kRawStages && !mbar_wait_sleepy(&raw_empty[s], ((i / kRawStages) - 1) & 1, err, 11)) break;
-                const int tile = blockIdx.x + (i / p.nb) * gridDim.x, b = i % p.nb;
+                if (i >= kRawStages && !mbar_wait_sleepy(&raw_empty[s], par, err, 11)) break;
                 uint8_t* slot = raw + (size_t)s * p.raw_bytes;
                 mbar_expect_tx(&raw_full[s], (uint32_t)(kRowsBytes + p.act_bytes));
                 tma_rows_2d(slot, &wmap, b * (BPDQ_Q4K_BYTES / 4), tile * kRows, &raw_full[s]);
                 bulk_g2s(slot + kRowsBytes, acts + (size_t)b * p.act_bytes, (uint32_t)p.act_bytes, &raw_full[s]);
                 TC5_TRACE(0, i);
+                if (++s == kRawStages) { s = 0; par ^= 1u; }
+                if (++b == p.nb) { b = 0; tile += gridDim.x; }
             }
         }
-    } else if (warp == 13) {
-        // ---------------- MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NPAD >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
-            for (int i = 0; i < total_sb; i++) {
-                const int s = i % kRawStages, a = i & 1;
-                if (!mbar_wait_bounded(&raw_full[s], (i / kRawStages) & 1, err, 12)) break;
-                if (i >= 2 && !mbar_wait_bounded(&acc_empty[a], ((i >> 1) - 1) & 1, err, 13)) break;
-                TC5_TRACE(9, i);
-                // descriptors differ only in their 14-bit start-address field (bytes >> 4): build one
-                // per operand and step it with an add
-                const uint32_t acts_s = smem_addr(raw + (size_t)s * p.raw_bytes + kRowsBytes);
-                const uint64_t b_base = umma_desc(acts_s, 16 * NPAD, 128);
-                const uint32_t d_lo = tmem_base + (uint32_t)(a * 4 + 0) * NPAD, d_hi = d_lo + NPAD;
-                const uint32_t d_ml = d_lo + 2 * NPAD, d_mh = d_lo + 3 * NPAD;
-                bool gave_up = false;
+    } else if (warp == kMmaWarp) {
+        // ---------------- MMA issuer.  The whole warp walks the loop so that addresses, descriptors and
+        // ring counters stay warp-uniform (the MMA takes them from uniform registers); one elected lane issues.
+        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kAccCols >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+        const uint64_t b_desc0 = umma_desc(smem_addr(raw + kRowsBytes), 16 * NPAD, 128);
+        const uint32_t b_step = (uint32_t)p.raw_bytes >> 4;
+        int s = 0, o = 0;
+        uint32_t raw_par = 0;
+        bool gave_up = false;
+        for (int i = 0; i < total_sb && !gave_up; i++) {
+            if (!mbar_wait_bounded(&raw_full[s], raw_par, err, 12)) break;
+            if (!mbar_wait_bounded(&xf_full[i & 1], (uint32_t)(i >> 1) & 1u, err, 14)) break;
+            TC5_TRACE(5, i);
+            const int o1 = (o + 1 == kOpStages) ? 0 : o + 1;
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    const int h = 2 * i + half, o = h % kOpStages;
-                    if (!mbar_wait_bounded(&op_full[o], (h / kOpStages) & 1, err, 14)) { gave_up = true; break; }
-                    TC5_TRACE(5 + 2 * half, i);
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t a_base = umma_desc(smem_addr(ops + (size_t)o * kOpBytes), 2048, 128);
+            for (int pass = 0; pass < kPasses; pass++) {
+                // set and the parity of its release by the epilogue one use back
+                const int a = kPasses == 2 ? pass : (i & 1);
+                const int use = kPasses == 2 ? i : (i >> 1);
+                if (use >= 1 && !mbar_wait_bounded(&acc_empty[a], (uint32_t)(use - 1) & 1u, err, 13)) { gave_up = true; break; }
+                if (pass == 0) TC5_TRACE(9, i);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // the B descriptors differ only in their 14-bit start-address field (bytes >> 4); tokens
+                // 32.. of the second pass start four 128-byte core matrices further on
+                const uint64_t b_base = b_desc0 + (uint64_t)((uint32_t)s * b_step + (uint32_t)pass * (4u * 128u >> 4));
+                const uint32_t d_lo = tmem_base + (uint32_t)(a * 4) * kAccCols, d_hi = d_lo + kAccCols;
+                const uint32_t d_ml = d_lo + 2 * kAccCols, d_mh = d_lo + 3 * kAccCols;
+                if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const int j = 4 * half + k;   // sub-block: K-chunks 2j, 2j+1 of the B operand
-                        const uint64_t bdesc = b_base + (uint64_t)((2 * j * 16 * NPAD) >> 4);
-                        const uint32_t accum = (half | k) ? 1u : 0u;
-                        umma_i8(d_lo, a_base + (uint64_t)((2 * k * 2048) >> 4), bdesc, idesc, accum);
-                        umma_i8(d_hi, a_base + (uint64_t)((kPlaneBytes + 2 * k * 2048) >> 4), bdesc, idesc, accum);
+                    for (int half = 0; half < 2; half++) {
+                        const int oh = half ? o1 : o;
+                        const uint32_t a_lo = tmem_base + kColOps + (uint32_t)oh * kOpCols, a_hi = a_lo + 32;
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const int j = 4 * half + k;   // sub-block: K-chunks 2j, 2j+1 of the B operand
+                            const uint64_t bdesc = b_base + (uint64_t)((2 * j * 16 * NPAD) >> 4);
+                            if (half == 0 && k == 0) {
+                                umma_i8_ts<0>(d_lo, a_lo, bdesc, idesc);
+                                umma_i8_ts<0>(d_hi, a_hi, bdesc, idesc);
+                            } else {
+                                umma_i8_ts<1>(d_lo, a_lo + 8 * k, bdesc, idesc);
+                                umma_i8_ts<1>(d_hi, a_hi + 8 * k, bdesc, idesc);
+                            }
+                        }
+                        if (half == 1) {
+                            const uint32_t a_mn = tmem_base + kColMins + (uint32_t)(i & 1) * kMinCols;
+                            umma_i8_ts<0>(d_ml, a_mn, b_base + (uint64_t)((256 * NPAD) >> 4), idesc);
+                            umma_i8_ts<0>(d_mh, a_mn, b_base + (uint64_t)((288 * NPAD) >> 4), idesc);
+                        }
+                        if (pass == kPasses - 1) umma_commit(&op_empty[oh]);
                     }
-                    if (half == 1) {
-                        const uint64_t mdesc = a_base + (uint64_t)((2 * kPlaneBytes) >> 4);
-                        umma_i8(d_ml, mdesc, b_base + (uint64_t)((256 * NPAD) >> 4), idesc, 0u);
-                        umma_i8(d_mh, mdesc, b_base + (uint64_t)((288 * NPAD) >> 4), idesc, 0u);
-                    }
-                    umma_commit(&op_empty[o]);
-                    TC5_TRACE(6 + 2 * half, i);
+                    if (pass == kPasses - 1) umma_commit(&raw_empty[s]);
+                    umma_commit(&acc_full[a]);
                 }
-                if (gave_up) break;
-                umma_commit(&raw_empty[s]);
-                umma_commit(&acc_full[a]);
-                TC5_TRACE(2, i);
+                __syncwarp();
             }
+            TC5_TRACE(2, i);
+            o = (o1 + 1 == kOpStages) ? 0 : o1 + 1;
+            if (++s == kRawStages) { s = 0; raw_par ^= 1u; }
         }
     } else if (warp < kTransformWarps) {
-        // ---------------- transform: threads r and 128 + r share row r of the tile (sub-blocks 2*part, 2*part+1 of each half)
-        const int r = tid & 127, part = tid >> 7;
-        for (int i = 0; i < total_sb; i++) {
-            const int s = i % kRawStages;
-            if (!mbar_wait_sleepy(&raw_full[s], (i / kRawStages) & 1, err, 15)) break;
-            if (tid == 0) TC5_TRACE(1, i);
+        // ---------------- transform: two threads share row r of the tile (kSubs sub-blocks each per half);
+        // warp w may touch TMEM lanes 32*(w%4)..+31, which are its rows
+        const int group = warp >> 3, part = (warp >> 2) & 1;
+        const int r = 32 * (warp & 3) + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp & 3)) << 16);
+        int s = group, o = (2 * group) % kOpStages;
+        uint32_t raw_par = 0, op_par = 1;   // op_par: parity of the issuer's release one round of stages back
+        for (int i = group; i < total_sb; i += kGroups) {
+            if (!mbar_wait_sleepy(&raw_full[s], raw_par, err, 15)) break;
+            if ((tid & 255) == 0) TC5_TRACE(1, i);
+            // both A stages of this super-block must be free
+            const int o1 = (o + 1 == kOpStages) ? 0 : o + 1;
+            const uint32_t op_par1 = (o + 1 == kOpStages) ? op_par ^ 1u : op_par;
+            // (the issuer commits in order: the release of the second stage implies that of the first)
+            if (2 * i + 1 >= kOpStages && !mbar_wait_sleepy(&op_empty[o1], op_par1, err, 16)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint8_t* slot = raw + (size_t)s * p.raw_bytes;
             const uint8_t* row = slot + (size_t)r * BPDQ_Q4K_BYTES;
             const uint4 hdr = *reinterpret_cast<const uint4*>(row);
+            uint4 qv[2][kSubs];
+#pragma unroll
+            for (int half = 0; half < 2; half++)
+#pragma unroll
+                for (int kk = 0; kk < kSubs; kk++)
+                    qv[half][kk] = *reinterpret_cast<const uint4*>(row + 16 + 64 * half + 16 * (kSubs * part + kk));
             float* sd = side + (size_t)(i % kSideSlots) * kSideFloats;
             if (part == 0) {
-                sd[2 * r] = f16_bits_to_f32(hdr.x & 0xFFFFu);
-                sd[2 * r + 1] = f16_bits_to_f32(hdr.x >> 16);
-            } else if (r < NPAD) {
+                *reinterpret_cast<float2*>(sd + 2 * r) = make_float2(f16_bits_to_f32(hdr.x & 0xFFFFu), f16_bits_to_f32(hdr.x >> 16));
+            } else if (part == 1 && r < NPAD) {
                 sd[256 + r] = reinterpret_cast<const float*>(slot + kRowsBytes + 320 * NPAD)[r];
             }
-            bool gave_up = false;
-            for (int half = 0; half < 2; half++) {
-                const int h = 2 * i + half, o = h % kOpStages;
-                if (h >= kOpStages && !mbar_wait_sleepy(&op_empty[o], ((h / kOpStages) - 1) & 1, err, 16)) { gave_up = true; break; }
-                uint8_t* op = ops + (size_t)o * kOpBytes;
-                uint8_t* dst = op + (r >> 3) * 128 + (r & 7) * 16;     // this row's 16 bytes inside every core matrix
-                uint32_t sc4, mn4;
-                q4k_scales4(hdr.y, hdr.z, hdr.w, half, sc4, mn4);
-                const uint4* qs = reinterpret_cast<const uint4*>(row + 16 + 64 * half);
 #pragma unroll
-                for (int kk = 0; kk < 2; kk++) {
-                    const int k = 2 * part + kk;
-                    const uint4 qv = qs[k];
-                    const uint32_t sc = byte_of(sc4, k), sl = sc & 7u, sh = sc >> 3;
-                    const uint32_t l0 = qv.x & 0x0F0F0F0Fu, l1 = qv.y & 0x0F0F0F0Fu, l2 = qv.z & 0x0F0F0F0Fu, l3 = qv.w & 0x0F0F0F0Fu;
-                    const uint32_t h0 = (qv.x >> 4) & 0x0F0F0F0Fu, h1 = (qv.y >> 4) & 0x0F0F0F0Fu, h2 = (qv.z >> 4) & 0x0F0F0F0Fu,
-                                   h3 = (qv.w >> 4) & 0x0F0F0F0Fu;
-                    // K-chunk 2k = elements 0..15 of the sub-block (low nibbles), 2k+1 = elements 16..31 (high)
-                    *reinterpret_cast<uint4*>(dst + (2 * k) * 2048) = make_uint4(l0 * sl, l1 * sl, l2 * sl, l3 * sl);
-                    *reinterpret_cast<uint4*>(dst + (2 * k + 1) * 2048) = make_uint4(h0 * sl, h1 * sl, h2 * sl, h3 * sl);
-                    *reinterpret_cast<uint4*>(dst + kPlaneBytes + (2 * k) * 2048) = make_uint4(l0 * sh, l1 * sh, l2 * sh, l3 * sh);
-                    *reinterpret_cast<uint4*>(dst + kPlaneBytes + (2 * k + 1) * 2048) = make_uint4(h0 * sh, h1 * sh, h2 * sh, h3 * sh);
+            for (int half = 0; half < 2; half++) {
+                uint32_t lo[8 * kSubs], hi[8 * kSubs];
+                uint32_t sc4 = 0;
+                if (kSubs > 1) {
+                    uint32_t mn4;
+                    q4k_scales4(hdr.y, hdr.z, hdr.w, half, sc4, mn4);
                 }
-                if (half == 1 && part == 1) {
-                    uint32_t sca, mna;
-                    q4k_scales4(hdr.y, hdr.z, hdr.w, 0, sca, mna);
-                    *reinterpret_cast<uint4*>(dst + 2 * kPlaneBytes) = make_uint4(mna, mn4, 0, 0);    // mins of sub-blocks 0..7
-                    *reinterpret_cast<uint4*>(dst + 2 * kPlaneBytes + 2048) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int kk = 0; kk < kSubs; kk++) {
+                    const int k = kSubs * part + kk;
+                    const uint4 q = qv[half][kk];
+                    uint32_t sc;
+                    if (kSubs > 1) {
+                        sc = byte_of(sc4, k);
+                    } else {
+                        // the one 6-bit scale of sub-block 4*half + part: byte `part` of the scale words
+                        const uint32_t y = hdr.y >> (8 * part);
+                        sc = half == 0 ? (y & 63u) : (((hdr.w >> (8 * part)) & 0xFu) | ((y >> 2) & 0x30u));
+                    }
+                    const uint32_t sl = sc & 7u, sh = sc >> 3;
+                    const uint32_t l0 = q.x & 0x0F0F0F0Fu, l1 = q.y & 0x0F0F0F0Fu, l2 = q.z & 0x0F0F0F0Fu, l3 = q.w & 0x0F0F0F0Fu;
+                    const uint32_t h0 = (q.x >> 4) & 0x0F0F0F0Fu, h1 = (q.y >> 4) & 0x0F0F0F0Fu, h2 = (q.z >> 4) & 0x0F0F0F0Fu,
+                                   h3 = (q.w >> 4) & 0x0F0F0F0Fu;
+                    // columns 0..3 of a K=32 step = elements 0..15 of the sub-block (low nibbles), 4..7 = elements 16..31 (high)
+                    lo[8 * kk + 0] = l0 * sl; lo[8 * kk + 1] = l1 * sl; lo[8 * kk + 2] = l2 * sl; lo[8 * kk + 3] = l3 * sl;
+                    lo[8 * kk + 4] = h0 * sl; lo[8 * kk + 5] = h1 * sl; lo[8 * kk + 6] = h2 * sl; lo[8 * kk + 7] = h3 * sl;
+                    hi[8 * kk + 0] = l0 * sh; hi[8 * kk + 1] = l1 * sh; hi[8 * kk + 2] = l2 * sh; hi[8 * kk + 3] = l3 * sh;
+                    hi[8 * kk + 4] = h0 * sh; hi[8 * kk + 5] = h1 * sh; hi[8 * kk + 6] = h2 * sh; hi[8 * kk + 7] = h3 * sh;
                 }
-                // make the generic-proxy writes visible to the tensor core's reads, then publish
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&op_full[o]);
+                const uint32_t a_lo = lane_base + kColOps + (uint32_t)(half ? o1 : o) * kOpCols + (uint32_t)(8 * kSubs) * (uint32_t)part;
+                tmem_st(a_lo, lo);
+                tmem_st(a_lo + 32, hi);
             }
-            if (gave_up) break;
+            op_par = op_par1;
+            o = o1;
+#pragma unroll
+            for (int q = 0; q < 2 * kGroups - 1; q++)
+                if (++o == kOpStages) { o = 0; op_par ^= 1u; }
+            if (part == kParts - 1) {
+                uint32_t sca, mna, scb, mnb;
+                q4k_scales4(hdr.y, hdr.z, hdr.w, 0, sca, mna);
+                q4k_scales4(hdr.y, hdr.z, hdr.w, 1, scb, mnb);
+                const uint32_t mins[8] = {mna, mnb, 0, 0, 0, 0, 0, 0};    // mins of sub-blocks 0..7, then zero K padding
+                tmem_st(lane_base + kColMins + (uint32_t)(i & 1) * kMinCols, mins);
+            }
+            // the stores must have landed before the issuer's MMAs may read them
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(&raw_empty[s]);
-            if (tid == 0) TC5_TRACE(3, i);
+            if (lane == 0) mbar_arrive(&xf_full[i & 1]);
+            if ((tid & 255) == 0) TC5_TRACE(3, i);
+            s += kGroups;
+            if (s >= kRawStages) { s -= kRawStages; raw_par ^= 1u; }
         }
     } else {
-        // ---------------- epilogue: thread r owns TMEM lane r and output row tile*128 + r
-        const int r = tid - 32 * kTransformWarps;
-        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (warp - kTransformWarps)) << 16);
-        float facc[NPAD];
+        // ---------------- epilogue: a thread owns one TMEM lane (output row) and kEpiCols token columns
+        const int e = warp - kTransformWarps, pass = e >> 2;
+        const int r = 32 * (e & 3) + lane, c0 = pass * kEpiCols;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (e & 3)) << 16);
+        float facc[kEpiCols];
         int i = 0;
         for (int tl = 0; tl < my_tiles; tl++) {
 #pragma unroll
-            for (int t = 0; t < NPAD; t++) facc[t] = 0.0f;
+            for (int t = 0; t < kEpiCols; t++) facc[t] = 0.0f;
             bool gave_up = false;
             for (int b = 0; b < p.nb; b++, i++) {
-                const int a = i & 1;
-                if (!mbar_wait_sleepy(&acc_full[a], (i >> 1) & 1, err, 17)) { gave_up = true; break; }
+                const int a = kPasses == 2 ? pass : (i & 1);
+                const int use = kPasses == 2 ? i : (i >> 1);
+                if (!mbar_wait_sleepy(&acc_full[a], (uint32_t)use & 1u, err, 17)) { gave_up = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float* sd = side + (size_t)(i % kSideSlots) * kSideFloats;
-                const float d = sd[2 * r], dmin = sd[2 * r + 1];
-                const uint32_t col0 = lane_base + (uint32_t)(a * 4) * NPAD;
+                const float2 dd = *reinterpret_cast<const float2*>(sd + 2 * r);
+                const float d = dd.x, dmin = dd.y;
+                const uint32_t col0 = lane_base + (uint32_t)(a * 4) * kAccCols;
 #pragma unroll
-                for (int c = 0; c < NPAD / 16; c++) {
-                    int lo[16], hi[16], ml[16], mh[16];
-                    tmem_ld16(col0 + 16 * c, lo);
-                    tmem_ld16(col0 + NPAD + 16 * c, hi);
-                    tmem_ld16(col0 + 2 * NPAD + 16 * c, ml);
-                    tmem_ld16(col0 + 3 * NPAD + 16 * c, mh);
+                for (int c = 0; c < kEpiCols / 8; c++) {
+                    int lo[8], hi[8], ml[8], mh[8];
+                    tmem_ld(col0 + 8 * c, lo);
+                    tmem_ld(col0 + kAccCols + 8 * c, hi);
+                    tmem_ld(col0 + 2 * kAccCols + 8 * c, ml);
+                    tmem_ld(col0 + 3 * kAccCols + 8 * c, mh);
+                    const float4 dA0 = *reinterpret_cast<const float4*>(sd + 256 + c0 + 8 * c);
+                    const float4 dA1 = *reinterpret_cast<const float4*>(sd + 256 + c0 + 8 * c + 4);
+                    const float dA[8] = {dA0.x, dA0.y, dA0.z, dA0.w, dA1.x, dA1.y, dA1.z, dA1.w};
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                    for (int t = 0; t < 16; t++) {
+                    for (int t = 0; t < 8; t++) {
                         const float v = d * (float)(8 * hi[t] + lo[t]) - dmin * (float)(64 * mh[t] + ml[t]);
-                        facc[16 * c + t] = fmaf(sd[256 + 16 * c + t], v, facc[16 * c + t]);
+                        facc[8 * c + t] = fmaf(dA[t], v, facc[8 * c + t]);
                     }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&acc_empty[a]);
-                if (r == 0) TC5_TRACE(4, i);
+                if (tid == 32 * kTransformWarps) TC5_TRACE(4, i);
             }
             if (gave_up) break;
             const int rowg = (blockIdx.x + tl * gridDim.x) * kRows + r;
             if (rowg < p.N) {
 #pragma unroll
-                for (int t = 0; t < NPAD; t++)
-                    if (t < p.tokens) out[(size_t)t * p.N + rowg] = facc[t];
+                for (int t = 0; t < kEpiCols; t++)
+                    if (c0 + t < p.tokens) out[(size_t)(c0 + t) * p.N + rowg] = facc[t];
             }
         }
     }
     // ---------------- teardown: everybody meets, then the allocating warp frees tensor memory
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 13) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
@@ -435,7 +549,7 @@ static int launch_tc5(const CUtensorMap& wmap, const uint8_t* acts, float* out, 
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.grid);
-    cfg.blockDim = dim3(448);
+    cfg.blockDim = dim3(Tc5Shape<NPAD>::kThreads);
     cfg.dynamicSmemBytes = p.smem;
     cfg.stream = s;
     cudaLaunchAttribute at[1];
@@ -471,12 +585,11 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
         p.raw_bytes = (kRowsBytes + p.act_bytes + 127) / 128 * 128;
         size_t off = 0;
         auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
-        const size_t fixed = (size_t)kOpStages * kOpBytes + ((size_t)kSideSlots * (256 + p.npad) * 4 + 127) / 128 * 128 + 256;
+        const size_t fixed = ((size_t)kSideSlots * (256 + p.npad) * 4 + 127) / 128 * 128 + 256;
         p.raw_stages = (int)((227 * 1024 - fixed) / p.raw_bytes);
         if (p.raw_stages > kMaxRawStages) p.raw_stages = kMaxRawStages;
         if (p.raw_stages < 2) return latch(BPDQ_ERR_RANGE);
         p.off_raw = take((size_t)p.raw_stages * p.raw_bytes);
-        p.off_op = take((size_t)kOpStages * kOpBytes);
         p.off_side = take((size_t)kSideSlots * (256 + p.npad) * 4);
         p.off_bar = take(256);
         p.smem = off;
