@@ -45,6 +45,9 @@ constexpr int kRowsBytes = kRows * BPDQ_Q4K_BYTES; // 18432
 struct Tc5Plan {
     int N, nb, tokens, npad;      // weight rows, super-blocks per row, valid / padded tokens (16, 32 or 64)
     int n_tiles, grid, raw_stages;
+    int splits, sb_per_unit, n_units;   // K is cut into `splits` ranges of sb_per_unit super-blocks; unit = (tile, range)
+    float* partials;              // [splits][tokens][N] fp32, used when splits > 1
+    unsigned* arrivals;           // [n_tiles][2] units of a tile (and token half) that have stored their partial
     int act_bytes;                // scratch bytes per super-block: 324 * npad
     int raw_bytes;                // ring slot: rows + activations
     int off_raw, off_side, off_bar;
@@ -138,8 +141,11 @@ __device__ __forceinline__ void tma_rows_2d(void* dst_smem, const CUtensorMap* m
 //   [32*npad]  bl plane, [32*npad] bh plane (K = 32 bytes per token, bytes 0..7 = sub-blocks 0..7, rest 0)
 //   [4*npad]   fp32 block scales
 __global__ void __launch_bounds__(256) k_quant_tc5_acts(const float* __restrict__ X, uint8_t* __restrict__ scratch,
-                                                        int tokens, int npad, int K)
+                                                        int tokens, int npad, int K, unsigned* __restrict__ arrivals,
+                                                        int n_arrivals)
 {
+    // the split-K arrival counters of the product that follows start at zero
+    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < n_arrivals; q += gridDim.x * blockDim.x) arrivals[q] = 0u;
     const int nb = K / 256;
     const int lane = threadIdx.x & 31;
     const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -265,13 +271,14 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     pdl_launch_dependents();
     pdl_wait();   // the activations in scratch come from the quantizer launched just before
 
-    const int my_tiles = (p.n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int total_sb = my_tiles * p.nb;       // super-blocks this CTA walks, over all its tiles
+    const int my_units = (p.n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total_sb = my_units * p.sb_per_unit;   // super-blocks this CTA walks, over all its units
 
     if (warp == kProducerWarp) {
         // ---------------- producer
         if (lane == 0) {
-            int s = 0, b = 0, tile = blockIdx.x;
+            int s = 0, q = 0, unit = blockIdx.x;
+            int tile = unit / p.splits, b = (unit - tile * p.splits) * p.sb_per_unit;
             uint32_t par = 1;   // parity of the consumers' release one round of stages back
             for (int i = 0; i < total_sb; i++) {
                 if (i >= kRawStages && !mbar_wait_sleepy(&raw_empty[s], par, err, 11)) break;
@@ -281,7 +288,13 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                 bulk_g2s(slot + kRowsBytes, acts + (size_t)b * p.act_bytes, (uint32_t)p.act_bytes, &raw_full[s]);
                 TC5_TRACE(0, i);
                 if (++s == kRawStages) { s = 0; par ^= 1u; }
-                if (++b == p.nb) { b = 0; tile += gridDim.x; }
+                b++;
+                if (++q == p.sb_per_unit) {
+                    q = 0;
+                    unit += gridDim.x;
+                    tile = unit / p.splits;
+                    b = (unit - tile * p.splits) * p.sb_per_unit;
+                }
             }
         }
     } else if (warp == kMmaWarp) {
@@ -438,11 +451,12 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
         const uint32_t lane_base = tmem_base + ((uint32_t)(32 * (e & 3)) << 16);
         float facc[kEpiCols];
         int i = 0;
-        for (int tl = 0; tl < my_tiles; tl++) {
+        int* last_flag = reinterpret_cast<int*>(tmem_slot + 2) + pass;
+        for (int ul = 0; ul < my_units; ul++) {
 #pragma unroll
             for (int t = 0; t < kEpiCols; t++) facc[t] = 0.0f;
             bool gave_up = false;
-            for (int b = 0; b < p.nb; b++, i++) {
+            for (int b = 0; b < p.sb_per_unit; b++, i++) {
                 const int a = kPasses == 2 ? pass : (i & 1);
                 const int use = kPasses == 2 ? i : (i >> 1);
                 if (!mbar_wait_sleepy(&acc_full[a], (uint32_t)use & 1u, err, 17)) { gave_up = true; break; }
@@ -474,11 +488,57 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                 if (tid == 32 * kTransformWarps) TC5_TRACE(4, i);
             }
             if (gave_up) break;
-            const int rowg = (blockIdx.x + tl * gridDim.x) * kRows + r;
-            if (rowg < p.N) {
+            const int unit = blockIdx.x + ul * gridDim.x;
+            const int tile = unit / p.splits, split = unit - tile * p.splits;
+            const int rowg = tile * kRows + r;
+            if (p.splits == 1) {
+                if (rowg < p.N) {
 #pragma unroll
-                for (int t = 0; t < kEpiCols; t++)
-                    if (c0 + t < p.tokens) out[(size_t)(c0 + t) * p.N + rowg] = facc[t];
+                    for (int t = 0; t < kEpiCols; t++)
+                        if (c0 + t < p.tokens) out[(size_t)(c0 + t) * p.N + rowg] = facc[t];
+                }
+            } else {
+                // split K: store this range's partial sums; the unit that arrives last adds the ranges in
+                // their fixed order 0, 1, ..., so the result does not depend on which one that was
+                if (rowg < p.N) {
+#pragma unroll
+                    for (int t = 0; t < kEpiCols; t++)
+                        if (c0 + t < p.tokens) __stcg(p.partials + ((size_t)split * p.tokens + (c0 + t)) * p.N + rowg, facc[t]);
+                }
+                __threadfence();
+                named_bar_sync(1 + pass, 128);
+                if ((e & 3) == 0 && lane == 0) {
+                    const unsigned before = atomicAdd(p.arrivals + 2 * tile + pass, 1u);
+                    *last_flag = (before == (unsigned)p.splits - 1u) ? 1 : 0;
+                }
+                named_bar_sync(1 + pass, 128);
+                const bool last = *last_flag != 0;
+                named_bar_sync(1 + pass, 128);   // everybody has read the flag before the next unit rewrites it
+                if (last) {
+                    __threadfence();
+                    if (rowg < p.N) {
+                        // four tokens x up to eight ranges of loads in flight, then the sums in range order
+#pragma unroll 1
+                        for (int t0 = 0; t0 < kEpiCols && c0 + t0 < p.tokens; t0 += 4) {
+                            float v[4][8];
+#pragma unroll
+                            for (int tt = 0; tt < 4; tt++)
+#pragma unroll
+                                for (int q = 0; q < 8; q++)
+                                    v[tt][q] = (q < p.splits && c0 + t0 + tt < p.tokens)
+                                                   ? __ldcg(p.partials + ((size_t)q * p.tokens + (c0 + t0 + tt)) * p.N + rowg)
+                                                   : 0.0f;
+#pragma unroll
+                            for (int tt = 0; tt < 4; tt++) {
+                                float sum = 0.0f;
+#pragma unroll
+                                for (int q = 0; q < 8; q++)
+                                    if (q < p.splits) sum += v[tt][q];
+                                if (c0 + t0 + tt < p.tokens) out[(size_t)(c0 + t0 + tt) * p.N + rowg] = sum;
+                            }
+                        }
+                    }
+                }
             }
         }
     }
@@ -493,12 +553,15 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
 
 static unsigned long long* g_tc5_trace = nullptr;
 
-static uint8_t* tc5_scratch(size_t bytes)
+// Per-device grow-only buffers: slot 0 = quantized activations, slot 1 = split-K partial sums and arrival counters.
+static uint8_t* tc5_scratch(int slot, size_t bytes)
 {
-    static uint8_t* buf[64] = {nullptr};
-    static size_t cap[64] = {0};
+    static uint8_t* bufs[2][64] = {{nullptr}};
+    static size_t caps[2][64] = {{0}};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    uint8_t** buf = bufs[slot];
+    size_t* cap = caps[slot];
     if (cap[dev] < bytes) {
         if (buf[dev]) {
             cudaDeviceSynchronize();
@@ -580,7 +643,23 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
         p.trace = g_tc5_trace;
         p.npad = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
         p.n_tiles = (N + kRows - 1) / kRows;
-        p.grid = p.n_tiles < sm_count() ? p.n_tiles : sm_count();
+        // Split K so that every SM has work and the per-CTA chain of super-blocks is short: pick the
+        // number of ranges (a power of two dividing the super-blocks per row, at least two per range)
+        // with the fewest super-block steps on the busiest SM, charging each unit two steps of set-up.
+        p.splits = 1;
+        {
+            long best = -1;
+            for (int sp = 1; sp <= 8; sp *= 2) {
+                if (p.nb % sp != 0 || p.nb / sp < 2) break;
+                const long units = (long)p.n_tiles * sp;
+                const long waves = (units + sm_count() - 1) / sm_count();
+                const long cost = waves * (p.nb / sp + 2);
+                if (best < 0 || cost < best) { best = cost; p.splits = sp; }
+            }
+        }
+        p.sb_per_unit = p.nb / p.splits;
+        p.n_units = p.n_tiles * p.splits;
+        p.grid = p.n_units < sm_count() ? p.n_units : sm_count();
         p.act_bytes = 324 * p.npad;
         p.raw_bytes = (kRowsBytes + p.act_bytes + 127) / 128 * 128;
         size_t off = 0;
@@ -594,11 +673,17 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
         p.off_bar = take(256);
         p.smem = off;
         if (p.smem > 227 * 1024) return latch(BPDQ_ERR_RANGE);
-        uint8_t* acts = tc5_scratch((size_t)p.nb * p.act_bytes);
+        uint8_t* acts = tc5_scratch(0, (size_t)p.nb * p.act_bytes);
         if (!acts) return latch(BPDQ_ERR_CUDA);
+        const size_t arrivals_bytes = ((size_t)p.n_tiles * 2 * sizeof(unsigned) + 255) / 256 * 256;
+        uint8_t* red = tc5_scratch(1, arrivals_bytes + (p.splits > 1 ? (size_t)p.splits * T * N * sizeof(float) : 0));
+        if (!red) return latch(BPDQ_ERR_CUDA);
+        p.arrivals = reinterpret_cast<unsigned*>(red);
+        p.partials = reinterpret_cast<float*>(red + arrivals_bytes);
         const long units = (long)p.nb * p.npad;
         long want = (units + 7) / 8, cap = (long)sm_count() * 8;
-        k_quant_tc5_acts<<<(int)(want < cap ? want : cap), 256, 0, s>>>(X + (size_t)t0 * K, acts, T, p.npad, K);
+        k_quant_tc5_acts<<<(int)(want < cap ? want : cap), 256, 0, s>>>(X + (size_t)t0 * K, acts, T, p.npad, K, p.arrivals,
+                                                                        p.n_tiles * 2);
         rc = check_cuda(cudaGetLastError());
         if (rc) return rc;
         float* o = out + (size_t)t0 * N;
