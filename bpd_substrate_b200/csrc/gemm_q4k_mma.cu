@@ -56,6 +56,11 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint
 __global__ void __launch_bounds__(256) k_quant_gemm_acts(const float* __restrict__ X, uint8_t* __restrict__ scratch,
                                                          int tokens, int tok_pad, int K)
 {
+    // Programmatic launch on both sides: the product's CTAs may set up while this kernel runs, and this
+    // kernel is resident before the launch ahead of it has finished, which it waits for here because
+    // that launch may produce X and may still read the scratch.
+    pdl_launch_dependents();
+    pdl_wait();
     const int nb = K / 256;
     const int lane = threadIdx.x & 31;
     const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -382,9 +387,20 @@ int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, i
         if (!acts) return latch(BPDQ_ERR_CUDA);
         const long units = (long)p.nb * p.tok_pad;
         long want = (units + 7) / 8, cap = (long)sm_count() * 8;
-        k_quant_gemm_acts<<<(int)(want < cap ? want : cap), 256, 0, s>>>(X + (size_t)t0 * K, acts, T, p.tok_pad, K);
-        int rc = check_cuda(cudaGetLastError());
-        if (rc) return rc;
+        int rc;
+        {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(want < cap ? want : cap));
+            cfg.blockDim = dim3(256);
+            cfg.stream = s;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = tuning().pdl ? 1 : 0;
+            rc = check_cuda(cudaLaunchKernelEx(&cfg, k_quant_gemm_acts, (const float*)(X + (size_t)t0 * K), acts, T, p.tok_pad, K));
+            if (rc) return rc;
+        }
         float* o = out + (size_t)t0 * N;
         rc = nt == 1 ? launch_gemm<1>(W, acts, o, p, s) : (nt == 2 ? launch_gemm<2>(W, acts, o, p, s) : launch_gemm<4>(W, acts, o, p, s));
         if (rc) return latch(rc);

@@ -144,6 +144,11 @@ __global__ void __launch_bounds__(256) k_quant_tc5_acts(const float* __restrict_
                                                         int tokens, int npad, int K, unsigned* __restrict__ arrivals,
                                                         int n_arrivals)
 {
+    // Programmatic launch on both sides: the product's CTAs may start their weight loads while this
+    // kernel runs, and this kernel is resident before the launch ahead of it has finished, which it
+    // waits for here because that launch may produce X and may still read the scratch.
+    pdl_launch_dependents();
+    pdl_wait();
     // the split-K arrival counters of the product that follows start at zero
     for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < n_arrivals; q += gridDim.x * blockDim.x) arrivals[q] = 0u;
     const int nb = K / 256;
@@ -243,20 +248,21 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     float* side = reinterpret_cast<float*>(smem + p.off_side);   // [kSideSlots][256 hdr floats + NPAD dA floats]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.off_bar);
     const int kRawStages = p.raw_stages;
-    uint64_t* raw_full = bars;                       // [raw_stages] producer's expect_tx + bytes
-    uint64_t* raw_empty = raw_full + kMaxRawStages;  // MMA commit (its MMAs follow the transform's reads of the slot)
+    uint64_t* w_full = bars;                         // [raw_stages] weight rows of a slot have landed (TMA bytes)
+    uint64_t* a_full = w_full + kMaxRawStages;       // [raw_stages] activation block of a slot has landed
+    uint64_t* raw_empty = a_full + kMaxRawStages;    // MMA commit (its MMAs follow the transform's reads of the slot)
     uint64_t* xf_full = raw_empty + kMaxRawStages;   // [2] by super-block parity: the eight warps of a transform group
     uint64_t* op_empty = xf_full + 2;                // [kOpStages] MMA commit
-    uint64_t* acc_full = op_empty + kMaxOpStages;    // [kAccSets] MMA commit
+    uint64_t* acc_full = op_empty + kMaxOpStages;    // [kAccSets] MMA commit + the issuer's arrival after it wrote the token scales
     uint64_t* acc_empty = acc_full + 2;              // epilogue warps
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     constexpr int kSideFloats = 256 + NPAD;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
-        for (int s = 0; s < kMaxRawStages; s++) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 1); }
+        for (int s = 0; s < kMaxRawStages; s++) { mbar_init(&w_full[s], 1); mbar_init(&a_full[s], 1); mbar_init(&raw_empty[s], 1); }
         for (int s = 0; s < kMaxOpStages; s++) mbar_init(&op_empty[s], 1);
-        for (int s = 0; s < 2; s++) { mbar_init(&xf_full[s], 8); mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+        for (int s = 0; s < 2; s++) { mbar_init(&xf_full[s], 8); mbar_init(&acc_full[s], 2); mbar_init(&acc_empty[s], 4); }
         mbar_init_fence();
     }
     if (warp == kMmaWarp) {
@@ -269,7 +275,9 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
-    pdl_wait();   // the activations in scratch come from the quantizer launched just before
+    // Everything up to here, the weight loads of the first ring round and their transform overlap the
+    // activation quantizer launched just before this kernel: only what that kernel wrote (the
+    // activation blocks, the split-K counters) waits for it, in the producer and the epilogue warps.
 
     const int my_units = (p.n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int total_sb = my_units * p.sb_per_unit;   // super-blocks this CTA walks, over all its units
@@ -277,24 +285,43 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     if (warp == kProducerWarp) {
         // ---------------- producer
         if (lane == 0) {
-            int s = 0, q = 0, unit = blockIdx.x;
-            int tile = unit / p.splits, b = (unit - tile * p.splits) * p.sb_per_unit;
+            // two walks over the same sequence of (tile, super-block): weights may run ahead of the
+            // activations by the ring's depth, and do so before the quantizer has finished
+            struct Walk { int q, unit, tile, b; };
+            auto start = [&]() { Walk w; w.q = 0; w.unit = blockIdx.x; w.tile = w.unit / p.splits; w.b = (w.unit - w.tile * p.splits) * p.sb_per_unit; return w; };
+            auto step = [&](Walk& w) {
+                w.b++;
+                if (++w.q == p.sb_per_unit) {
+                    w.q = 0;
+                    w.unit += gridDim.x;
+                    w.tile = w.unit / p.splits;
+                    w.b = (w.unit - w.tile * p.splits) * p.sb_per_unit;
+                }
+            };
+            Walk ww = start(), wa = start();
+            const int ahead = total_sb < kRawStages ? total_sb : kRawStages;
+            for (int i = 0; i < ahead; i++) {
+                mbar_expect_tx(&w_full[i], (uint32_t)kRowsBytes);
+                tma_rows_2d(raw + (size_t)i * p.raw_bytes, &wmap, ww.b * (BPDQ_Q4K_BYTES / 4), ww.tile * kRows, &w_full[i]);
+                TC5_TRACE(0, i);
+                step(ww);
+            }
+            pdl_wait();
+            int s = 0;
             uint32_t par = 1;   // parity of the consumers' release one round of stages back
             for (int i = 0; i < total_sb; i++) {
-                if (i >= kRawStages && !mbar_wait_sleepy(&raw_empty[s], par, err, 11)) break;
                 uint8_t* slot = raw + (size_t)s * p.raw_bytes;
-                mbar_expect_tx(&raw_full[s], (uint32_t)(kRowsBytes + p.act_bytes));
-                tma_rows_2d(slot, &wmap, b * (BPDQ_Q4K_BYTES / 4), tile * kRows, &raw_full[s]);
-                bulk_g2s(slot + kRowsBytes, acts + (size_t)b * p.act_bytes, (uint32_t)p.act_bytes, &raw_full[s]);
-                TC5_TRACE(0, i);
-                if (++s == kRawStages) { s = 0; par ^= 1u; }
-                b++;
-                if (++q == p.sb_per_unit) {
-                    q = 0;
-                    unit += gridDim.x;
-                    tile = unit / p.splits;
-                    b = (unit - tile * p.splits) * p.sb_per_unit;
+                if (i >= kRawStages) {
+                    if (!mbar_wait_sleepy(&raw_empty[s], par, err, 11)) break;
+                    mbar_expect_tx(&w_full[s], (uint32_t)kRowsBytes);
+                    tma_rows_2d(slot, &wmap, ww.b * (BPDQ_Q4K_BYTES / 4), ww.tile * kRows, &w_full[s]);
+                    TC5_TRACE(0, i);
+                    step(ww);
                 }
+                mbar_expect_tx(&a_full[s], (uint32_t)p.act_bytes);
+                bulk_g2s(slot + kRowsBytes, acts + (size_t)wa.b * p.act_bytes, (uint32_t)p.act_bytes, &a_full[s]);
+                step(wa);
+                if (++s == kRawStages) { s = 0; par ^= 1u; }
             }
         }
     } else if (warp == kMmaWarp) {
@@ -307,8 +334,16 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
         uint32_t raw_par = 0;
         bool gave_up = false;
         for (int i = 0; i < total_sb && !gave_up; i++) {
-            if (!mbar_wait_bounded(&raw_full[s], raw_par, err, 12)) break;
+            if (!mbar_wait_bounded(&a_full[s], raw_par, err, 12)) break;
+            // the tokens' block scales go from the activation block to the side ring for the epilogue
+            {
+                const float* dA = reinterpret_cast<const float*>(raw + (size_t)s * p.raw_bytes + kRowsBytes + 320 * NPAD);
+                float* sd = side + (size_t)(i % kSideSlots) * kSideFloats + 256;
+#pragma unroll
+                for (int q = lane; q < NPAD; q += 32) sd[q] = dA[q];
+            }
             if (!mbar_wait_bounded(&xf_full[i & 1], (uint32_t)(i >> 1) & 1u, err, 14)) break;
+            __syncwarp();
             TC5_TRACE(5, i);
             const int o1 = (o + 1 == kOpStages) ? 0 : o + 1;
 #pragma unroll
@@ -318,6 +353,9 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                 const int use = kPasses == 2 ? i : (i >> 1);
                 if (use >= 1 && !mbar_wait_bounded(&acc_empty[a], (uint32_t)(use - 1) & 1u, err, 13)) { gave_up = true; break; }
                 if (pass == 0) TC5_TRACE(9, i);
+                // first of the two arrivals on acc_full: publishes the side ring's scales (and, through the
+                // transform's arrival seen above, its d/dmin) to the epilogue; the MMA commit is the second
+                if (lane == 0) mbar_arrive(&acc_full[a]);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // the B descriptors differ only in their 14-bit start-address field (bytes >> 4); tokens
                 // 32.. of the second pass start four 128-byte core matrices further on
@@ -366,7 +404,7 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
         int s = group, o = (2 * group) % kOpStages;
         uint32_t raw_par = 0, op_par = 1;   // op_par: parity of the issuer's release one round of stages back
         for (int i = group; i < total_sb; i += kGroups) {
-            if (!mbar_wait_sleepy(&raw_full[s], raw_par, err, 15)) break;
+            if (!mbar_wait_sleepy(&w_full[s], raw_par, err, 15)) break;
             if ((tid & 255) == 0) TC5_TRACE(1, i);
             // both A stages of this super-block must be free
             const int o1 = (o + 1 == kOpStages) ? 0 : o + 1;
@@ -384,11 +422,8 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                 for (int kk = 0; kk < kSubs; kk++)
                     qv[half][kk] = *reinterpret_cast<const uint4*>(row + 16 + 64 * half + 16 * (kSubs * part + kk));
             float* sd = side + (size_t)(i % kSideSlots) * kSideFloats;
-            if (part == 0) {
+            if (part == 0)
                 *reinterpret_cast<float2*>(sd + 2 * r) = make_float2(f16_bits_to_f32(hdr.x & 0xFFFFu), f16_bits_to_f32(hdr.x >> 16));
-            } else if (part == 1 && r < NPAD) {
-                sd[256 + r] = reinterpret_cast<const float*>(slot + kRowsBytes + 320 * NPAD)[r];
-            }
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 uint32_t lo[8 * kSubs], hi[8 * kSubs];
@@ -452,6 +487,7 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
         float facc[kEpiCols];
         int i = 0;
         int* last_flag = reinterpret_cast<int*>(tmem_slot + 2) + pass;
+        pdl_wait();   // the quantizer zeroed the split-K counters
         for (int ul = 0; ul < my_units; ul++) {
 #pragma unroll
             for (int t = 0; t < kEpiCols; t++) facc[t] = 0.0f;
@@ -682,10 +718,20 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
         p.partials = reinterpret_cast<float*>(red + arrivals_bytes);
         const long units = (long)p.nb * p.npad;
         long want = (units + 7) / 8, cap = (long)sm_count() * 8;
-        k_quant_tc5_acts<<<(int)(want < cap ? want : cap), 256, 0, s>>>(X + (size_t)t0 * K, acts, T, p.npad, K, p.arrivals,
-                                                                        p.n_tiles * 2);
-        rc = check_cuda(cudaGetLastError());
-        if (rc) return rc;
+        {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(want < cap ? want : cap));
+            cfg.blockDim = dim3(256);
+            cfg.stream = s;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = tuning().pdl ? 1 : 0;
+            rc = check_cuda(cudaLaunchKernelEx(&cfg, k_quant_tc5_acts, (const float*)(X + (size_t)t0 * K), acts, T, p.npad, K,
+                                               p.arrivals, p.n_tiles * 2));
+            if (rc) return rc;
+        }
         float* o = out + (size_t)t0 * N;
         rc = p.npad == 16 ? launch_tc5<16>(wmap, acts, o, p, s) : (p.npad == 32 ? launch_tc5<32>(wmap, acts, o, p, s) : launch_tc5<64>(wmap, acts, o, p, s));
         if (rc) return latch(rc);

@@ -721,9 +721,15 @@ int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M,
 {
     if (M < 0) return latch(BPDQ_ERR_ARG);
     // many tokens: the weights would be streamed once per four tokens here; the tensor-core
-    // kernel reads them once per 64
-    if (tokens > 4 && layout == BPDQ_LAYOUT_BPD && xsrc == 0 && !dbg)
+    // kernels read them once per 64.  Measured on 14336x4096, 4096x14336, 4096x4096 and 1024x4096:
+    // the tcgen05 kernel (128-row tiles, split K) is ahead from 24 tokens on matrices of 2^25
+    // weights and more (from 33 when there are fewer than 8192 rows), mma.sync everywhere else.
+    if (tokens > 4 && layout == BPDQ_LAYOUT_BPD && xsrc == 0 && !dbg) {
+        const bool large = (long)M * K >= (1L << 25);
+        if (large && (tokens >= 33 || (tokens >= 24 && M >= 8192)))
+            return gemm_q4k_q8k_tc5(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s);
         return gemm_q4k_q8k_mma(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s);
+    }
     return gemm_q4k_q8k_multi(1, &W, &out, &M, x, tokens, K, layout, xsrc, dbg, s);
 }
 
