@@ -1,6 +1,9 @@
 """Timings of the secondary configurations (the benchmark line itself comes from bench.py).
 
     python -m bpd_substrate_b200.measure            # prints one JSON object per configuration
+    python -m bpd_substrate_b200.measure --gemm-once tc5 64 [N K]
+                                                    # five launches of one many-token product (kernel
+                                                    # tc5 | mma | dispatch): a small case for a profiler
 
 Cold-HBM protocol: every timed launch reads a different copy of its weights, with enough
 copies that the working set is several times the L2 size, so no launch finds its inputs
@@ -53,9 +56,31 @@ def _copies(nbytes, target=600e6):
     return max(2, int(target // nbytes) + 1)
 
 
+def gemm_once(lib, kernel, tokens, N=14336, K=4096, launches=5):
+    """One Q4_K x Q8_K product, a few launches, nothing else on the device."""
+    entry = {"tc5": lib.bpd_qmm_q4k_q8k_tc5_cuda, "mma": lib.bpd_qmm_q4k_q8k_mma_cuda}.get(kernel)
+    w = _dev(lib, synth.q4k_matrix(N, K, 1))
+    x = _dev(lib, synth.activations(K, 2, rows=tokens))
+    o = lib.bpdq_alloc(tokens * N * 4)
+    for _ in range(launches):
+        if entry is not None:
+            capi.check(entry(w, x, o, tokens, N, K, None))
+        else:
+            capi.check(lib.bpd_qmm_q4k_q8k_cuda(w, x, o, tokens, N, K, 0, 0, None, None))
+    lib.bpdq_sync()
+    status = lib.bpdq_last_status()
+    for p in (w, x, o):
+        lib.bpdq_free(p)
+    print(json.dumps({"gemm_once": kernel, "tokens": tokens, "N": N, "K": K, "status": status}))
+    return 0 if status == 0 else 1
+
+
 def main():
     lib = capi.load()
     lib.bpdq_clear_status()
+    if len(sys.argv) >= 4 and sys.argv[1] == "--gemm-once":
+        extra = [int(v) for v in sys.argv[4:6]]
+        return gemm_once(lib, sys.argv[2], int(sys.argv[3]), *extra)
     peak = _peak()
     tm = Timer(lib)
     s = tm.stream
