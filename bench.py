@@ -32,9 +32,11 @@ METRIC = "Q4_K x Q8_K GEMV effective HBM bandwidth"
 UNIT = "GB/s"
 WORKLOAD = "mistral7b_layer_set_x32_q4k_decode_batch1"
 N_LAYERS = 32
-KERNEL_OF = {"batched": "k_gemv_batch_q4k_q8k", "grouped": "k_gemv_q4k_q8k", "separate": "k_gemv_q4k_q8k"}
+KERNEL_OF = {"batched": "k_gemv_batch_q4k_q8k", "grouped": "k_gemv_q4k_q8k", "separate": "k_gemv_q4k_q8k",
+             "chain": "k_gemv_batch_q4k_q8k", "chain4": "k_gemv_batch_q4k_q8k", "chain-separate": "k_gemv_batch_q4k_q8k"}
 # DRAM traffic / algorithmic bytes measured with ncu (profiles/*.md): nothing is re-read
-TRAFFIC_PER_ALGORITHMIC = {"batched": 1.03, "grouped": 1.00, "separate": 1.00}
+TRAFFIC_PER_ALGORITHMIC = {"batched": 1.03, "grouped": 1.00, "separate": 1.00, "chain": 1.03, "chain4": 1.03,
+                           "chain-separate": 1.03}
 
 
 def measured_peak():
@@ -212,14 +214,24 @@ def run_gpu(args):
         # NCCL reads this rank's output arena directly: let torch own that allocation
         o_floats = args.tokens * args.layers * sum(rows // shard[1] for _, rows, _ in shapes)
         out_local = torch.empty(o_floats, dtype=torch.float32, device="cuda")
-    ls = LayerSet(shapes, args.layers, seed=2000 + (rank if args.workload == "mistral7b" else 0), row_shard=shard,
-                  d_out=out_local.data_ptr() if out_local is not None else None, tokens=args.tokens)
-    step_bytes = ls.algorithmic_bytes()
     schedule = args.schedule
+    chain = schedule in ("chain", "chain4", "chain-separate")
+    if chain:
+        # the same seven matrices per layer as a DEPENDENT chain (every product reads what the step
+        # before it wrote), with the elementwise steps of the reference's decode loop in between
+        if world > 1 or args.workload != "mistral7b" or args.tokens != 1:
+            raise SystemExit("--schedule chain: one GPU, mistral7b shapes, one token")
+        from bpd_substrate_b200.dispatch import DecodeChain
+        ls = DecodeChain(n_layers=args.layers, seed=2000)
+    else:
+        ls = LayerSet(shapes, args.layers, seed=2000 + (rank if args.workload == "mistral7b" else 0), row_shard=shard,
+                      d_out=out_local.data_ptr() if out_local is not None else None, tokens=args.tokens)
+    step_bytes = ls.algorithmic_bytes()
     launches = ls.launches_per_step(schedule)
     # launches of the dominant kernel (the batched schedule adds one small quantizer per layer,
     # which overlaps the previous GEMV kernel and is counted in the step time)
-    main_launches = args.layers if schedule == "batched" else launches
+    main_launches = args.layers if schedule == "batched" else (
+        (7 if schedule == "chain-separate" else 4) * args.layers if chain else launches)
     x_host = lib.bpdq_host_alloc(ls.x_bytes)
     o_host = lib.bpdq_host_alloc(ls.o_bytes)
     x_np = np.ctypeslib.as_array((np.ctypeslib.ctypes.c_float * (ls.x_bytes // 4)).from_address(x_host))
@@ -316,6 +328,8 @@ def run_gpu(args):
                        "layers": args.layers, "gemvs_per_step": 7 * args.layers, "tokens": args.tokens,
                        "schedule": schedule, "launches_per_step": launches,
                        "weights_bytes_per_gpu": ls.weight_bytes,
+                       "dependencies": "chain: every product reads the previous step's output" if chain else
+                       "independent products, inputs resident before the step",
                        "l2": "inputs larger than L2: 3.9 GB of weights stream through once per step",
                        "parallelism": f"row-shard x{world}" if world > 1 else "single GPU",
                        "exchange": "NCCL all-gather of output slices once per step" if world > 1 else "none"},
@@ -352,7 +366,12 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--schedule", default="batched", choices=["batched", "grouped", "separate"])
+    ap.add_argument("--schedule", default="batched", choices=["batched", "grouped", "separate", "chain", "chain4", "chain-separate"],
+                    help="batched: the benchmark (a layer's seven independent products in one launch); grouped / "
+                         "separate: fewer products per launch; chain: the seven products as a dependent decode chain, "
+                         "rms_norm / SwiGLU as small kernels writing quantized records, residual add in the product's "
+                         "epilogue (8 launches per layer); chain4: the steps inside the product kernels (4); "
+                         "chain-separate: the reference's 13-call sequence per layer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="mistral7b", choices=["mistral7b", "llama70b"],
                     help="mistral7b: the benchmark (every rank a full layer set, weak scaling); llama70b: the "

@@ -78,6 +78,14 @@ SIGNATURES = {
     "bpd_qmatmul_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, vp]),
     "bpd_qmatmul_q4k_q8k_multi_cuda": (i32, [i32, vp, vp, vp, vp, i32, vp]),
     "bpd_qmatmul_q4k_q8k_batch_cuda": (i32, [i32, vp, vp]),
+    "bpd_qmatmul_q4k_q8k_batch_ready_cuda": (i32, [i32, vp, vp, sz, vp]),
+    # decode glue: record producers and products over records
+    "bpdq_records_bytes": (sz, [i32]),
+    "bpd_quant_q8k_records_cuda": (i32, [vp, vp, i32, vp]),
+    "bpd_rmsnorm_q8k_records_cuda": (i32, [vp, vp, vp, i32, i32, f32, vp]),
+    "bpd_swiglu_q8k_records_cuda": (i32, [vp, vp, vp, i32, vp]),
+    "bpd_qmatmul_q4k_records_cuda": (i32, [i32, vp, vp, C.c_uint, vp]),
+    "bpd_qmatmul_q4k_fused_cuda": (i32, [i32, vp, i32, vp, vp, f32, C.c_uint, vp]),
     "bpd_qmatmul_q4k_q8k_batch_ws_cuda": (i32, [i32, vp, vp, sz, vp]),
     "bpdq_batch_workspace_bytes": (sz, [i32, vp]),
     "bpd_qmatmul_q4k_q8k_batch_static_cuda": (i32, [i32, vp, vp]),

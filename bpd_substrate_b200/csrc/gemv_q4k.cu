@@ -760,6 +760,7 @@ struct BatchProblem {
     int M, nb, row_bytes, rt;     // rows, super-blocks per row, bytes per row, rows per tile
     int tile_begin;
     int xq_off;                   // byte offset of this problem's activation records in shared memory
+    int accumulate;               // 1: out[row] += result (residual connection folded into the product)
 };
 struct BatchVector {              // one distinct activation vector
     const float* x;
@@ -775,6 +776,12 @@ struct BatchPlan {
     // records, xq_bytes in all), or null: quantize inside this kernel
     const uint8_t* records;
     int xq_bytes;
+    // what the CTAs do to the launch's single input vector before they quantize it themselves (records
+    // null): 0 nothing, 1 rms_norm(pro_a, weights pro_b, pro_eps), 2 silu(pro_a) * pro_b
+    int prologue;
+    const float* pro_a;
+    const float* pro_b;
+    float pro_eps;
     BatchProblem prob[kMaxBatch];
     BatchVector vec[kMaxBatch];
 };
@@ -916,6 +923,81 @@ __global__ void __launch_bounds__(256) k_quant_records(const QuantVectors q, uin
 }
 
 
+// ---- Decode glue: the elementwise steps either side of a product write the product's activation
+// records directly, so the fp32 vector between them never goes to memory and the step is one launch.
+//
+// rms_norm fused with the record quantizer.  One CTA per row; arithmetic and summation order are
+// those of k_rms_norm in decode_ops.cu (lib/kernel_templates_llama.pl:529-593 of the reference):
+// per-thread fmaf chain over c = t, t+256, ..., butterfly over the warp, the eight warp sums added
+// in order, scale = rsqrtf(sum/cols + eps), y = (x*scale)*w; then the rule of quantize_block_256.
+__global__ void __launch_bounds__(256) k_rmsnorm_records(const float* __restrict__ in, const float* __restrict__ w,
+                                                          uint8_t* __restrict__ records, int cols, float eps)
+{
+    __shared__ float s_sum[8];
+    pdl_launch_dependents();
+    pdl_wait();   // the row is the previous product's output (residual stream)
+    const float* x = in + (size_t)blockIdx.x * cols;
+    uint8_t* rec = records + (size_t)blockIdx.x * (cols / 256) * 2 * kXqStride;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float t = 0.0f;
+    // (data written by the launch before this one is read past L1: ld.global.cg)
+    for (int c = threadIdx.x; c < cols; c += 256) {
+        const float v = __ldcg(x + c);
+        t = fmaf(v, v, t);
+    }
+    t = warp_sum(t);
+    if (lane == 0) s_sum[warp] = t;
+    __syncthreads();
+    float tot = s_sum[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) tot += s_sum[i];
+    const float scale = rsqrtf(tot / (float)cols + eps);
+    for (int b = warp; b < cols / 256; b += 8) {
+        const float4* xb = reinterpret_cast<const float4*>(x + (size_t)b * 256);
+        const float4* wb = reinterpret_cast<const float4*>(w + (size_t)b * 256);
+        const float4 a0 = __ldcg(xb + lane), a1 = __ldcg(xb + 32 + lane), w0 = __ldg(wb + lane), w1 = __ldg(wb + 32 + lane);
+        const float4 v0 = make_float4(a0.x * scale * w0.x, a0.y * scale * w0.y, a0.z * scale * w0.z, a0.w * scale * w0.w);
+        const float4 v1 = make_float4(a1.x * scale * w1.x, a1.y * scale * w1.y, a1.z * scale * w1.z, a1.w * scale * w1.w);
+        write_records(v0, v1, rec + (size_t)(2 * b) * kXqStride, lane);
+    }
+}
+
+// silu(gate) * up fused with the record quantizer (the arithmetic of k_elementwise's OP_SILU then
+// OP_MUL: x / (1 + expf(-x)), lib/kernel_templates_llama.pl:668).  One warp per 256-block.
+__global__ void __launch_bounds__(256) k_swiglu_records(const float* __restrict__ gate, const float* __restrict__ up,
+                                                         uint8_t* __restrict__ records, long n_blocks)
+{
+    pdl_launch_dependents();
+    pdl_wait();   // gate and up come from the product launched just before
+    const int lane = threadIdx.x & 31;
+    const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long n_warps = ((long)gridDim.x * blockDim.x) >> 5;
+    auto act = [](float g, float u) { return (g / (1.0f + expf(-g))) * u; };
+    for (long b = warp; b < n_blocks; b += n_warps) {
+        const float4* gb = reinterpret_cast<const float4*>(gate + (size_t)b * 256);
+        const float4* ub = reinterpret_cast<const float4*>(up + (size_t)b * 256);
+        const float4 g0 = __ldcg(gb + lane), g1 = __ldcg(gb + 32 + lane), u0 = __ldcg(ub + lane), u1 = __ldcg(ub + 32 + lane);
+        const float4 v0 = make_float4(act(g0.x, u0.x), act(g0.y, u0.y), act(g0.z, u0.z), act(g0.w, u0.w));
+        const float4 v1 = make_float4(act(g1.x, u1.x), act(g1.y, u1.y), act(g1.z, u1.z), act(g1.w, u1.w));
+        write_records(v0, v1, records + (size_t)(2 * b) * kXqStride, lane);
+    }
+}
+
+// Plain quantizer to records for a vector that the previous launch produced.
+__global__ void __launch_bounds__(256) k_vector_records(const float* __restrict__ x, uint8_t* __restrict__ records,
+                                                         long n_blocks)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const long n_warps = ((long)gridDim.x * blockDim.x) >> 5;
+    for (long b = warp; b < n_blocks; b += n_warps) {
+        const float4* xb = reinterpret_cast<const float4*>(x + (size_t)b * 256);
+        write_records(__ldcg(xb + lane), __ldcg(xb + 32 + lane), records + (size_t)(2 * b) * kXqStride, lane);
+    }
+}
+
 template <int R, int LAYOUT>
 __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8_t* xq, const BatchProblem& pb, int row0,
                                            int lane)
@@ -954,7 +1036,9 @@ __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8
     const float total = fold_rows<R>(v, lane);
     constexpr int kLanesPerRow = 32 / R;
     const int my_row = lane / kLanesPerRow;
-    if ((lane % kLanesPerRow) == 0 && my_row < rows) pb.out[row0 + my_row] = total;
+    // (the residual stream was written by an earlier launch: read it past L1)
+    if ((lane % kLanesPerRow) == 0 && my_row < rows)
+        pb.out[row0 + my_row] = pb.accumulate ? __ldcg(pb.out + row0 + my_row) + total : total;
 }
 
 template <int FMT, int LAYOUT, int MAXTHREADS>
@@ -1028,6 +1112,47 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
         // Activations may be written by the previous kernel: wait for it before the first read.
         pdl_wait();
         BPDQ_TRACE(2);
+        if (p.prologue == 1) {
+            // ---- rms_norm of the launch's one vector, then its records, in every CTA.  The sum of
+            // squares is formed exactly as k_rms_norm (decode_ops.cu) forms it with 256 threads:
+            // thread t chains c = t, t+256, ...; butterfly over each warp of 32; the eight warp sums
+            // added in order.  Consumer warps play those eight warps in turn.
+            float* s_sum = reinterpret_cast<float*>(xbar + 1);
+            const int cols = p.vec[0].nb * 256;
+            for (int vw = warp; vw < 8; vw += p.nw) {
+                float t = 0.0f;
+                for (int c = vw * 32 + lane; c < cols; c += 256) {
+                    const float v = __ldcg(p.pro_a + c);
+                    t = fmaf(v, v, t);
+                }
+                t = warp_sum(t);
+                if (lane == 0) s_sum[vw] = t;
+            }
+            named_bar_sync(2, p.nw * 32);
+            float tot = s_sum[0];
+#pragma unroll
+            for (int i = 1; i < 8; i++) tot += s_sum[i];
+            const float scale = rsqrtf(tot / (float)cols + p.pro_eps);
+            for (int b = warp; b < p.vec[0].nb; b += p.nw) {
+                const float4* xb = reinterpret_cast<const float4*>(p.pro_a + (size_t)b * 256);
+                const float4* wb = reinterpret_cast<const float4*>(p.pro_b + (size_t)b * 256);
+                const float4 a0 = __ldcg(xb + lane), a1 = __ldcg(xb + 32 + lane), w0 = __ldg(wb + lane), w1 = __ldg(wb + 32 + lane);
+                const float4 v0 = make_float4(a0.x * scale * w0.x, a0.y * scale * w0.y, a0.z * scale * w0.z, a0.w * scale * w0.w);
+                const float4 v1 = make_float4(a1.x * scale * w1.x, a1.y * scale * w1.y, a1.z * scale * w1.z, a1.w * scale * w1.w);
+                write_records(v0, v1, xq + (size_t)(2 * b) * kXqStride, lane);
+            }
+        } else if (p.prologue == 2) {
+            // ---- silu(gate) * up (k_elementwise's arithmetic), then its records, in every CTA
+            auto act = [](float g, float u) { return (g / (1.0f + expf(-g))) * u; };
+            for (int b = warp; b < p.vec[0].nb; b += p.nw) {
+                const float4* gb = reinterpret_cast<const float4*>(p.pro_a + (size_t)b * 256);
+                const float4* ub = reinterpret_cast<const float4*>(p.pro_b + (size_t)b * 256);
+                const float4 g0 = __ldcg(gb + lane), g1 = __ldcg(gb + 32 + lane), u0 = __ldcg(ub + lane), u1 = __ldcg(ub + 32 + lane);
+                const float4 v0 = make_float4(act(g0.x, u0.x), act(g0.y, u0.y), act(g0.z, u0.z), act(g0.w, u0.w));
+                const float4 v1 = make_float4(act(g1.x, u1.x), act(g1.y, u1.y), act(g1.z, u1.z), act(g1.w, u1.w));
+                write_records(v0, v1, xq + (size_t)(2 * b) * kXqStride, lane);
+            }
+        } else {
         // ---- quantize every activation vector of the launch into shared memory (all consumer warps)
         constexpr int UNR = 4;
         for (int blk0 = warp; blk0 < p.total_blocks; blk0 += p.nw * UNR) {
@@ -1044,8 +1169,8 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
                     int k = 0;
                     while (k + 1 < p.n_vectors && blk >= p.vec[k].nb) { blk -= p.vec[k].nb; k++; }
                     const float4* xb = reinterpret_cast<const float4*>(p.vec[k].x + (size_t)blk * 256);
-                    v0[u] = __ldg(xb + lane);
-                    v1[u] = __ldg(xb + 32 + lane);
+                    v0[u] = __ldcg(xb + lane);      // may be the output of the launch before this one
+                    v1[u] = __ldcg(xb + 32 + lane);
                     vb[u] = blk;
                     vq[u] = p.vec[k].xq_off;
                 }
@@ -1056,6 +1181,7 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
                 if (FMT == 0) write_records(v0[u], v1[u], xq + vq[u] + (size_t)(2 * vb[u]) * kXqStride, lane);
                 else write_records_q80(v0[u], v1[u], xq + vq[u] + (size_t)(4 * vb[u]) * kQ80PairStride, lane);
             }
+        }
         }
         named_bar_sync(2, p.nw * 32);
     }
@@ -1115,12 +1241,16 @@ static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt = 0)
     p.slot_bytes = 0;
     p.trace = nullptr;
     p.records = nullptr;
+    p.prologue = 0;
+    p.pro_a = p.pro_b = nullptr;
+    p.pro_eps = 0.0f;
     int xq_bytes = 0;
     for (int j = 0; j < n; j++) {
         if (d[j].M <= 0 || d[j].K <= 0 || (d[j].K % 256) != 0) return BPDQ_ERR_ARG;
         BatchProblem& pb = p.prob[j];
         pb.W = d[j].W;
         pb.out = d[j].out;
+        pb.accumulate = 0;
         pb.M = d[j].M;
         pb.nb = d[j].K / 256;
         pb.row_bytes = fmt == 0 ? pb.nb * BPDQ_Q4K_BYTES : pb.nb * 8 * BPDQ_Q80_BYTES;
@@ -1155,7 +1285,7 @@ static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt = 0)
         auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
         p.off_ring = take((size_t)p.nw * p.slots * p.slot_bytes);
         p.off_xq = take((size_t)xq_bytes);
-        p.off_bar = take((size_t)2 * p.nw * p.slots * 8 + 8);
+        p.off_bar = take((size_t)2 * p.nw * p.slots * 8 + 8 + 64);   // barriers, then nine floats of the rms_norm prologue
         p.smem = off;
         if (p.smem <= (size_t)kSmemLimit) break;
         if (p.slots > 2) p.slots--;
@@ -1271,6 +1401,80 @@ int gemv_q4k_q8k_batch(const BatchDesc* d, int n, int layout, uint8_t* ws, size_
     return 0;
 }
 
+// Products over records that an earlier launch wrote (k_rmsnorm_records, k_swiglu_records,
+// k_vector_records): up to kMaxBatch matrices with the same K sharing one record vector, one
+// launch.  Bit j of accumulate_mask: out_j[row] += result (the residual connection).
+int gemv_q4k_records(const BatchDesc* d, int n, const uint8_t* records, unsigned accumulate_mask, int layout, cudaStream_t s)
+{
+    if (n < 1 || n > kMaxBatch || !d || !records) return latch(BPDQ_ERR_ARG);
+    if ((uintptr_t)records & 15) return latch(BPDQ_ERR_ALIGN);
+    BatchDesc run[kMaxBatch];
+    for (int j = 0; j < n; j++) {
+        if (d[j].M <= 0 || d[j].K <= 0 || (d[j].K % 256) != 0 || d[j].K != d[0].K) return latch(BPDQ_ERR_ARG);
+        if (!d[j].W || !d[j].out) return latch(BPDQ_ERR_ARG);
+        if (((uintptr_t)d[j].W & 15) || ((uintptr_t)d[j].out & 3)) return latch(BPDQ_ERR_ALIGN);
+        run[j] = d[j];
+        run[j].x = reinterpret_cast<const float*>(records);   // one shared vector: identical key for the planner
+    }
+    BatchPlan plan;
+    int rc = make_batch_plan(run, n, plan);
+    if (rc) return latch(rc);
+    plan.records = records;
+    for (int j = 0; j < n; j++) plan.prob[j].accumulate = (accumulate_mask >> j) & 1u;
+    rc = layout == BPDQ_LAYOUT_GGML ? launch_batch<0, BPDQ_LAYOUT_GGML>(plan, s) : launch_batch<0, BPDQ_LAYOUT_BPD>(plan, s);
+    return rc ? latch(rc) : 0;
+}
+
+// One launch for "elementwise step, quantize, products, residual add": the CTAs of the product
+// kernel apply the step to the single input vector themselves (each CTA redundantly: the vector is
+// 16-56 KB and comes from L2) while their producer warp is already filling the weight ring.
+// prologue 0: records of a;  1: records of rms_norm(a, weights b, eps);  2: records of silu(a) * b.
+int gemv_q4k_fused(const BatchDesc* d, int n, int prologue, const float* a, const float* b, float eps,
+                   unsigned accumulate_mask, int layout, cudaStream_t s)
+{
+    if (n < 1 || n > kMaxBatch || !d || !a || prologue < 0 || prologue > 2 || (prologue && !b)) return latch(BPDQ_ERR_ARG);
+    if (((uintptr_t)a & 15) || (b && ((uintptr_t)b & 15))) return latch(BPDQ_ERR_ALIGN);
+    BatchDesc run[kMaxBatch];
+    for (int j = 0; j < n; j++) {
+        if (d[j].M <= 0 || d[j].K <= 0 || (d[j].K % 256) != 0 || d[j].K != d[0].K) return latch(BPDQ_ERR_ARG);
+        if (!d[j].W || !d[j].out) return latch(BPDQ_ERR_ARG);
+        if (((uintptr_t)d[j].W & 15) || ((uintptr_t)d[j].out & 3)) return latch(BPDQ_ERR_ALIGN);
+        run[j] = d[j];
+        run[j].x = a;
+    }
+    BatchPlan plan;
+    int rc = make_batch_plan(run, n, plan);
+    if (rc) return latch(rc);
+    plan.prologue = prologue;
+    plan.pro_a = a;
+    plan.pro_b = b;
+    plan.pro_eps = eps;
+    for (int j = 0; j < n; j++) plan.prob[j].accumulate = (accumulate_mask >> j) & 1u;
+    rc = layout == BPDQ_LAYOUT_GGML ? launch_batch<0, BPDQ_LAYOUT_GGML>(plan, s) : launch_batch<0, BPDQ_LAYOUT_BPD>(plan, s);
+    return rc ? latch(rc) : 0;
+}
+
+template <typename Kern, typename... Args>
+static int launch_glue(Kern kern, int grid, cudaStream_t s, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, args...));
+}
+
+static int glue_grid(long n_blocks)
+{
+    long want = (n_blocks + 7) / 8, cap = (long)sm_count() * 8;
+    return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
 // Q8_0 weights [N][K/32][34] times one activation vector, activations quantized to Q8_0 inside
 // the kernel.  Fast path only: K a multiple of 256 (rows are then 16-byte multiples and can be
 // bulk-copied); returns BPDQ_ERR_RANGE otherwise so that the caller can take the generic kernel.
@@ -1364,10 +1568,19 @@ int bpd_qmatmul_q4k_q8k_batch_cuda(int n, const bpdq_gemv_desc* descs, void* str
                               (cudaStream_t)stream);
 }
 // Same, with caller-owned scratch for the quantized activations (bpdq_batch_workspace_bytes
-// says how much).  The scratch must not be in use by an earlier launch that may still run
-// (give every call in flight its own piece).
+// says how much).  Ordered like any launch: the quantizer waits for the work ahead of it in the
+// stream before it reads the activations or writes the scratch.
 int bpd_qmatmul_q4k_q8k_batch_ws_cuda(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes,
                                       void* stream)
+{
+    return gemv_q4k_q8k_batch(reinterpret_cast<const BatchDesc*>(descs), n, BPDQ_LAYOUT_BPD, (uint8_t*)workspace,
+                              workspace_bytes, 0, (cudaStream_t)stream);
+}
+// Same, for activation vectors that are complete when the call is made (nothing still in flight on
+// the stream writes them) and scratch that no launch still in flight uses: the quantizer then
+// runs under the tail of the launch ahead of it instead of after it.
+int bpd_qmatmul_q4k_q8k_batch_ready_cuda(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes,
+                                         void* stream)
 {
     return gemv_q4k_q8k_batch(reinterpret_cast<const BatchDesc*>(descs), n, BPDQ_LAYOUT_BPD, (uint8_t*)workspace,
                               workspace_bytes, 1, (cudaStream_t)stream);
@@ -1397,6 +1610,45 @@ size_t bpdq_batch_static_capacity(void) { return kStaticRecordBytes; }
 
 // Full-control form: tokens >= 1, layout 0/1, xsrc 0 (fp32) / 1 (pre-quantized Q8_K), optional
 // int32 [M][K/256][8] buffer receiving token 0's exact sub-block dots.
+size_t bpdq_records_bytes(int K) { return K > 0 && (K % 256) == 0 ? (size_t)(K / 256) * 2 * kXqStride : 0; }
+int bpd_quant_q8k_records_cuda(const float* x, void* records, int K, void* stream)
+{
+    if (!x || !records || K <= 0 || (K % 256) != 0) return latch(BPDQ_ERR_ARG);
+    if (((uintptr_t)x & 15) || ((uintptr_t)records & 15)) return latch(BPDQ_ERR_ALIGN);
+    int rc = launch_glue(k_vector_records, glue_grid(K / 256), (cudaStream_t)stream, x, (uint8_t*)records, (long)(K / 256));
+    return rc ? latch(rc) : 0;
+}
+int bpd_rmsnorm_q8k_records_cuda(const float* x, const float* w, void* records, int rows, int K, float eps, void* stream)
+{
+    if (rows < 0 || K <= 0 || (K % 256) != 0 || (rows > 0 && (!x || !w || !records))) return latch(BPDQ_ERR_ARG);
+    if (rows == 0) return 0;
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)records & 15)) return latch(BPDQ_ERR_ALIGN);
+    int rc = launch_glue(k_rmsnorm_records, rows, (cudaStream_t)stream, x, w, (uint8_t*)records, K, eps);
+    return rc ? latch(rc) : 0;
+}
+int bpd_swiglu_q8k_records_cuda(const float* gate, const float* up, void* records, int K, void* stream)
+{
+    if (!gate || !up || !records || K <= 0 || (K % 256) != 0) return latch(BPDQ_ERR_ARG);
+    if (((uintptr_t)gate & 15) || ((uintptr_t)up & 15) || ((uintptr_t)records & 15)) return latch(BPDQ_ERR_ALIGN);
+    int rc = launch_glue(k_swiglu_records, glue_grid(K / 256), (cudaStream_t)stream, gate, up, (uint8_t*)records, (long)(K / 256));
+    return rc ? latch(rc) : 0;
+}
+int bpd_qmatmul_q4k_fused_cuda(int n, const bpdq_gemv_desc* descs, int prologue, const float* a, const float* b, float eps,
+                               unsigned accumulate_mask, void* stream)
+{
+    if (n < 1 || n > kMaxBatch || !descs) return latch(BPDQ_ERR_ARG);
+    BatchDesc d[kMaxBatch];
+    for (int j = 0; j < n; j++) d[j] = {descs[j].W, nullptr, descs[j].out, descs[j].M, descs[j].K};
+    return gemv_q4k_fused(d, n, prologue, a, b, eps, accumulate_mask, BPDQ_LAYOUT_BPD, (cudaStream_t)stream);
+}
+int bpd_qmatmul_q4k_records_cuda(int n, const bpdq_gemv_desc* descs, const void* records, unsigned accumulate_mask,
+                                 void* stream)
+{
+    if (n < 1 || n > kMaxBatch || !descs) return latch(BPDQ_ERR_ARG);
+    BatchDesc d[kMaxBatch];
+    for (int j = 0; j < n; j++) d[j] = {descs[j].W, nullptr, descs[j].out, descs[j].M, descs[j].K};
+    return gemv_q4k_records(d, n, (const uint8_t*)records, accumulate_mask, BPDQ_LAYOUT_BPD, (cudaStream_t)stream);
+}
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,
                          int xsrc, int32_t* subdots, void* stream)
 {

@@ -133,9 +133,10 @@ class LayerSet:
                 if self.ws is None:
                     self.ws_stride = (lib.bpdq_batch_workspace_bytes(nm, descs) + 255) // 256 * 256
                     self.ws = lib.bpdq_alloc(self.ws_stride * self.n_layers)
-                # every layer has its own scratch: launches of one step never share it
-                capi.check(lib.bpd_qmatmul_q4k_q8k_batch_ws_cuda(nm, descs, self.ws + layer * self.ws_stride,
-                                                                 self.ws_stride, s), "batched GEMV launch")
+                # every layer has its own scratch and the step's activations are all on the device before
+                # its first launch (independent products): the quantizers may run ahead of stream order
+                capi.check(lib.bpd_qmatmul_q4k_q8k_batch_ready_cuda(nm, descs, self.ws + layer * self.ws_stride,
+                                                                    self.ws_stride, s), "batched GEMV launch")
             return
         groups = GROUPS_DECODE if schedule == "grouped" else GROUPS_NONE
         for layer in range(self.n_layers):
@@ -212,4 +213,207 @@ class LayerSet:
             lib.bpdq_free(self.ws)
         if self._own_out:
             lib.bpdq_free(self.d_out)
+        lib.bpdq_stream_destroy(self.stream)
+
+
+class DecodeChain:
+    """One token through ``n_layers`` decoder layers, in the order of the reference's decode loop
+    (inference/llamatov_gpu_llama.py:119-166), as a DEPENDENT chain: every product reads what the
+    step before it wrote.  As in that loop, attention over a single position is the identity and
+    ``wo`` is applied to ``q`` directly (``:133-146``).
+
+    Per layer the reference makes 13 launches (rms_norm, q, k, v, o, add, rms_norm, gate, silu,
+    up, mul, down, add) on fp32 weights.  Modes here, all on Q4_K weights and all giving the same bits:
+
+    * ``"chain"`` -- 8 launches: each elementwise step is a small kernel that writes the next
+      product's activation records (``bpd_rmsnorm_q8k_records_cuda`` and friends), products that
+      share an input share a launch, the residual add is the product's epilogue::
+
+          rms_norm -> rec | q,k,v | q -> rec | o, += x | rms_norm -> rec | gate,up | silu(gate)*up -> rec | down, += x
+
+    * ``"chain4"`` -- 4 launches: the step runs inside the product kernel that consumes it
+      (``bpd_qmatmul_q4k_fused_cuda``), in every CTA.  Fewer launches, but 148 CTAs repeat the step
+      after the wait for the previous launch: measured slower than ``"chain"`` on the benchmark's shapes;
+    * ``"chain-separate"`` -- the reference's call sequence (gpu_rms_norm, gpu_silu, gpu_mul,
+      gpu_add and one product per matrix).
+    """
+
+    MODES = {"chain": 8, "chain4": 4, "chain-separate": 13}
+    NAMES = ("wq", "wk", "wv", "wo", "w1", "w3", "w2")
+
+    def __init__(self, hidden=4096, kv=1024, ffn=14336, n_layers=32, seed=3000, eps=1e-5, lib=None):
+        self.lib = lib = lib or capi.load()
+        self.hidden, self.kv, self.ffn, self.n_layers, self.eps = hidden, kv, ffn, n_layers, eps
+        self.shapes = (("wq", hidden, hidden), ("wk", kv, hidden), ("wv", kv, hidden), ("wo", hidden, hidden),
+                       ("w1", ffn, hidden), ("w3", ffn, hidden), ("w2", hidden, ffn))
+        rng = np.random.default_rng(seed)
+        self.base_weights = [synth.q4k_matrix(rows, cols, rng) for _, rows, cols in self.shapes]
+        self.norm_host = (1.0 + 0.1 * rng.standard_normal((n_layers, 2, hidden))).astype(np.float32)
+        self.weights, self.weight_bytes = [], 0
+        for layer in range(n_layers):
+            ptrs = []
+            for m in range(7):
+                w = self.host_weight(layer, m)
+                p = lib.bpdq_alloc(w.nbytes)
+                lib.bpdq_h2d(p, w.ctypes.data, w.nbytes)
+                ptrs.append(p)
+                self.weight_bytes += w.nbytes
+            self.weights.append(ptrs)
+        self.d_norm = lib.bpdq_alloc(self.norm_host.nbytes)
+        lib.bpdq_h2d(self.d_norm, self.norm_host.ctypes.data, self.norm_host.nbytes)
+        f = 4
+        self.buf = {name: lib.bpdq_alloc(n * f) for name, n in
+                    (("x", hidden), ("h", hidden), ("q", hidden), ("k", kv), ("v", kv), ("gate", ffn), ("up", ffn),
+                     ("attn", hidden), ("down", hidden))}
+        self.rec = {name: lib.bpdq_alloc(lib.bpdq_records_bytes(n)) for name, n in
+                    (("h", hidden), ("q", hidden), ("act", ffn))}
+        self.ws = lib.bpdq_alloc(lib.bpdq_records_bytes(ffn) + 4096)   # scratch of the separate (unfused) products
+        self.ws_bytes = lib.bpdq_records_bytes(ffn) + 4096
+        self.stream = lib.bpdq_stream_create()
+        self.graph = {}
+        capi.check(lib.bpdq_last_status(), "DecodeChain setup")
+
+    def host_weight(self, layer, m):
+        return np.roll(self.base_weights[m], synth.Q4K_BYTES * (layer + 1))
+
+    def norm_ptr(self, layer, which):
+        return self.d_norm + (layer * 2 + which) * self.hidden * 4
+
+    def algorithmic_bytes(self):
+        """Quantized weights + fp32 vector in + fp32 vector out of every product, per token."""
+        return self.n_layers * sum(synth.gemv_bytes_q4k(rows, cols) for _, rows, cols in self.shapes)
+
+    @staticmethod
+    def _mode(mode):
+        if isinstance(mode, str):
+            return mode
+        return "chain" if mode else "chain-separate"
+
+    def launches_per_token(self, mode="chain"):
+        return self.n_layers * self.MODES[self._mode(mode)]
+
+    # ---- state
+    def set_state(self, x):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        assert x.size == self.hidden
+        self.lib.bpdq_h2d(self.buf["x"], x.ctypes.data, x.nbytes)
+
+    def get_state(self):
+        out = np.empty(self.hidden, np.float32)
+        self.lib.bpdq_stream_sync(self.stream)
+        self.lib.bpdq_d2h(out.ctypes.data, self.buf["x"], out.nbytes)
+        return out
+
+    # ---- launches
+    def _descs(self, layer, members, outs):
+        d = (capi.GemvDesc * len(members))()
+        for j, (m, o) in enumerate(zip(members, outs)):
+            _, rows, cols = self.shapes[m]
+            d[j] = capi.GemvDesc(self.weights[layer][m], None, self.buf[o], rows, cols)
+        return d
+
+    def enqueue_token(self, mode="chain", stream=None):
+        lib, s, b, r = self.lib, (stream if stream is not None else self.stream), self.buf, self.rec
+        H, F, eps = self.hidden, self.ffn, self.eps
+        mode = self._mode(mode)
+        if mode == "chain4":
+            for layer in range(self.n_layers):
+                capi.check(lib.bpd_qmatmul_q4k_fused_cuda(3, self._descs(layer, (0, 1, 2), ("q", "k", "v")), 1, b["x"],
+                                                          self.norm_ptr(layer, 0), eps, 0, s))
+                capi.check(lib.bpd_qmatmul_q4k_fused_cuda(1, self._descs(layer, (3,), ("x",)), 0, b["q"], None, 0.0, 1, s))
+                capi.check(lib.bpd_qmatmul_q4k_fused_cuda(2, self._descs(layer, (4, 5), ("gate", "up")), 1, b["x"],
+                                                          self.norm_ptr(layer, 1), eps, 0, s))
+                capi.check(lib.bpd_qmatmul_q4k_fused_cuda(1, self._descs(layer, (6,), ("x",)), 2, b["gate"], b["up"], 0.0,
+                                                          1, s))
+            return
+        if mode == "chain":
+            for layer in range(self.n_layers):
+                capi.check(lib.bpd_rmsnorm_q8k_records_cuda(b["x"], self.norm_ptr(layer, 0), r["h"], 1, H, eps, s))
+                capi.check(lib.bpd_qmatmul_q4k_records_cuda(3, self._descs(layer, (0, 1, 2), ("q", "k", "v")), r["h"], 0, s))
+                capi.check(lib.bpd_quant_q8k_records_cuda(b["q"], r["q"], H, s))
+                capi.check(lib.bpd_qmatmul_q4k_records_cuda(1, self._descs(layer, (3,), ("x",)), r["q"], 1, s))
+                capi.check(lib.bpd_rmsnorm_q8k_records_cuda(b["x"], self.norm_ptr(layer, 1), r["h"], 1, H, eps, s))
+                capi.check(lib.bpd_qmatmul_q4k_records_cuda(2, self._descs(layer, (4, 5), ("gate", "up")), r["h"], 0, s))
+                capi.check(lib.bpd_swiglu_q8k_records_cuda(b["gate"], b["up"], r["act"], F, s))
+                capi.check(lib.bpd_qmatmul_q4k_records_cuda(1, self._descs(layer, (6,), ("x",)), r["act"], 1, s))
+            return
+        # the reference's call sequence; the fp32 ops launch on the library's current stream
+        prev = lib.bpdq_get_stream()
+        lib.bpdq_set_stream(s)
+
+        def product(layer, m, x, out):
+            _, rows, cols = self.shapes[m]
+            d = (capi.GemvDesc * 1)(capi.GemvDesc(self.weights[layer][m], b[x], b[out], rows, cols))
+            capi.check(lib.bpd_qmatmul_q4k_q8k_batch_ws_cuda(1, d, self.ws, self.ws_bytes, s))
+
+        try:
+            for layer in range(self.n_layers):
+                lib.gpu_rms_norm(b["x"], self.norm_ptr(layer, 0), b["h"], 1, H, eps)
+                product(layer, 0, "h", "q")
+                product(layer, 1, "h", "k")
+                product(layer, 2, "h", "v")
+                product(layer, 3, "q", "attn")
+                lib.gpu_add(b["x"], b["attn"], b["x"], H)
+                lib.gpu_rms_norm(b["x"], self.norm_ptr(layer, 1), b["h"], 1, H, eps)
+                product(layer, 4, "h", "gate")
+                lib.gpu_silu(b["gate"], b["gate"], F)
+                product(layer, 5, "h", "up")
+                lib.gpu_mul(b["gate"], b["up"], b["gate"], F)
+                product(layer, 6, "gate", "down")
+                lib.gpu_add(b["x"], b["down"], b["x"], H)
+            capi.check(lib.bpdq_last_status(), "decode chain")
+        finally:
+            lib.bpdq_set_stream(prev)
+
+    def capture(self, mode="chain"):
+        """Records one token's chain into a CUDA graph."""
+        mode = self._mode(mode)
+        if mode not in self.graph:
+            lib = self.lib
+            self.enqueue_token(mode)                 # warm-up outside capture (attributes, caches)
+            capi.check(lib.bpdq_stream_sync(self.stream))
+            capi.check(lib.bpdq_graph_begin(self.stream), "graph capture")
+            self.enqueue_token(mode)
+            g = lib.bpdq_graph_end(self.stream)
+            if not g:
+                raise capi.BpdqError(f"graph capture failed (status {lib.bpdq_last_status()})")
+            self.graph[mode] = g
+        return self.graph[mode]
+
+    def step(self, mode="chain"):
+        capi.check(self.lib.bpdq_graph_launch(self.capture(mode), self.stream), "graph launch")
+
+    # ---- the part of LayerSet's interface that the benchmark driver uses (schedule = mode)
+    @property
+    def x_bytes(self):
+        return self.hidden * 4
+
+    o_bytes = x_bytes
+
+    def launches_per_step(self, schedule):
+        return self.launches_per_token(schedule)
+
+    def upload_activations(self, x):
+        self.set_state(x)
+
+    def step_host(self, x_host_ptr, out_host_ptr, schedule="chain"):
+        """One token from HOST buffers: hidden state in, chain, hidden state out, wait."""
+        lib = self.lib
+        capi.check(lib.bpdq_h2d_async(self.buf["x"], x_host_ptr, self.x_bytes, self.stream))
+        self.step(schedule)
+        capi.check(lib.bpdq_d2h_async(out_host_ptr, self.buf["x"], self.o_bytes, self.stream))
+        capi.check(lib.bpdq_stream_sync(self.stream))
+
+    def close(self):
+        lib = self.lib
+        lib.bpdq_stream_sync(self.stream)
+        for g in self.graph.values():
+            lib.bpdq_graph_destroy(g)
+        self.graph = {}
+        for ptrs in self.weights:
+            for p in ptrs:
+                lib.bpdq_free(p)
+        self.weights = []
+        for p in list(self.buf.values()) + list(self.rec.values()) + [self.d_norm, self.ws]:
+            lib.bpdq_free(p)
         lib.bpdq_stream_destroy(self.stream)

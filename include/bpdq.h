@@ -147,9 +147,15 @@ typedef struct bpdq_gemv_desc {
 int bpd_qmatmul_q4k_q8k_batch_cuda(int n, const bpdq_gemv_desc* descs, void* stream);
 /* same with caller-owned device scratch for the quantized activations: a small kernel quantizes
  * each distinct x once and the GEMV kernel bulk-copies the result, instead of every CTA
- * quantizing every x.  The scratch must not be in use by a launch that may still be running. */
+ * quantizing every x.  Ordered after everything ahead of it in the stream, like any launch. */
 int bpd_qmatmul_q4k_q8k_batch_ws_cuda(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes,
                                       void* stream);
+/* same, for callers that can promise more: every x is complete when the call is made (no launch
+ * still in flight on the stream writes it) and no launch still in flight uses the scratch.  The
+ * quantizer then reads x ahead of stream order, under the tail of the launch before it.  Right for
+ * independent products whose inputs were uploaded beforehand; WRONG for a dependent chain. */
+int bpd_qmatmul_q4k_q8k_batch_ready_cuda(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes,
+                                         void* stream);
 size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs);
 /* No counterpart in the reference.  The same batched product for callers that cannot allocate
  * device memory at the time of the call: plugins of a host application that owns every byte of
@@ -169,6 +175,30 @@ size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs);
  *    must be serialized by the caller. */
 int bpd_qmatmul_q4k_q8k_batch_static_cuda(int n, const bpdq_gemv_desc* descs, void* stream);
 size_t bpdq_batch_static_capacity(void);
+/* ---- Decode glue.  Replaces, around the products of a decoder layer, the separate elementwise
+ * launches of the reference's decode loop (inference/llamatov_gpu_llama.py:119-166: gpu_rms_norm,
+ * gpu_silu, gpu_mul, gpu_add; kernels lib/kernel_templates_llama.pl:529-593, :600-830): each step
+ * writes the next product's quantized activation records (144 bytes per 128 activations: int8
+ * values, four int16 sub-block sums, the fp32 block scale) instead of an fp32 vector, and the
+ * residual add is the product's own epilogue.  Same arithmetic as the separate calls, bit for bit.
+ * All launch asynchronously on `stream` and are ordered after the launch before them. */
+size_t bpdq_records_bytes(int K);                       /* bytes of the records of K activations */
+/* records = q8K(x) */
+int bpd_quant_q8k_records_cuda(const float* x, void* records, int K, void* stream);
+/* records[r] = q8K(rms_norm(x[r], w, eps)), rows of K floats (gpu_rms_norm's arithmetic) */
+int bpd_rmsnorm_q8k_records_cuda(const float* x, const float* w, void* records, int rows, int K, float eps, void* stream);
+/* records = q8K(silu(gate) * up) (gpu_silu then gpu_mul) */
+int bpd_swiglu_q8k_records_cuda(const float* gate, const float* up, void* records, int K, void* stream);
+/* out_j[M_j] (+)= W_j[M_j][K] . records for n <= 8 matrices with the same K in one launch; descs[j].x is
+ * ignored; bit j of accumulate_mask: add to out_j instead of overwriting it (gpu_add folded in) */
+int bpd_qmatmul_q4k_records_cuda(int n, const bpdq_gemv_desc* descs, const void* records, unsigned accumulate_mask,
+                                 void* stream);
+/* The step, its quantization, the products and the residual add as ONE launch: every CTA of the
+ * product kernel applies the step to the input vector itself while its weight ring fills.
+ * prologue 0: x = a;  1: x = rms_norm(a, weights b, eps);  2: x = silu(a) * b;  then
+ * out_j[M_j] (+)= W_j[M_j][K] . q8K(x), n <= 8 matrices with the same K.  Same bits as the separate calls. */
+int bpd_qmatmul_q4k_fused_cuda(int n, const bpdq_gemv_desc* descs, int prologue, const float* a, const float* b, float eps,
+                               unsigned accumulate_mask, void* stream);
 /* out[tokens][M]; layout 0/1 as above; xsrc 0: x is float [tokens][K], 1: x is Q8_K blocks
  * [tokens][K/256]; subdots (may be NULL): int32 [M][K/256][8], token 0's exact sub-block dots */
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,

@@ -1,0 +1,227 @@
+"""Decode glue: record producers fused with rms_norm / SwiGLU, products over records with the
+residual add as their epilogue, and the dependent per-layer chain built from them.
+
+Each fused step must give the same bits as the separate calls it replaces (whose arithmetic is
+checked against the CPU checker elsewhere); the records themselves are checked against the
+checker's Q8_K quantizer, integer for integer."""
+import numpy as np
+import pytest
+
+from bpd_substrate_b200 import capi, synth
+from bpd_substrate_b200.dispatch import DecodeChain
+from tests.util import Dev, normwise
+
+pytestmark = pytest.mark.gpu
+
+
+def decode_records(raw, K):
+    """records -> (int8 [K], int sums of 32 [K/32], fp32 scale per 256 [K/256])."""
+    rec = np.asarray(raw, np.uint8)[: K // 128 * 144].reshape(K // 128, 144)
+    q = rec[:, :128].copy().view(np.int8).reshape(K)
+    sums = rec[:, 128:136].copy().view(np.int16).reshape(K // 32).astype(np.int64)
+    d = rec[:, 136:140].copy().view(np.float32).reshape(K // 128)
+    assert np.array_equal(d[0::2].view(np.uint32), d[1::2].view(np.uint32))   # both halves carry the block scale
+    return q, sums, d[0::2]
+
+
+def decode_q8k(blocks, K):
+    """the checker's 292-byte blocks -> the same triple."""
+    b = np.asarray(blocks, np.uint8).reshape(K // 256, 292)
+    d = b[:, :4].copy().view(np.float32).reshape(K // 256)
+    q = b[:, 4:260].copy().view(np.int8).reshape(K)
+    bs = b[:, 260:292].copy().view(np.int16).reshape(K // 16).astype(np.int64)
+    return q, bs[0::2] + bs[1::2], d
+
+
+def records_of(lib, x):
+    K = x.size
+    dX, dR = Dev(lib, x), Dev(lib, nbytes=lib.bpdq_records_bytes(K), fill=0xEE)
+    assert lib.bpd_quant_q8k_records_cuda(dX.ptr, dR.ptr, K, None) == 0
+    lib.bpdq_sync()
+    return dR.read(np.uint8)
+
+
+@pytest.mark.parametrize("K", [256, 4096, 14336])
+def test_records_match_checker_quantizer(lib, oracle, K):
+    rng = np.random.default_rng(K)
+    x = rng.standard_normal(K, dtype=np.float32) * 3
+    if K > 256:
+        x[K // 2: K // 2 + 256] = 0.0      # an all-zero block: scale 0, multiplier 0
+    assert lib.bpdq_records_bytes(K) == K // 128 * 144
+    q, sums, d = decode_records(records_of(lib, x), K)
+    q_ref, sums_ref, d_ref = decode_q8k(oracle.quant_q8_K(x), K)
+    assert np.array_equal(q, q_ref)
+    assert np.array_equal(sums, sums_ref)
+    assert np.array_equal(d.view(np.uint32), d_ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("rows,K", [(1, 4096), (3, 512), (2, 14336)])
+def test_rmsnorm_records_equal_separate_calls(lib, rows, K):
+    rng = np.random.default_rng(rows * K)
+    x = rng.standard_normal((rows, K), dtype=np.float32) * 5
+    w = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    dX, dW, dH = Dev(lib, x), Dev(lib, w), Dev(lib, nbytes=rows * K * 4)
+    rb = lib.bpdq_records_bytes(K)
+    dR = Dev(lib, nbytes=rows * rb, fill=0xEE)
+    assert lib.bpd_rmsnorm_q8k_records_cuda(dX.ptr, dW.ptr, dR.ptr, rows, K, 1e-5, None) == 0
+    lib.gpu_rms_norm(dX.ptr, dW.ptr, dH.ptr, rows, K, 1e-5)
+    lib.bpdq_sync()
+    h = dH.read(np.float32).reshape(rows, K)
+    fused = dR.read(np.uint8).reshape(rows, rb)
+    for r in range(rows):
+        assert np.array_equal(fused[r], records_of(lib, h[r])), r
+
+
+def test_swiglu_records_equal_separate_calls(lib):
+    K = 14336
+    rng = np.random.default_rng(77)
+    g = rng.standard_normal(K, dtype=np.float32) * 6
+    g[:8] = [-200.0, 200.0, -90.0, 90.0, 0.0, -0.0, 1e-30, -1e-30]     # exp overflow/underflow ends
+    u = rng.standard_normal(K, dtype=np.float32) * 2
+    dG, dU, dT = Dev(lib, g), Dev(lib, u), Dev(lib, nbytes=K * 4)
+    dR = Dev(lib, nbytes=lib.bpdq_records_bytes(K), fill=0xEE)
+    assert lib.bpd_swiglu_q8k_records_cuda(dG.ptr, dU.ptr, dR.ptr, K, None) == 0
+    lib.gpu_silu(dG.ptr, dT.ptr, K)
+    lib.gpu_mul(dT.ptr, dU.ptr, dT.ptr, K)
+    lib.bpdq_sync()
+    assert np.array_equal(dR.read(np.uint8), records_of(lib, dT.read(np.float32)))
+
+
+def test_products_over_records_and_residual_epilogue(lib, oracle):
+    K = 2048
+    shapes = [(96, K), (40, K), (130, K)]
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal(K, dtype=np.float32)
+    Ws = [synth.q4k_matrix(m, k, rng) for m, k in shapes]
+    prev = [rng.standard_normal(m, dtype=np.float32) * 100 for m, _ in shapes]
+    dX, dWs = Dev(lib, x), [Dev(lib, w) for w in Ws]
+    dR = Dev(lib, nbytes=lib.bpdq_records_bytes(K))
+    assert lib.bpd_quant_q8k_records_cuda(dX.ptr, dR.ptr, K, None) == 0
+    # the separate path: each product through the batched entry (its own quantizer launch)
+    plain = []
+    ws = Dev(lib, nbytes=lib.bpdq_records_bytes(K) + 4096)
+    for (m, k), dW in zip(shapes, dWs):
+        dO = Dev(lib, nbytes=m * 4, fill=0xFF)
+        d = (capi.GemvDesc * 1)(capi.GemvDesc(dW.ptr, dX.ptr, dO.ptr, m, k))
+        assert lib.bpd_qmatmul_q4k_q8k_batch_ws_cuda(1, d, ws.ptr, ws.nbytes, None) == 0
+        lib.bpdq_sync()
+        plain.append(dO.read(np.float32))
+    xq = oracle.quant_q8_K(x)
+    for (m, k), W, got in zip(shapes, Ws, plain):
+        _, ref64 = oracle.qmatmul_q4k_q8k(W, xq, m, k)
+        assert normwise(got, ref64) <= 1e-5
+    # one launch over the records: overwrite, accumulate, overwrite
+    outs = [Dev(lib, p) for p in prev]
+    descs = (capi.GemvDesc * 3)(*[capi.GemvDesc(dW.ptr, None, o.ptr, m, k) for (m, k), dW, o in zip(shapes, dWs, outs)])
+    assert lib.bpd_qmatmul_q4k_records_cuda(3, descs, dR.ptr, 0b010, None) == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == 0
+    for j, (o, p, pl) in enumerate(zip(outs, prev, plain)):
+        want = p + pl if j == 1 else pl
+        assert np.array_equal(o.read(np.float32).view(np.uint32), want.astype(np.float32).view(np.uint32)), j
+
+
+def test_products_over_records_reject_bad_calls(lib):
+    d = Dev(lib, nbytes=1 << 16)
+    descs = (capi.GemvDesc * 2)(capi.GemvDesc(d.ptr, None, d.ptr, 8, 256), capi.GemvDesc(d.ptr, None, d.ptr, 8, 512))
+    assert lib.bpd_qmatmul_q4k_records_cuda(2, descs, d.ptr, 0, None) == -1      # different K
+    assert lib.bpd_qmatmul_q4k_records_cuda(0, descs, d.ptr, 0, None) == -1
+    assert lib.bpd_qmatmul_q4k_records_cuda(1, descs, None, 0, None) == -1
+    assert lib.bpd_quant_q8k_records_cuda(d.ptr, d.ptr, 100, None) == -1
+    assert lib.bpd_swiglu_q8k_records_cuda(d.ptr, d.ptr + 4, d.ptr, 256, None) == -2
+    lib.bpdq_clear_status()
+
+
+@pytest.fixture(scope="module")
+def chain(lib):
+    c = DecodeChain(hidden=512, kv=256, ffn=1024, n_layers=3, seed=11, lib=lib)
+    yield c
+    c.close()
+
+
+def test_chain_fused_equals_reference_call_sequence(chain):
+    """4 and 8 launches per layer against the reference's 13-call sequence on the same weights: same
+    bits, directly enqueued and replayed from a CUDA graph."""
+    rng = np.random.default_rng(5)
+    x0 = rng.standard_normal(chain.hidden, dtype=np.float32)
+    results = []
+    for mode in ("chain-separate", "chain4", "chain", "chain-graph"):
+        chain.set_state(x0)
+        if mode == "chain-graph":
+            chain.capture("chain")       # (the capture's warm-up runs advance the state: reset it)
+            chain.set_state(x0)
+            chain.step("chain")
+        else:
+            chain.enqueue_token(mode)
+        results.append(chain.get_state())
+        assert chain.lib.bpdq_last_status() == 0
+    assert np.isfinite(results[0]).all()
+    for other in results[1:]:
+        assert np.array_equal(results[0].view(np.uint32), other.view(np.uint32))
+    assert [chain.launches_per_token(m) for m in ("chain", "chain4", "chain-separate")] == [24, 12, 39]
+
+
+def test_chain_layer_against_cpu_restatement(chain, oracle):
+    """One layer recomputed on the CPU from the checker's pieces (wiring check: which matrix, which
+    vector, where the residual goes).  rms_norm there is evaluated in binary64, so a quantized
+    activation may differ by one step here and there; the bound allows for that and for nothing
+    structural (a wrong matrix or a missing residual is an O(1) difference)."""
+    rng = np.random.default_rng(6)
+    x0 = rng.standard_normal(chain.hidden, dtype=np.float32)
+    H, KV, F = chain.hidden, chain.kv, chain.ffn
+
+    def prod(layer, m, vec):
+        _, rows, cols = chain.shapes[m]
+        return oracle.qmatmul_q4k_q8k(chain.host_weight(layer, m), oracle.quant_q8_K(vec), rows, cols)[0]
+
+    x = x0.copy()
+    for layer in range(chain.n_layers):
+        h = oracle.rms_norm(x, chain.norm_host[layer, 0], 1, H, chain.eps).ravel()
+        q = prod(layer, 0, h)
+        x = x + prod(layer, 3, q)
+        h = oracle.rms_norm(x, chain.norm_host[layer, 1], 1, H, chain.eps).ravel()
+        g, u = prod(layer, 4, h), prod(layer, 5, h)
+        with np.errstate(over="ignore"):
+            act = (g / (np.float32(1) + np.exp(-g, dtype=np.float32))) * u
+        x = x + prod(layer, 6, act.astype(np.float32))
+    chain.set_state(x0)
+    chain.enqueue_token("chain")
+    got = chain.get_state()
+    assert normwise(got, x) <= 1e-2
+
+
+@pytest.mark.parametrize("prologue", [0, 1, 2])
+def test_fused_product_equals_records_path(lib, prologue):
+    """bpd_qmatmul_q4k_fused_cuda against the producer kernel + product over records, shapes of the
+    benchmark's layer (K = 4096 and 14336, several matrices per launch, residual on one of them)."""
+    K = 14336 if prologue == 2 else 4096
+    shapes = [(4096, K)] if prologue == 2 else [(1024, K), (4096, K), (260, K)]
+    rng = np.random.default_rng(40 + prologue)
+    a = rng.standard_normal(K, dtype=np.float32) * 4
+    b = (1 + 0.1 * rng.standard_normal(K)).astype(np.float32) if prologue == 1 else rng.standard_normal(K, dtype=np.float32)
+    Ws = [synth.q4k_matrix(m, k, rng) for m, k in shapes]
+    prev = [rng.standard_normal(m, dtype=np.float32) * 50 for m, _ in shapes]
+    dA, dB, dWs = Dev(lib, a), Dev(lib, b), [Dev(lib, w) for w in Ws]
+    dR = Dev(lib, nbytes=lib.bpdq_records_bytes(K))
+    mask = 0b001
+    got = []
+    for fused in (False, True):
+        outs = [Dev(lib, p) for p in prev]
+        descs = (capi.GemvDesc * len(shapes))(*[capi.GemvDesc(dW.ptr, None, o.ptr, m, k)
+                                                for (m, k), dW, o in zip(shapes, dWs, outs)])
+        if fused:
+            assert lib.bpd_qmatmul_q4k_fused_cuda(len(shapes), descs, prologue, dA.ptr, dB.ptr if prologue else None,
+                                                  1e-5, mask, None) == 0
+        else:
+            if prologue == 0:
+                assert lib.bpd_quant_q8k_records_cuda(dA.ptr, dR.ptr, K, None) == 0
+            elif prologue == 1:
+                assert lib.bpd_rmsnorm_q8k_records_cuda(dA.ptr, dB.ptr, dR.ptr, 1, K, 1e-5, None) == 0
+            else:
+                assert lib.bpd_swiglu_q8k_records_cuda(dA.ptr, dB.ptr, dR.ptr, K, None) == 0
+            assert lib.bpd_qmatmul_q4k_records_cuda(len(shapes), descs, dR.ptr, mask, None) == 0
+        lib.bpdq_sync()
+        assert lib.bpdq_last_status() == 0
+        got.append([o.read(np.uint32) for o in outs])
+    for x, y in zip(*got):
+        assert np.array_equal(x, y)
