@@ -998,7 +998,7 @@ __global__ void __launch_bounds__(256) k_vector_records(const float* __restrict_
     }
 }
 
-template <int R, int LAYOUT>
+template <int R, int LAYOUT, int ACC>
 __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8_t* xq, const BatchProblem& pb, int row0,
                                            int lane)
 {
@@ -1036,12 +1036,13 @@ __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8
     const float total = fold_rows<R>(v, lane);
     constexpr int kLanesPerRow = 32 / R;
     const int my_row = lane / kLanesPerRow;
-    // (the residual stream was written by an earlier launch: read it past L1)
+    // ACC: launches with a residual epilogue are a separate instantiation (the conditional costs the
+    // plain product 2 % of its bandwidth); the residual stream was written by an earlier launch: read it past L1
     if ((lane % kLanesPerRow) == 0 && my_row < rows)
-        pb.out[row0 + my_row] = pb.accumulate ? __ldcg(pb.out + row0 + my_row) + total : total;
+        pb.out[row0 + my_row] = (ACC && pb.accumulate) ? __ldcg(pb.out + row0 + my_row) + total : total;
 }
 
-template <int FMT, int LAYOUT, int MAXTHREADS>
+template <int FMT, int LAYOUT, int MAXTHREADS, int ACC>
 __global__ void __launch_bounds__(MAXTHREADS, 1)
 k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
 {
@@ -1206,9 +1207,9 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
         const int row0 = (v - pb.tile_begin) * pb.rt;
         const uint8_t* tile_smem = ring + (size_t)s * p.slot_bytes;
         if (FMT == 0) {
-            if (pb.rt == 4) batch_tile<4, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-            else if (pb.rt == 2) batch_tile<2, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-            else batch_tile<1, LAYOUT>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+            if (pb.rt == 4) batch_tile<4, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+            else if (pb.rt == 2) batch_tile<2, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+            else batch_tile<1, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane);
         } else {
             if (pb.rt == 4) batch_tile_q80<4>(tile_smem, xq + pb.xq_off, pb, row0, lane);
             else if (pb.rt == 2) batch_tile_q80<2>(tile_smem, xq + pb.xq_off, pb, row0, lane);
@@ -1298,10 +1299,14 @@ static int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt = 0)
     return 0;
 }
 
-template <int FMT, int LAYOUT>
+template <int FMT, int LAYOUT, int ACC = 0>
 static int launch_batch(const BatchPlan& p, cudaStream_t s)
 {
-    auto kern = k_gemv_batch_q4k_q8k<FMT, LAYOUT, kMidCtaThreads>;
+    if (ACC == 0) {
+        for (int j = 0; j < p.n_problems; j++)
+            if (p.prob[j].accumulate) return launch_batch<FMT, LAYOUT, 1>(p, s);
+    }
+    auto kern = k_gemv_batch_q4k_q8k<FMT, LAYOUT, kMidCtaThreads, ACC>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
