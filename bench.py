@@ -33,10 +33,11 @@ UNIT = "GB/s"
 WORKLOAD = "mistral7b_layer_set_x32_q4k_decode_batch1"
 N_LAYERS = 32
 KERNEL_OF = {"batched": "k_gemv_batch_q4k_q8k", "grouped": "k_gemv_q4k_q8k", "separate": "k_gemv_q4k_q8k",
-             "chain": "k_gemv_batch_q4k_q8k", "chain4": "k_gemv_batch_q4k_q8k", "chain-separate": "k_gemv_batch_q4k_q8k"}
+             "chain": "k_gemv_batch_q4k_q8k", "chain4": "k_gemv_batch_q4k_q8k", "chain-separate": "k_gemv_batch_q4k_q8k",
+             "chain-persistent": "k_decode_chain"}
 # DRAM traffic / algorithmic bytes measured with ncu (profiles/*.md): nothing is re-read
 TRAFFIC_PER_ALGORITHMIC = {"batched": 1.03, "grouped": 1.00, "separate": 1.00, "chain": 1.03, "chain4": 1.03,
-                           "chain-separate": 1.03}
+                           "chain-separate": 1.03, "chain-persistent": 1.03}
 
 
 def measured_peak():
@@ -215,7 +216,7 @@ def run_gpu(args):
         o_floats = args.tokens * args.layers * sum(rows // shard[1] for _, rows, _ in shapes)
         out_local = torch.empty(o_floats, dtype=torch.float32, device="cuda")
     schedule = args.schedule
-    chain = schedule in ("chain", "chain4", "chain-separate")
+    chain = schedule in ("chain", "chain4", "chain-separate", "chain-persistent")
     if chain:
         # the same seven matrices per layer as a DEPENDENT chain (every product reads what the step
         # before it wrote), with the elementwise steps of the reference's decode loop in between
@@ -231,6 +232,7 @@ def run_gpu(args):
     # launches of the dominant kernel (the batched schedule adds one small quantizer per layer,
     # which overlaps the previous GEMV kernel and is counted in the step time)
     main_launches = args.layers if schedule == "batched" else (
+        1 if schedule == "chain-persistent" else
         (7 if schedule == "chain-separate" else 4) * args.layers if chain else launches)
     x_host = lib.bpdq_host_alloc(ls.x_bytes)
     o_host = lib.bpdq_host_alloc(ls.o_bytes)
@@ -366,12 +368,13 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--schedule", default="batched", choices=["batched", "grouped", "separate", "chain", "chain4", "chain-separate"],
+    ap.add_argument("--schedule", default="batched", choices=["batched", "grouped", "separate", "chain", "chain4", "chain-separate", "chain-persistent"],
                     help="batched: the benchmark (a layer's seven independent products in one launch); grouped / "
                          "separate: fewer products per launch; chain: the seven products as a dependent decode chain, "
                          "rms_norm / SwiGLU as small kernels writing quantized records, residual add in the product's "
                          "epilogue (8 launches per layer); chain4: the steps inside the product kernels (4); "
-                         "chain-separate: the reference's 13-call sequence per layer")
+                         "chain-separate: the reference's 13-call sequence per layer; chain-persistent: the whole token as "
+                         "one cooperative launch with grid-wide barriers between dependent phases")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="mistral7b", choices=["mistral7b", "llama70b"],
                     help="mistral7b: the benchmark (every rank a full layer set, weak scaling); llama70b: the "

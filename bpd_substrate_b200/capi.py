@@ -86,6 +86,9 @@ SIGNATURES = {
     "bpd_swiglu_q8k_records_cuda": (i32, [vp, vp, vp, i32, vp]),
     "bpd_qmatmul_q4k_records_cuda": (i32, [i32, vp, vp, C.c_uint, vp]),
     "bpd_qmatmul_q4k_fused_cuda": (i32, [i32, vp, i32, vp, vp, f32, C.c_uint, vp]),
+    "bpdq_chain_create": (vp, [i32, vp]),
+    "bpdq_chain_run": (i32, [vp, vp]),
+    "bpdq_chain_destroy": (None, [vp]),
     "bpd_qmatmul_q4k_q8k_batch_ws_cuda": (i32, [i32, vp, vp, sz, vp]),
     "bpdq_batch_workspace_bytes": (sz, [i32, vp]),
     "bpd_qmatmul_q4k_q8k_batch_static_cuda": (i32, [i32, vp, vp]),
@@ -143,6 +146,12 @@ def load(build_if_missing=True):
 class GemvDesc(C.Structure):
     """bpdq_gemv_desc: one product of a batched launch."""
     _fields_ = [("W", vp), ("x", vp), ("out", vp), ("M", i32), ("K", i32)]
+
+
+class ChainPhase(C.Structure):
+    """bpdq_chain_phase: one phase of a persistent decode chain."""
+    _fields_ = [("n", i32), ("prologue", i32), ("a", vp), ("b", vp), ("eps", f32), ("accumulate_mask", C.c_uint),
+                ("prod", GemvDesc * 3)]
 
 
 class BpdqError(RuntimeError):

@@ -235,10 +235,14 @@ class DecodeChain:
       (``bpd_qmatmul_q4k_fused_cuda``), in every CTA.  Fewer launches, but 148 CTAs repeat the step
       after the wait for the previous launch: measured slower than ``"chain"`` on the benchmark's shapes;
     * ``"chain-separate"`` -- the reference's call sequence (gpu_rms_norm, gpu_silu, gpu_mul,
-      gpu_add and one product per matrix).
+      gpu_add and one product per matrix);
+    * ``"chain-persistent"`` -- ONE cooperative launch per token (plus the memset of its barrier
+      counters): the 4-phase program of ``"chain4"`` for all layers inside one kernel whose producer
+      warps stream the weights of all phases back to back (``bpdq_chain_run``).
     """
 
-    MODES = {"chain": 8, "chain4": 4, "chain-separate": 13}
+    MODES = {"chain": 8, "chain4": 4, "chain-separate": 13, "chain-persistent": 0}
+
     NAMES = ("wq", "wk", "wv", "wo", "w1", "w3", "w2")
 
     def __init__(self, hidden=4096, kv=1024, ffn=14336, n_layers=32, seed=3000, eps=1e-5, lib=None):
@@ -271,6 +275,7 @@ class DecodeChain:
         self.ws_bytes = lib.bpdq_records_bytes(ffn) + 4096
         self.stream = lib.bpdq_stream_create()
         self.graph = {}
+        self.program = None        # handle of the persistent-chain program, built on first use
         capi.check(lib.bpdq_last_status(), "DecodeChain setup")
 
     def host_weight(self, layer, m):
@@ -290,7 +295,8 @@ class DecodeChain:
         return "chain" if mode else "chain-separate"
 
     def launches_per_token(self, mode="chain"):
-        return self.n_layers * self.MODES[self._mode(mode)]
+        mode = self._mode(mode)
+        return 1 if mode == "chain-persistent" else self.n_layers * self.MODES[mode]
 
     # ---- state
     def set_state(self, x):
@@ -316,6 +322,24 @@ class DecodeChain:
         lib, s, b, r = self.lib, (stream if stream is not None else self.stream), self.buf, self.rec
         H, F, eps = self.hidden, self.ffn, self.eps
         mode = self._mode(mode)
+        if mode == "chain-persistent":
+            if self.program is None:
+                ph = (capi.ChainPhase * (4 * self.n_layers))()
+                for layer in range(self.n_layers):
+                    for k, (members, outs, pro, a, bb, mask) in enumerate((
+                            ((0, 1, 2), ("q", "k", "v"), 1, b["x"], self.norm_ptr(layer, 0), 0),
+                            ((3,), ("x",), 0, b["q"], None, 1),
+                            ((4, 5), ("gate", "up"), 1, b["x"], self.norm_ptr(layer, 1), 0),
+                            ((6,), ("x",), 2, b["gate"], b["up"], 1))):
+                        p = ph[4 * layer + k]
+                        p.n, p.prologue, p.a, p.b, p.eps, p.accumulate_mask = len(members), pro, a, bb, eps, mask
+                        for j, d in enumerate(self._descs(layer, members, outs)):
+                            p.prod[j] = d
+                self.program = lib.bpdq_chain_create(len(ph), ph)
+                if not self.program:
+                    raise capi.BpdqError(f"chain program rejected (status {lib.bpdq_last_status()})")
+            capi.check(lib.bpdq_chain_run(self.program, s), "persistent chain launch")
+            return
         if mode == "chain4":
             for layer in range(self.n_layers):
                 capi.check(lib.bpd_qmatmul_q4k_fused_cuda(3, self._descs(layer, (0, 1, 2), ("q", "k", "v")), 1, b["x"],
@@ -414,6 +438,9 @@ class DecodeChain:
             for p in ptrs:
                 lib.bpdq_free(p)
         self.weights = []
+        if self.program:
+            lib.bpdq_chain_destroy(self.program)
+            self.program = None
         for p in list(self.buf.values()) + list(self.rec.values()) + [self.d_norm, self.ws]:
             lib.bpdq_free(p)
         lib.bpdq_stream_destroy(self.stream)

@@ -199,6 +199,23 @@ int bpd_qmatmul_q4k_records_cuda(int n, const bpdq_gemv_desc* descs, const void*
  * out_j[M_j] (+)= W_j[M_j][K] . q8K(x), n <= 8 matrices with the same K.  Same bits as the separate calls. */
 int bpd_qmatmul_q4k_fused_cuda(int n, const bpdq_gemv_desc* descs, int prologue, const float* a, const float* b, float eps,
                                unsigned accumulate_mask, void* stream);
+/* A whole chain of dependent phases (each: step, quantize, up to three products with the same K,
+ * optional residual adds) as ONE cooperative launch of one CTA per SM: the weights of all phases
+ * stream back to back through the shared-memory ring, the consumer warps meet at a grid-wide barrier
+ * (bounded wait, status -4 on a timeout) between phases.  The program is planned and uploaded once
+ * (bpdq_chain_create, which allocates device memory), then run once per token.  Phase fields as the
+ * arguments of bpd_qmatmul_q4k_fused_cuda.  Same bits as the separate calls. */
+typedef struct bpdq_chain_phase {
+    int n, prologue;
+    const float* a;
+    const float* b;
+    float eps;
+    unsigned accumulate_mask;
+    bpdq_gemv_desc prod[3];
+} bpdq_chain_phase;
+void* bpdq_chain_create(int n_phases, const bpdq_chain_phase* phases);   /* NULL on error (bpdq_last_status) */
+int bpdq_chain_run(void* chain, void* stream);
+void bpdq_chain_destroy(void* chain);
 /* out[tokens][M]; layout 0/1 as above; xsrc 0: x is float [tokens][K], 1: x is Q8_K blocks
  * [tokens][K/256]; subdots (may be NULL): int32 [M][K/256][8], token 0's exact sub-block dots */
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,

@@ -145,12 +145,13 @@ def test_chain_fused_equals_reference_call_sequence(chain):
     rng = np.random.default_rng(5)
     x0 = rng.standard_normal(chain.hidden, dtype=np.float32)
     results = []
-    for mode in ("chain-separate", "chain4", "chain", "chain-graph"):
+    for mode in ("chain-separate", "chain4", "chain", "chain-persistent", "chain-graph", "chain-persistent", "persistent-graph"):
         chain.set_state(x0)
-        if mode == "chain-graph":
-            chain.capture("chain")       # (the capture's warm-up runs advance the state: reset it)
+        if mode.endswith("-graph"):
+            which = "chain" if mode == "chain-graph" else "chain-persistent"
+            chain.capture(which)         # (the capture's warm-up runs advance the state: reset it)
             chain.set_state(x0)
-            chain.step("chain")
+            chain.step(which)
         else:
             chain.enqueue_token(mode)
         results.append(chain.get_state())
