@@ -86,6 +86,15 @@ SIGNATURES = {
     "bpd_swiglu_q8k_records_cuda": (i32, [vp, vp, vp, i32, vp]),
     "bpd_qmatmul_q4k_records_cuda": (i32, [i32, vp, vp, C.c_uint, vp]),
     "bpd_qmatmul_q4k_fused_cuda": (i32, [i32, vp, i32, vp, vp, f32, C.c_uint, vp]),
+    "bpd_rmsnorm_llama_cuda": (i32, [vp, vp, vp, i32, i32, f32, vp]),
+    "bpd_rope_norm_freqs_cuda": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, f32, vp]),
+    "bpd_kv_cache_write_f16_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "bpd_kv_cache_write_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "bpd_gqa_attn_cuda": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, f32, i32, i32, vp]),
+    "bpd_swiglu_fuse_cuda": (i32, [vp, vp, vp, i32, vp]),
+    "bpd_argmax_dim_cuda": (i32, [vp, vp, i32, i32, i32, vp]),
+    "bpd_llama_block_cuda": (i32, [vp, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
+    "bpd_llama_forward_cuda": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "bpdq_chain_create": (vp, [i32, vp]),
     "bpdq_chain_run": (i32, [vp, vp]),
     "bpdq_chain_destroy": (None, [vp]),
@@ -152,6 +161,24 @@ class ChainPhase(C.Structure):
     """bpdq_chain_phase: one phase of a persistent decode chain."""
     _fields_ = [("n", i32), ("prologue", i32), ("a", vp), ("b", vp), ("eps", f32), ("accumulate_mask", C.c_uint),
                 ("prod", GemvDesc * 3)]
+
+
+class LlamaConfig(C.Structure):
+    """bpd_llama_config (bench/bpd_cpu.c:5537-5553 of the reference)."""
+    _fields_ = [(n, i32) for n in ("n_layers", "n_heads", "n_kv_heads", "head_dim", "embed_dim", "ffn_dim", "vocab_size",
+                                   "max_seq_len")] + [("rms_eps", f32), ("rope_base", f32), ("rope_dim", i32),
+                                                      ("kv_cache_f16", i32)]
+
+
+class LlamaLayerWeights(C.Structure):
+    """bpd_llama_layer_weights: nine pointers in the reference's order."""
+    _fields_ = [(n, vp) for n in ("attn_norm_w", "w_q", "w_k", "w_v", "w_o", "ffn_norm_w", "w_gate", "w_up", "w_down")]
+
+
+class LlamaWeights(C.Structure):
+    """bpd_llama_weights; `layers` points to a host array of LlamaLayerWeights."""
+    _fields_ = [("token_embd", vp), ("layers", C.POINTER(LlamaLayerWeights)), ("output_norm_w", vp), ("output_w", vp),
+                ("rope_freqs", vp)]
 
 
 class BpdqError(RuntimeError):

@@ -1,0 +1,427 @@
+// Q8_0 Llama forward on the device: the composition of bpd_llama_block_cpu / bpd_llama_forward_cpu
+// (bench/bpd_cpu.c:5608-5798 of the reference) out of the Q8_0 products of q8_0.cu / gemv_q4k.cu and
+// the small kernels below, which restate the reference's own steps:
+//   rms_norm with a binary64 sum of squares        bench/bpd_cpu.c:4959-4988
+//   rotary embedding, NORM pairing, freq factors   bench/bpd_cpu.c:5146-5183
+//   f16 KV-cache write (round to nearest even)     bench/bpd_cpu.c:5240-5257
+//   grouped-query attention, three-pass softmax    bench/bpd_cpu.c:5370-5433
+//   SwiGLU, residual add, argmax (lowest index)    bench/bpd_cpu.c:5504-5507, 5466, 4512-4529
+// Weights, caches and activations are device memory; the descriptor structs are host memory holding
+// device pointers, with the reference's field order.  Everything runs on one stream in the reference's
+// order; no kernel waits on another.
+#include "bpdq_common.cuh"
+#include "../../include/bpdq.h"
+
+#include <cuda_fp16.h>
+
+namespace bpdq {
+
+// One CTA per row.  The reference adds the squares in binary64 in index order and rounds the mean
+// to fp32; here 256 threads add strided partial sums in binary64 and a tree joins them.  The
+// binary64 sums differ by ~1e-16 relative, which vanishes in the rounding to fp32 except when the
+// mean sits within that distance of a rounding boundary.
+__global__ void __launch_bounds__(256) k_rmsnorm_llama(const float* __restrict__ in, const float* __restrict__ w,
+                                                        float* __restrict__ out, int cols, float eps)
+{
+    __shared__ double s_part[8];
+    const float* x = in + (size_t)blockIdx.x * cols;
+    float* y = out + (size_t)blockIdx.x * cols;
+    double t = 0.0;
+    for (int c = threadIdx.x; c < cols; c += 256) {
+        const double v = (double)x[c];
+        t += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = t;
+    __syncthreads();
+    double tot = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += s_part[i];
+    const float mean = (float)(tot / (double)cols);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    for (int c = threadIdx.x; c < cols; c += 256) {
+        const float v = __fmul_rn(x[c], scale);
+        y[c] = w ? __fmul_rn(v, w[c]) : v;
+    }
+}
+
+// The reference's libm returns the correctly rounded fp32 value of expf / cosf / sinf for all but
+// a fraction of a percent of arguments; the device's fp32 versions are 1-2 ulp off for about half of
+// them.  Such last-bit differences are harmless by themselves, but every product that follows
+// re-quantizes its input to int8, where a last-bit difference now and then flips a rounding and
+// becomes a 1e-3 difference.  So these small kernels evaluate in binary64 and round once.
+__device__ __forceinline__ float exp_rounded(float x) { return (float)exp((double)x); }
+__device__ __forceinline__ float cos_rounded(float x) { return (float)cos((double)x); }
+__device__ __forceinline__ float sin_rounded(float x) { return (float)sin((double)x); }
+
+// In place or out of place.  Thread = (token, head, pair).  theta is reached as the reference reaches
+// it, by repeated multiplication from (float)pos, so that the angle has the same bits.
+__global__ void __launch_bounds__(256) k_rope_norm(const float* __restrict__ in, float* __restrict__ out,
+                                                    const int32_t* __restrict__ pos_ids, const float* __restrict__ freq_factors,
+                                                    int n_tokens, int n_heads, int head_dim, int n_dims, float theta_scale)
+{
+    const int half = n_dims / 2;
+    const long total = (long)n_tokens * n_heads * (head_dim / 2);
+    for (long u = (long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long)gridDim.x * blockDim.x) {
+        const int pair = (int)(u % (head_dim / 2));
+        const long th = u / (head_dim / 2);
+        const int t = (int)(th / n_heads);
+        const float* src = in + th * head_dim;
+        float* dst = out + th * head_dim;
+        const float x0 = src[2 * pair], x1 = src[2 * pair + 1];
+        if (pair < half) {
+            float theta = (float)pos_ids[t];
+            for (int i = 0; i < pair; i++) theta = __fmul_rn(theta, theta_scale);
+            const float ff = freq_factors ? freq_factors[pair] : 1.0f;
+            const float te = __fdiv_rn(theta, ff);
+            const float c = cos_rounded(te), s = sin_rounded(te);
+            dst[2 * pair] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+            dst[2 * pair + 1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+        } else {
+            dst[2 * pair] = x0;
+            dst[2 * pair + 1] = x1;
+        }
+    }
+}
+
+// cache[pos[t]][:] = f16(src[t][:]) (round to nearest even) or the fp32 copy
+template <int F16>
+__global__ void __launch_bounds__(256) k_kv_write(void* __restrict__ cache, const float* __restrict__ src,
+                                                   const int32_t* __restrict__ pos_ids, int n_tokens, int row)
+{
+    const long total = (long)n_tokens * row;
+    for (long u = (long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long)gridDim.x * blockDim.x) {
+        const int t = (int)(u / row), i = (int)(u - (long)t * row);
+        const size_t at = (size_t)pos_ids[t] * row + i;
+        if (F16) reinterpret_cast<__half*>(cache)[at] = __float2half_rn(src[u]);
+        else reinterpret_cast<float*>(cache)[at] = src[u];
+    }
+}
+
+// One CTA per (query token, query head).  As in the reference, ALL n_kv cache rows take part: rows
+// past the query's position score -1e38 and contribute exp(-huge) = 0.  Scores: raw dot products
+// (multiply, then add, in index order, one thread per cache row), scaled afterwards; maximum; exp and
+// sum (added in index order by one thread, as the reference adds them); normalisation by the
+// reciprocal; then thread d adds v[ic][d] * w[ic] over the rows in order.
+template <int F16>
+__global__ void __launch_bounds__(256) k_gqa_attn(const float* __restrict__ q, const void* __restrict__ kc,
+                                                   const void* __restrict__ vc, float* __restrict__ dst, int n_kv,
+                                                   int n_q_heads, int n_kv_heads, int head_dim, float scale, int kv_offset)
+{
+    extern __shared__ float sh[];
+    float* scores = sh;                   // [n_kv]
+    float* sq = sh + n_kv;                // [head_dim]
+    __shared__ float s_red[8];
+    const int qt = blockIdx.x / n_q_heads, iq = blockIdx.x % n_q_heads;
+    const int kv_head = iq / (n_q_heads / n_kv_heads);
+    const int q_pos = kv_offset + qt;
+    const float* pq = q + ((size_t)qt * n_q_heads + iq) * head_dim;
+    float* pdst = dst + ((size_t)qt * n_q_heads + iq) * head_dim;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int d = tid; d < head_dim; d += 256) sq[d] = pq[d];
+    __syncthreads();
+    auto load = [&](const void* base, size_t idx) -> float {
+        return F16 ? __half2float(reinterpret_cast<const __half*>(base)[idx]) : reinterpret_cast<const float*>(base)[idx];
+    };
+    float mx = -1e38f;
+    for (int ic = tid; ic < n_kv; ic += 256) {
+        const size_t row = ((size_t)ic * n_kv_heads + kv_head) * head_dim;
+        float s = 0.0f;
+        for (int d = 0; d < head_dim; d++) s = __fadd_rn(s, __fmul_rn(sq[d], load(kc, row + d)));
+        const float sv = (ic <= q_pos) ? __fmul_rn(s, scale) : -1e38f;
+        scores[ic] = sv;
+        mx = fmaxf(mx, sv);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    mx = s_red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) mx = fmaxf(mx, s_red[i]);
+    __syncthreads();
+    for (int ic = tid; ic < n_kv; ic += 256) scores[ic] = exp_rounded(__fsub_rn(scores[ic], mx));
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.0f;
+        for (int ic = 0; ic < n_kv; ic++) t = __fadd_rn(t, scores[ic]);
+        s_red[0] = t;
+    }
+    __syncthreads();
+    const float sum = s_red[0];
+    const float inv = (sum == 0.0f) ? 0.0f : __fdiv_rn(1.0f, sum);
+    for (int ic = tid; ic < n_kv; ic += 256) scores[ic] = __fmul_rn(scores[ic], inv);
+    __syncthreads();
+    for (int d = tid; d < head_dim; d += 256) {
+        float acc = 0.0f;
+        for (int ic = 0; ic < n_kv; ic++)
+            acc = __fadd_rn(acc, __fmul_rn(load(vc, ((size_t)ic * n_kv_heads + kv_head) * head_dim + d), scores[ic]));
+        pdst[d] = acc;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_swiglu_f32(const float* __restrict__ gate, const float* __restrict__ up,
+                                                     float* __restrict__ dst, long n)
+{
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const float g = gate[i];
+        dst[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, exp_rounded(-g))), up[i]);
+    }
+}
+__global__ void __launch_bounds__(256) k_add_f32(const float* a, const float* b, float* dst, long n)
+{
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+        dst[i] = __fadd_rn(a[i], b[i]);
+}
+
+// One CTA per row; the largest value wins, the lowest index among equals (v > best in index order).
+__global__ void __launch_bounds__(256) k_argmax_rows(const float* __restrict__ x, long long* __restrict__ out, int n)
+{
+    __shared__ float s_v[256];
+    __shared__ int s_i[256];
+    const float* row = x + (size_t)blockIdx.x * n;
+    float best = row[0];
+    int bi = 0;
+    for (int k = threadIdx.x; k < n; k += 256) {
+        const float v = row[k];
+        if (v > best || (v == best && k < bi)) { best = v; bi = k; }
+    }
+    s_v[threadIdx.x] = best;
+    s_i[threadIdx.x] = bi;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) {
+            const float v = s_v[threadIdx.x + o];
+            const int i = s_i[threadIdx.x + o];
+            if (v > s_v[threadIdx.x] || (v == s_v[threadIdx.x] && i < s_i[threadIdx.x])) {
+                s_v[threadIdx.x] = v;
+                s_i[threadIdx.x] = i;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = s_i[0];
+}
+
+static int grid_1d(long n)
+{
+    long want = (n + 255) / 256, cap = (long)sm_count() * 8;
+    return (int)(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+// grow-only per-device scratch of the forward pass (x and the three scratch vectors of the reference)
+static float* forward_scratch(size_t floats)
+{
+    static float* buf[64] = {nullptr};
+    static size_t cap[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cap[dev] < floats) {
+        if (buf[dev]) {
+            cudaDeviceSynchronize();
+            cudaFree(buf[dev]);
+            buf[dev] = nullptr;
+            cap[dev] = 0;
+        }
+        void* p = nullptr;
+        if (check_cuda(cudaMalloc(&p, floats * sizeof(float))) != 0) return nullptr;
+        buf[dev] = (float*)p;
+        cap[dev] = floats;
+    }
+    return buf[dev];
+}
+
+static int launch_attn(const float* q, const void* kc, const void* vc, float* dst, int n_q, int n_kv, int H, int HKV, int D,
+                       float scale, int kv_offset, int f16, cudaStream_t s)
+{
+    const size_t sh = (size_t)(n_kv + D) * sizeof(float);
+    if (sh > 200 * 1024) return BPDQ_ERR_RANGE;      // scores live in shared memory
+    static bool attr_set[2][64] = {{false}};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[f16 ? 1 : 0][dev]) {
+        int rc = f16 ? check_cuda(cudaFuncSetAttribute(k_gqa_attn<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024))
+                     : check_cuda(cudaFuncSetAttribute(k_gqa_attn<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (rc) return rc;
+        attr_set[f16 ? 1 : 0][dev] = true;
+    }
+    if (f16) k_gqa_attn<1><<<n_q * H, 256, sh, s>>>(q, kc, vc, dst, n_kv, H, HKV, D, scale, kv_offset);
+    else k_gqa_attn<0><<<n_q * H, 256, sh, s>>>(q, kc, vc, dst, n_kv, H, HKV, D, scale, kv_offset);
+    return check_cuda(cudaGetLastError());
+}
+
+static int launch_rope(const float* in, float* out, const int32_t* pos_ids, const float* ff, int n_tokens, int n_heads,
+                       int head_dim, int n_dims, float freq_base, cudaStream_t s)
+{
+    // the step between consecutive pairs' angles, computed where the reference computes it: on the host
+    const float theta_scale = powf(freq_base, -2.0f / (float)n_dims);
+    k_rope_norm<<<grid_1d((long)n_tokens * n_heads * head_dim / 2), 256, 0, s>>>(in, out, pos_ids, ff, n_tokens, n_heads,
+                                                                                 head_dim, n_dims, theta_scale);
+    return check_cuda(cudaGetLastError());
+}
+
+static int launch_kv_write(void* cache, const float* src, const int32_t* pos_ids, int n_tokens, int row, int f16, cudaStream_t s)
+{
+    if (f16) k_kv_write<1><<<grid_1d((long)n_tokens * row), 256, 0, s>>>(cache, src, pos_ids, n_tokens, row);
+    else k_kv_write<0><<<grid_1d((long)n_tokens * row), 256, 0, s>>>(cache, src, pos_ids, n_tokens, row);
+    return check_cuda(cudaGetLastError());
+}
+
+static int check_cfg(const bpd_llama_config* c, int n_tokens, int kv_pos)
+{
+    if (!c || n_tokens < 1 || kv_pos < 0) return BPDQ_ERR_ARG;
+    if (c->n_layers < 0 || c->n_heads < 1 || c->n_kv_heads < 1 || c->head_dim < 2 || (c->head_dim & 1)) return BPDQ_ERR_ARG;
+    if (c->n_heads % c->n_kv_heads) return BPDQ_ERR_ARG;
+    if (c->embed_dim != c->n_heads * c->head_dim || (c->embed_dim % 32) || c->ffn_dim < 32 || (c->ffn_dim % 32)) return BPDQ_ERR_ARG;
+    if (c->rope_dim < 0 || c->rope_dim > c->head_dim || (c->rope_dim & 1)) return BPDQ_ERR_ARG;
+    if (c->max_seq_len < 1 || kv_pos + n_tokens > c->max_seq_len) return BPDQ_ERR_RANGE;
+    if ((size_t)(c->max_seq_len + c->head_dim) * sizeof(float) > 200 * 1024) return BPDQ_ERR_RANGE;   // scores live in shared memory
+    return 0;
+}
+
+static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_llama_config* cfg, const int32_t* pos_ids,
+                         int n_tokens, int kv_pos, void* k_cache, void* v_cache, float* s1, float* s2, float* s3,
+                         const float* rope_freqs, cudaStream_t s)
+{
+    const int E = cfg->embed_dim, H = cfg->n_heads, HKV = cfg->n_kv_heads, D = cfg->head_dim, F = cfg->ffn_dim;
+    const int n_kv_full = cfg->max_seq_len;
+    int rc;
+    k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->attn_norm_w, s1, E, cfg->rms_eps);
+    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_q, s1, s2, n_tokens, H * D, E, s))) return rc;
+    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_k, s1, s3, n_tokens, HKV * D, E, s))) return rc;
+    if ((rc = launch_rope(s2, s2, pos_ids, rope_freqs, n_tokens, H, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
+    if ((rc = launch_rope(s3, s3, pos_ids, rope_freqs, n_tokens, HKV, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
+    const int row = HKV * D;
+    if ((rc = launch_kv_write(k_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
+    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_v, s1, s3, n_tokens, HKV * D, E, s))) return rc;
+    if ((rc = launch_kv_write(v_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
+    if ((rc = launch_attn(s2, k_cache, v_cache, s1, n_tokens, n_kv_full, H, HKV, D, 1.0f / sqrtf((float)D), kv_pos,
+                          cfg->kv_cache_f16, s)))
+        return rc;
+    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_o, s1, s2, n_tokens, E, H * D, s))) return rc;
+    k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s2, x, (long)n_tokens * E);
+    k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->ffn_norm_w, s1, E, cfg->rms_eps);
+    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_gate, s1, s2, n_tokens, F, E, s))) return rc;
+    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_up, s1, s3, n_tokens, F, E, s))) return rc;
+    k_swiglu_f32<<<grid_1d((long)n_tokens * F), 256, 0, s>>>(s2, s3, s2, (long)n_tokens * F);
+    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_down, s2, s1, n_tokens, E, F, s))) return rc;
+    k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s1, x, (long)n_tokens * E);
+    return check_cuda(cudaGetLastError());
+}
+
+}  // namespace bpdq
+
+using namespace bpdq;
+
+extern "C" {
+
+/* device-pointer twins of the steps' _cpu entry points (same argument order, plus the stream) */
+int bpd_rmsnorm_llama_cuda(const float* input, const float* weight, float* output, int n_rows, int row_len, float eps,
+                           void* stream)
+{
+    if (n_rows < 0 || row_len <= 0 || (n_rows > 0 && (!input || !output))) return latch(BPDQ_ERR_ARG);
+    if (n_rows == 0) return 0;
+    k_rmsnorm_llama<<<n_rows, 256, 0, (cudaStream_t)stream>>>(input, weight, output, row_len, eps);
+    int rc = check_cuda(cudaGetLastError());
+    return rc ? latch(rc) : 0;
+}
+int bpd_rope_norm_freqs_cuda(const float* input, float* output, const int32_t* pos_ids, const float* freq_factors,
+                             int n_tokens, int n_heads, int head_dim, int n_dims, float freq_base, void* stream)
+{
+    if (n_tokens < 0 || n_heads < 1 || head_dim < 2 || (head_dim & 1) || n_dims < 0 || n_dims > head_dim || (n_dims & 1))
+        return latch(BPDQ_ERR_ARG);
+    if (n_tokens == 0) return 0;
+    if (!input || !output || !pos_ids) return latch(BPDQ_ERR_ARG);
+    int rc = launch_rope(input, output, pos_ids, freq_factors, n_tokens, n_heads, head_dim, n_dims, freq_base, (cudaStream_t)stream);
+    return rc ? latch(rc) : 0;
+}
+int bpd_kv_cache_write_f16_cuda(uint16_t* cache, const float* src, const int32_t* pos_ids, int n_tokens, int n_kv_heads,
+                                int head_dim, int max_seq_len, void* stream)
+{
+    (void)max_seq_len;
+    if (n_tokens < 0 || n_kv_heads < 1 || head_dim < 1 || (n_tokens > 0 && (!cache || !src || !pos_ids))) return latch(BPDQ_ERR_ARG);
+    if (n_tokens == 0) return 0;
+    int rc = launch_kv_write(cache, src, pos_ids, n_tokens, n_kv_heads * head_dim, 1, (cudaStream_t)stream);
+    return rc ? latch(rc) : 0;
+}
+int bpd_kv_cache_write_cuda(float* cache, const float* src, const int32_t* pos_ids, int n_tokens, int n_kv_heads, int head_dim,
+                            int max_seq_len, void* stream)
+{
+    (void)max_seq_len;
+    if (n_tokens < 0 || n_kv_heads < 1 || head_dim < 1 || (n_tokens > 0 && (!cache || !src || !pos_ids))) return latch(BPDQ_ERR_ARG);
+    if (n_tokens == 0) return 0;
+    int rc = launch_kv_write(cache, src, pos_ids, n_tokens, n_kv_heads * head_dim, 0, (cudaStream_t)stream);
+    return rc ? latch(rc) : 0;
+}
+int bpd_gqa_attn_cuda(const float* q, const void* k, const void* v, float* dst, int n_q_tokens, int n_kv, int n_q_heads,
+                      int n_kv_heads, int head_dim, float scale, int kv_offset, int kv_is_f16, void* stream)
+{
+    if (n_q_tokens < 0 || n_kv < 1 || n_q_heads < 1 || n_kv_heads < 1 || (n_q_heads % n_kv_heads) || head_dim < 1)
+        return latch(BPDQ_ERR_ARG);
+    if (n_q_tokens == 0) return 0;
+    if (!q || !k || !v || !dst) return latch(BPDQ_ERR_ARG);
+    int rc = launch_attn(q, k, v, dst, n_q_tokens, n_kv, n_q_heads, n_kv_heads, head_dim, scale, kv_offset, kv_is_f16,
+                         (cudaStream_t)stream);
+    return rc ? latch(rc) : 0;
+}
+int bpd_swiglu_fuse_cuda(const float* gate, const float* up, float* dst, int n, void* stream)
+{
+    if (n < 0 || (n > 0 && (!gate || !up || !dst))) return latch(BPDQ_ERR_ARG);
+    if (n == 0) return 0;
+    k_swiglu_f32<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>(gate, up, dst, n);
+    int rc = check_cuda(cudaGetLastError());
+    return rc ? latch(rc) : 0;
+}
+int bpd_argmax_dim_cuda(const float* x, long long* out, int outer, int dim_size, int inner, void* stream)
+{
+    if (outer < 0 || dim_size < 1 || inner != 1 || (outer > 0 && (!x || !out))) return latch(BPDQ_ERR_ARG);
+    if (outer == 0) return 0;
+    k_argmax_rows<<<outer, 256, 0, (cudaStream_t)stream>>>(x, out, dim_size);
+    int rc = check_cuda(cudaGetLastError());
+    return rc ? latch(rc) : 0;
+}
+
+int bpd_llama_block_cuda(float* x, const bpd_llama_layer_weights* lw, const bpd_llama_config* cfg, const int32_t* pos_ids,
+                         int n_tokens, int kv_pos, void* k_cache, void* v_cache, float* scratch1, float* scratch2,
+                         float* scratch3, const float* rope_freqs, void* stream)
+{
+    int rc = check_cfg(cfg, n_tokens, kv_pos);
+    if (rc) return latch(rc);
+    if (!x || !lw || !pos_ids || !k_cache || !v_cache || !scratch1 || !scratch2 || !scratch3) return latch(BPDQ_ERR_ARG);
+    rc = block_forward(x, lw, cfg, pos_ids, n_tokens, kv_pos, k_cache, v_cache, scratch1, scratch2, scratch3, rope_freqs,
+                       (cudaStream_t)stream);
+    return rc ? latch(rc) : 0;
+}
+
+int bpd_llama_forward_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
+                           const bpd_llama_config* cfg, const int32_t* pos_ids, int kv_pos, void* k_cache, void* v_cache,
+                           float* logits_out, long long* token_out, void* stream)
+{
+    int rc = check_cfg(cfg, n_tokens, kv_pos);
+    if (rc) return latch(rc);
+    if (!token_ids || !weights || !pos_ids || !k_cache || !v_cache || !logits_out || !weights->token_embd ||
+        !weights->output_w || (cfg->n_layers > 0 && !weights->layers))
+        return latch(BPDQ_ERR_ARG);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int E = cfg->embed_dim, F = cfg->ffn_dim, H = cfg->n_heads, D = cfg->head_dim, HKV = cfg->n_kv_heads;
+    const size_t max_dim = (size_t)(E > F ? E : F), max_proj = (size_t)(H * D > F ? H * D : F);
+    const size_t nx = ((size_t)n_tokens * E + 63) / 64 * 64, n1 = ((size_t)n_tokens * max_dim + 63) / 64 * 64,
+                 n2 = ((size_t)n_tokens * max_proj + 63) / 64 * 64;
+    float* base = forward_scratch(nx + n1 + 2 * n2);
+    if (!base) return latch(BPDQ_ERR_CUDA);
+    float *x = base, *s1 = x + nx, *s2 = s1 + n1, *s3 = s2 + n2;
+    if ((rc = bpd_embed_lookup_q8_0_cuda(weights->token_embd, token_ids, x, n_tokens, E, s))) return rc;
+    const size_t kv_layer = (size_t)cfg->max_seq_len * HKV * D * (cfg->kv_cache_f16 ? 2 : 4);
+    for (int layer = 0; layer < cfg->n_layers; layer++) {
+        rc = block_forward(x, &weights->layers[layer], cfg, pos_ids, n_tokens, kv_pos, (uint8_t*)k_cache + layer * kv_layer,
+                           (uint8_t*)v_cache + layer * kv_layer, s1, s2, s3, weights->rope_freqs, s);
+        if (rc) return latch(rc);
+    }
+    k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, weights->output_norm_w, s1, E, cfg->rms_eps);
+    if ((rc = bpd_qmatmul_q8_0_cuda(weights->output_w, s1, logits_out, n_tokens, cfg->vocab_size, E, s))) return rc;
+    if (token_out) k_argmax_rows<<<n_tokens, 256, 0, s>>>(logits_out, token_out, cfg->vocab_size);
+    rc = check_cuda(cudaGetLastError());
+    return rc ? latch(rc) : 0;
+}
+
+}  // extern "C"

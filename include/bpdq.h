@@ -266,6 +266,52 @@ void gpu_silu(const float* in, float* out, int n);
 void gpu_matmul(const float* A, const float* B, float* C, int M, int N, int K);
 void gpu_matmul_opt(const float* A, const float* B, float* C, int M, int N, int K);
 
+/* ---- Q8_0 Llama forward (bench/bpd_cpu.c:5537-5798: bpd_llama_config, bpd_llama_layer_weights,
+ * bpd_llama_weights, bpd_llama_block_cpu, bpd_llama_forward_cpu).  Same structs (host memory, field
+ * for field), same argument order; every pointer inside them and every array argument is DEVICE
+ * memory; the KV caches are [n_layers][max_seq_len][n_kv_heads*head_dim] f16 (kv_cache_f16 = 1) or f32
+ * and must be zero where nothing has been written (all max_seq_len rows take part in the softmax,
+ * masked, as in the reference).  token_out may be NULL.  Asynchronous on `stream`; 0 or a status. */
+typedef struct {
+    int n_layers, n_heads, n_kv_heads, head_dim, embed_dim, ffn_dim, vocab_size, max_seq_len;
+    float rms_eps, rope_base;
+    int rope_dim, kv_cache_f16;
+} bpd_llama_config;
+typedef struct {
+    const float* attn_norm_w;
+    const uint8_t *w_q, *w_k, *w_v, *w_o;
+    const float* ffn_norm_w;
+    const uint8_t *w_gate, *w_up, *w_down;
+} bpd_llama_layer_weights;
+typedef struct {
+    const uint8_t* token_embd;
+    const bpd_llama_layer_weights* layers;   /* HOST array of n_layers descriptors */
+    const float* output_norm_w;
+    const uint8_t* output_w;
+    const float* rope_freqs;                 /* [rope_dim/2] or NULL */
+} bpd_llama_weights;
+/* the steps on device pointers, as the reference's _cpu entries (bench/bpd_cpu.c:4959, 5146, 5240, 5204,
+ * 5370, 5504, 4512) plus the stream; bpd_gqa_attn_cuda reads f16 caches directly when kv_is_f16 (the
+ * reference widens them to fp32 copies first); bpd_argmax_dim_cuda supports inner = 1 */
+int bpd_rmsnorm_llama_cuda(const float* input, const float* weight, float* output, int n_rows, int row_len, float eps,
+                           void* stream);
+int bpd_rope_norm_freqs_cuda(const float* input, float* output, const int32_t* pos_ids, const float* freq_factors,
+                             int n_tokens, int n_heads, int head_dim, int n_dims, float freq_base, void* stream);
+int bpd_kv_cache_write_f16_cuda(uint16_t* cache, const float* src, const int32_t* pos_ids, int n_tokens, int n_kv_heads,
+                                int head_dim, int max_seq_len, void* stream);
+int bpd_kv_cache_write_cuda(float* cache, const float* src, const int32_t* pos_ids, int n_tokens, int n_kv_heads, int head_dim,
+                            int max_seq_len, void* stream);
+int bpd_gqa_attn_cuda(const float* q, const void* k, const void* v, float* dst, int n_q_tokens, int n_kv, int n_q_heads,
+                      int n_kv_heads, int head_dim, float scale, int kv_offset, int kv_is_f16, void* stream);
+int bpd_swiglu_fuse_cuda(const float* gate, const float* up, float* dst, int n, void* stream);
+int bpd_argmax_dim_cuda(const float* x, long long* out, int outer, int dim_size, int inner, void* stream);
+int bpd_llama_block_cuda(float* x, const bpd_llama_layer_weights* lw, const bpd_llama_config* cfg, const int32_t* pos_ids,
+                         int n_tokens, int kv_pos, void* k_cache, void* v_cache, float* scratch1, float* scratch2,
+                         float* scratch3, const float* rope_freqs, void* stream);
+int bpd_llama_forward_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
+                           const bpd_llama_config* cfg, const int32_t* pos_ids, int kv_pos, void* k_cache, void* v_cache,
+                           float* logits_out, long long* token_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -82,6 +82,15 @@ class Oracle:
         lib.orc_qmm_q4k_q8k.restype = i
         lib.orc_vecmat_f32.argtypes = [vp, vp, vp, i, i]
         lib.orc_rms_norm_f64.argtypes = [vp, vp, vp, i, i, C.c_float]
+        f = C.c_float
+        lib.orc_rmsnorm_llama.argtypes = [vp, vp, vp, i, i, f]
+        lib.orc_rope_norm_freqs.argtypes = [vp, vp, vp, vp, i, i, i, i, f]
+        lib.orc_kv_cache_write.argtypes = [vp, vp, vp, i, i, i]
+        lib.orc_gqa_attn.argtypes = [vp, vp, vp, vp, i, i, i, i, i, f, i]
+        lib.orc_argmax_rows.argtypes = [vp, vp, i, i]
+        lib.orc_llama_block.argtypes = [vp, vp, vp, vp, i, i, vp, vp, vp, vp, vp, vp]
+        lib.orc_llama_forward.argtypes = [vp, i, vp, vp, vp, i, vp, vp, vp, vp]
+        lib.orc_llama_forward.restype = i
 
     # -- fp16
     def f16_to_f32(self, h):
@@ -214,6 +223,24 @@ class Oracle:
         return out
 
 
+    # -- Q8_0 Llama forward.  `weights` and `cfg` are ctypes structs with the layout of
+    # bench/bpd_cpu.c:5537-5588 whose pointers are HOST memory; the caches are updated in place.
+    def llama_forward(self, weights, cfg, token_ids, pos_ids, kv_pos, k_cache, v_cache):
+        return llama_forward_with(self.lib.orc_llama_forward, weights, cfg, token_ids, pos_ids, kv_pos, k_cache, v_cache)
+
+
+def llama_forward_with(fn, weights, cfg, token_ids, pos_ids, kv_pos, k_cache, v_cache):
+    """Calls a CPU forward (the checker's or the compiled reference's: same signature) and returns
+    (logits [n, vocab], argmax tokens [n])."""
+    token_ids = np.ascontiguousarray(token_ids, np.int32)
+    pos_ids = np.ascontiguousarray(pos_ids, np.int32)
+    n = token_ids.size
+    logits = np.empty((n, cfg.vocab_size), np.float32)
+    tokens = np.empty(n, np.int64)
+    fn(_p(token_ids), n, C.byref(weights), C.byref(cfg), _p(pos_ids), kv_pos, _p(k_cache), _p(v_cache), _p(logits), _p(tokens))
+    return logits, tokens
+
+
 def ref_available(name="bpd_quant.so"):
     return os.path.exists(os.path.join(REF_DIR, name))
 
@@ -237,6 +264,13 @@ def load_ref(name):
         lib.bpd_qmatmul_q8_0_llamafile_cpu.argtypes = [vp, vp, vp, i, i, i]
         lib.bpd_qmatmul_q8_0_dispatch_cpu.argtypes = [vp, vp, vp, i, i, i]
         lib.bpd_embed_lookup_q8_0_cpu.argtypes = [vp, vp, vp, i, i]
+        f = C.c_float
+        lib.bpd_rmsnorm_llama_cpu.argtypes = [vp, vp, vp, i, i, f]
+        lib.bpd_rope_norm_freqs_cpu.argtypes = [vp, vp, vp, vp, i, i, i, i, f]
+        lib.bpd_kv_cache_write_f16_cpu.argtypes = [vp, vp, vp, i, i, i, i]
+        lib.bpd_gqa_attn_cpu.argtypes = [vp, vp, vp, vp, i, i, i, i, i, f, i]
+        lib.bpd_argmax_dim_cpu.argtypes = [vp, vp, i, i, i]
+        lib.bpd_llama_forward_cpu.argtypes = [vp, i, vp, vp, vp, i, vp, vp, vp, vp]
         for rm in (1, 2, 4):
             for rn in (1, 2, 4):
                 getattr(lib, f"bpd_gemm_q8_0_{rm}_{rn}_cpu").argtypes = [vp, vp, i, i, i, vp, i]

@@ -526,3 +526,195 @@ void orc_rms_norm_f64(const float *in, const float *w, float *out,
             out[(size_t)r * cols + c] = (float)((double)x[c] * scale * (double)w[c]);
     }
 }
+
+/* ------------------------------------------------------------------------
+ * Q8_0 Llama forward: restatement of bpd_llama_block_cpu / bpd_llama_forward_cpu
+ * (bench/bpd_cpu.c:5608-5798) and of the steps they compose.  Own code, same
+ * arithmetic; pinned against the compiled reference by tests/test_oracle_pins.py.
+ * ------------------------------------------------------------------------ */
+
+/* bench/bpd_cpu.c:4959-4988: binary64 sum of squares in index order, mean rounded
+ * to fp32, scale = 1/sqrtf(mean + eps), y = (x*scale)*w. */
+void orc_rmsnorm_llama(const float *in, const float *w, float *out, int rows, int cols, float eps)
+{
+    for (int r = 0; r < rows; r++) {
+        const float *x = in + (size_t)r * cols;
+        float *y = out + (size_t)r * cols;
+        double acc = 0.0;
+        for (int i = 0; i < cols; i++) acc += (double)x[i] * (double)x[i];
+        const float mean = (float)(acc / cols);
+        const float scale = 1.0f / sqrtf(mean + eps);
+        for (int i = 0; i < cols; i++) y[i] = w ? x[i] * scale * w[i] : x[i] * scale;
+    }
+}
+
+/* bench/bpd_cpu.c:5146-5183: pairs (2p, 2p+1) of each head rotate by theta_p / ff_p,
+ * theta_0 = (float)pos, theta_{p+1} = theta_p * base^(-2/n_dims); dims past n_dims copy. */
+void orc_rope_norm_freqs(const float *in, float *out, const int32_t *pos, const float *ff,
+                         int n_tokens, int n_heads, int head_dim, int n_dims, float base)
+{
+    const float step = powf(base, -2.0f / (float)n_dims);
+    for (int t = 0; t < n_tokens; t++)
+        for (int h = 0; h < n_heads; h++) {
+            const float *src = in + ((size_t)t * n_heads + h) * head_dim;
+            float *dst = out + ((size_t)t * n_heads + h) * head_dim;
+            float theta = (float)pos[t];
+            for (int p = 0; 2 * p < n_dims; p++) {
+                const float te = theta / (ff ? ff[p] : 1.0f);
+                const float c = cosf(te), s = sinf(te);
+                const float a = src[2 * p], b = src[2 * p + 1];
+                dst[2 * p] = a * c - b * s;
+                dst[2 * p + 1] = a * s + b * c;
+                theta *= step;
+            }
+            for (int i = n_dims; i < head_dim; i++) dst[i] = src[i];
+        }
+}
+
+/* bench/bpd_cpu.c:5204-5257: cache row pos[t] = src row t, as fp32 or rounded to f16. */
+void orc_kv_cache_write(void *cache, const float *src, const int32_t *pos, int n_tokens, int row, int f16)
+{
+    for (int t = 0; t < n_tokens; t++)
+        for (int i = 0; i < row; i++) {
+            const size_t at = (size_t)pos[t] * row + i;
+            if (f16) ((uint16_t *)cache)[at] = orc_f32_to_f16(src[(size_t)t * row + i]);
+            else ((float *)cache)[at] = src[(size_t)t * row + i];
+        }
+}
+
+/* bench/bpd_cpu.c:5370-5433: raw dots, then scale and mask (-1e38 past the query's
+ * position), maximum, exp and sum, multiply by the reciprocal, weighted sum of V;
+ * every one of the n_kv rows takes part. */
+void orc_gqa_attn(const float *q, const float *k, const float *v, float *dst, int n_q, int n_kv,
+                  int n_q_heads, int n_kv_heads, int head_dim, float scale, int kv_offset)
+{
+    const int group = n_q_heads / n_kv_heads;
+    float *sc = (float *)malloc(sizeof(float) * (size_t)n_kv);
+    for (int t = 0; t < n_q; t++)
+        for (int h = 0; h < n_q_heads; h++) {
+            const int kh = h / group, qpos = kv_offset + t;
+            const float *pq = q + ((size_t)t * n_q_heads + h) * head_dim;
+            float *pd = dst + ((size_t)t * n_q_heads + h) * head_dim;
+            float mx = -1e38f;
+            for (int c = 0; c < n_kv; c++) {
+                const float *pk = k + ((size_t)c * n_kv_heads + kh) * head_dim;
+                float s = 0.0f;
+                for (int d = 0; d < head_dim; d++) s += pq[d] * pk[d];
+                sc[c] = (c <= qpos) ? s * scale : -1e38f;
+                if (sc[c] > mx) mx = sc[c];
+            }
+            float sum = 0.0f;
+            for (int c = 0; c < n_kv; c++) {
+                sc[c] = expf(sc[c] - mx);
+                sum += sc[c];
+            }
+            const float inv = (sum == 0.0f) ? 0.0f : 1.0f / sum;
+            for (int c = 0; c < n_kv; c++) sc[c] *= inv;
+            for (int d = 0; d < head_dim; d++) pd[d] = 0.0f;
+            for (int c = 0; c < n_kv; c++) {
+                const float *pv = v + ((size_t)c * n_kv_heads + kh) * head_dim;
+                for (int d = 0; d < head_dim; d++) pd[d] += pv[d] * sc[c];
+            }
+        }
+    free(sc);
+}
+
+/* bench/bpd_cpu.c:4512-4529 with inner = 1: first index of the largest value. */
+void orc_argmax_rows(const float *x, long *out, int rows, int n)
+{
+    for (int r = 0; r < rows; r++) {
+        long best = 0;
+        for (int kx = 1; kx < n; kx++)
+            if (x[(size_t)r * n + kx] > x[(size_t)r * n + best]) best = kx;
+        out[r] = best;
+    }
+}
+
+typedef struct {
+    int n_layers, n_heads, n_kv_heads, head_dim, embed_dim, ffn_dim, vocab_size, max_seq_len;
+    float rms_eps, rope_base;
+    int rope_dim, kv_cache_f16;
+} orc_llama_config;            /* bench/bpd_cpu.c:5537-5553 */
+typedef struct {
+    const float *attn_norm_w;
+    const uint8_t *w_q, *w_k, *w_v, *w_o;
+    const float *ffn_norm_w;
+    const uint8_t *w_gate, *w_up, *w_down;
+} orc_llama_layer;             /* bench/bpd_cpu.c:5569-5579 */
+typedef struct {
+    const uint8_t *token_embd;
+    const orc_llama_layer *layers;
+    const float *output_norm_w;
+    const uint8_t *output_w;
+    const float *rope_freqs;
+} orc_llama_weights;           /* bench/bpd_cpu.c:5582-5588 */
+
+/* out[t*rows + r] = W row r . q8_0(X row t): the scalar product of bench/bpd_cpu.c:4295-4315,
+ * which is what the reference's non-AVX build runs (bench/bpd_cpu.c:4455-4458). */
+static void llama_matmul(const uint8_t *W, const float *X, float *out, int rows, int tokens, int K)
+{
+    orc_qmatmul_q8_0(W, X, out, tokens, rows, K);
+}
+
+/* bench/bpd_cpu.c:5608-5738 */
+void orc_llama_block(float *x, const orc_llama_layer *lw, const orc_llama_config *cfg, const int32_t *pos,
+                     int n_tokens, int kv_pos, void *k_cache, void *v_cache, float *s1, float *s2, float *s3,
+                     const float *rope_freqs)
+{
+    const int E = cfg->embed_dim, H = cfg->n_heads, HKV = cfg->n_kv_heads, D = cfg->head_dim, F = cfg->ffn_dim;
+    const int n_kv = cfg->max_seq_len, row = HKV * D;
+    orc_rmsnorm_llama(x, lw->attn_norm_w, s1, n_tokens, E, cfg->rms_eps);
+    llama_matmul(lw->w_q, s1, s2, H * D, n_tokens, E);
+    llama_matmul(lw->w_k, s1, s3, row, n_tokens, E);
+    orc_rope_norm_freqs(s2, s2, pos, rope_freqs, n_tokens, H, D, cfg->rope_dim, cfg->rope_base);
+    orc_rope_norm_freqs(s3, s3, pos, rope_freqs, n_tokens, HKV, D, cfg->rope_dim, cfg->rope_base);
+    orc_kv_cache_write(k_cache, s3, pos, n_tokens, row, cfg->kv_cache_f16);
+    llama_matmul(lw->w_v, s1, s3, row, n_tokens, E);
+    orc_kv_cache_write(v_cache, s3, pos, n_tokens, row, cfg->kv_cache_f16);
+    const size_t n = (size_t)n_kv * row;
+    float *kf = (float *)k_cache, *vf = (float *)v_cache;
+    if (cfg->kv_cache_f16) {
+        kf = (float *)malloc(sizeof(float) * n);
+        vf = (float *)malloc(sizeof(float) * n);
+        for (size_t i = 0; i < n; i++) {
+            kf[i] = orc_f16_to_f32(((const uint16_t *)k_cache)[i]);
+            vf[i] = orc_f16_to_f32(((const uint16_t *)v_cache)[i]);
+        }
+    }
+    orc_gqa_attn(s2, kf, vf, s1, n_tokens, n_kv, H, HKV, D, 1.0f / sqrtf((float)D), kv_pos);
+    if (cfg->kv_cache_f16) {
+        free(kf);
+        free(vf);
+    }
+    llama_matmul(lw->w_o, s1, s2, E, n_tokens, H * D);
+    for (long i = 0; i < (long)n_tokens * E; i++) x[i] = x[i] + s2[i];
+    orc_rmsnorm_llama(x, lw->ffn_norm_w, s1, n_tokens, E, cfg->rms_eps);
+    llama_matmul(lw->w_gate, s1, s2, F, n_tokens, E);
+    llama_matmul(lw->w_up, s1, s3, F, n_tokens, E);
+    for (long i = 0; i < (long)n_tokens * F; i++) s2[i] = (s2[i] / (1.0f + expf(-s2[i]))) * s3[i];   /* :5504-5507 */
+    llama_matmul(lw->w_down, s2, s1, E, n_tokens, F);
+    for (long i = 0; i < (long)n_tokens * E; i++) x[i] = x[i] + s1[i];
+}
+
+/* bench/bpd_cpu.c:5741-5798 */
+int orc_llama_forward(const int32_t *token_ids, int n_tokens, const orc_llama_weights *w, const orc_llama_config *cfg,
+                      const int32_t *pos, int kv_pos, void *k_cache, void *v_cache, float *logits, long *token_out)
+{
+    const int E = cfg->embed_dim, F = cfg->ffn_dim, H = cfg->n_heads, D = cfg->head_dim, HKV = cfg->n_kv_heads;
+    const size_t max_dim = (size_t)(E > F ? E : F), max_proj = (size_t)(H * D > F ? H * D : F);
+    float *x = (float *)malloc(sizeof(float) * (size_t)n_tokens * E);
+    float *s1 = (float *)malloc(sizeof(float) * (size_t)n_tokens * max_dim);
+    float *s2 = (float *)malloc(sizeof(float) * (size_t)n_tokens * max_proj);
+    float *s3 = (float *)malloc(sizeof(float) * (size_t)n_tokens * max_proj);
+    if (!x || !s1 || !s2 || !s3) { free(x); free(s1); free(s2); free(s3); return -1; }
+    orc_embed_lookup_q8_0(w->token_embd, token_ids, x, n_tokens, E);
+    const size_t layer_bytes = (size_t)cfg->max_seq_len * HKV * D * (cfg->kv_cache_f16 ? 2 : 4);
+    for (int l = 0; l < cfg->n_layers; l++)
+        orc_llama_block(x, &w->layers[l], cfg, pos, n_tokens, kv_pos, (uint8_t *)k_cache + l * layer_bytes,
+                        (uint8_t *)v_cache + l * layer_bytes, s1, s2, s3, w->rope_freqs);
+    orc_rmsnorm_llama(x, w->output_norm_w, s1, n_tokens, E, cfg->rms_eps);
+    llama_matmul(w->output_w, s1, logits, cfg->vocab_size, n_tokens, E);
+    if (token_out) orc_argmax_rows(logits, token_out, n_tokens, cfg->vocab_size);
+    free(x); free(s1); free(s2); free(s3);
+    return 0;
+}

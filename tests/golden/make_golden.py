@@ -25,6 +25,12 @@ from bpd_substrate_b200 import synth  # noqa: E402
 from oracle import binding  # noqa: E402
 
 
+# the tiny Llama of the forward-pass fixture (shared with tests/test_llama_forward.py)
+LLAMA_TINY = dict(n_layers=2, n_heads=4, n_kv_heads=2, head_dim=32, ffn_dim=256, vocab_size=96, max_seq_len=16)
+LLAMA_TINY_SEED = 77
+LLAMA_TINY_STEPS = (("prefill", [3, 17, 95, 0, 42]), ("step1", [7]), ("step2", [64]))
+
+
 def sha(a):
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
@@ -87,6 +93,22 @@ def main():
     rc.bpd_qmatmul_q8_0_cpu(W.ctypes.data, x.ctypes.data, y.ctypes.data, 1, 4096, 4096)
     np.savez_compressed(os.path.join(HERE, "q8_0_gemv_4096x4096.npz"), w_seed=np.array([1001]), x_seed=np.array([1002]),
                         input_sha256=np.array([sha(W)]), out=y.view(np.uint32))
+    # ---- Q8_0 Llama forward of a tiny synthetic model (bpd_llama_forward_cpu, scalar build): prefill of
+    # five tokens, then two single-token steps against the f16 KV cache
+    from bpd_substrate_b200 import llama
+    cfg = llama.make_config(**LLAMA_TINY)
+    model = llama.SyntheticLlama(cfg, seed=LLAMA_TINY_SEED)
+    w, keep = model.host_structs()
+    k, v = model.kv_cache()
+    steps, kv_pos = {}, 0
+    for name, toks in LLAMA_TINY_STEPS:
+        pos = np.arange(kv_pos, kv_pos + len(toks), dtype=np.int32)
+        logits, out = binding.llama_forward_with(rc.bpd_llama_forward_cpu, w, cfg, toks, pos, kv_pos, k, v)
+        steps[f"{name}_logits"] = logits.view(np.uint32)
+        steps[f"{name}_tokens"] = out
+        kv_pos += len(toks)
+    np.savez_compressed(os.path.join(HERE, "llama_tiny.npz"), k_cache=k, v_cache=v, **steps)
+    del keep
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))
