@@ -1,6 +1,8 @@
 """Timings of the secondary configurations (the benchmark line itself comes from bench.py).
 
     python -m bpd_substrate_b200.measure            # prints one JSON object per configuration
+    python -m bpd_substrate_b200.measure --llama-decode [LAYERS]
+                                                    # Q8_0 Llama forward, 8B-shaped layers: ms per decoded token
     python -m bpd_substrate_b200.measure --gemm-once tc5 64 [N K]
                                                     # five launches of one many-token product (kernel
                                                     # tc5 | mma | dispatch): a small case for a profiler
@@ -75,9 +77,69 @@ def gemm_once(lib, kernel, tokens, N=14336, K=4096, launches=5):
     return 0 if status == 0 else 1
 
 
+def llama_decode(lib, n_layers=4, steps=32):
+    """Single-token steps of bpd_llama_forward_cuda on a synthetic model with Llama-3-8B-shaped layers
+    (32 heads, 8 KV heads, head 128, FFN 14336; vocabulary cut to 32000 to keep host generation short),
+    f16 KV cache of 256 positions.  Prints ms per token and the bytes that a token must read."""
+    import ctypes as C
+
+    from . import llama
+    cfg = llama.make_config(n_layers=n_layers, n_heads=32, n_kv_heads=8, head_dim=128, ffn_dim=14336, vocab_size=32000,
+                            max_seq_len=256)
+    model = llama.SyntheticLlama(cfg, seed=1)
+    dev = llama.DeviceLlama(model, lib)
+    n_pre = 8
+    dev.forward(np.arange(n_pre, dtype=np.int32), np.arange(n_pre, dtype=np.int32), 0)      # prefill
+    d_tok, d_pos = lib.bpdq_alloc(16), lib.bpdq_alloc(16 * (steps + 4))
+    d_logits, d_out = lib.bpdq_alloc(4 * cfg.vocab_size), lib.bpdq_alloc(16)
+    pos = np.arange(n_pre, n_pre + steps + 4, dtype=np.int32)
+    lib.bpdq_h2d(d_pos, pos.ctypes.data, pos.nbytes)
+    tok = np.array([5], np.int32)
+    lib.bpdq_h2d(d_tok, tok.ctypes.data, 4)
+    ev0, ev1 = lib.bpdq_event_create(), lib.bpdq_event_create()
+
+    def step(i):
+        capi.check(lib.bpd_llama_forward_cuda(d_tok, 1, C.byref(dev.weights), C.byref(cfg), d_pos + 4 * i, n_pre + i, dev.d_k,
+                                              dev.d_v, d_logits, d_out, dev.stream))
+    for i in range(4):
+        step(i)
+    lib.bpdq_stream_sync(dev.stream)
+    lib.bpdq_event_record(ev0, dev.stream)
+    for i in range(4, 4 + steps):
+        step(i)
+    lib.bpdq_event_record(ev1, dev.stream)
+    ms = lib.bpdq_event_elapsed_ms(ev0, ev1) / steps
+    # the same step replayed from a CUDA graph (one position: the arguments are fixed at capture)
+    capi.check(lib.bpdq_graph_begin(dev.stream), "graph capture")
+    step(4 + steps - 1)
+    graph = lib.bpdq_graph_end(dev.stream)
+    ms_graph = None
+    if graph:
+        for _ in range(3):
+            capi.check(lib.bpdq_graph_launch(graph, dev.stream))
+        lib.bpdq_event_record(ev0, dev.stream)
+        for _ in range(steps):
+            capi.check(lib.bpdq_graph_launch(graph, dev.stream))
+        lib.bpdq_event_record(ev1, dev.stream)
+        ms_graph = lib.bpdq_event_elapsed_ms(ev0, ev1) / steps
+        lib.bpdq_graph_destroy(graph)
+    kv_row = cfg.n_kv_heads * cfg.head_dim
+    per_token = (sum(sum(v.nbytes for k, v in layer.items() if k.startswith("w_")) for layer in model.layers)
+                 + model.output_w.nbytes + cfg.n_layers * 2 * cfg.max_seq_len * kv_row * 2)
+    status = lib.bpdq_last_status()
+    print(json.dumps({"config": f"Q8_0 Llama forward, {n_layers} layers of 8B shape, decode", "ms_per_token": round(ms, 4),
+                      "ms_per_token_graph": round(ms_graph, 4) if ms_graph else None,
+                      "bytes_per_token": per_token, "gbs": round(per_token / (ms_graph or ms) / 1e6, 1),
+                      "launches_per_token": 17 * n_layers + 4, "status": status}))
+    dev.close()
+    return 0 if status == 0 else 1
+
+
 def main():
     lib = capi.load()
     lib.bpdq_clear_status()
+    if len(sys.argv) >= 2 and sys.argv[1] == "--llama-decode":
+        return llama_decode(lib, *[int(v) for v in sys.argv[2:3]])
     if len(sys.argv) >= 4 and sys.argv[1] == "--gemm-once":
         extra = [int(v) for v in sys.argv[4:6]]
         return gemm_once(lib, sys.argv[2], int(sys.argv[3]), *extra)
