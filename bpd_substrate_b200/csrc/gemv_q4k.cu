@@ -1816,6 +1816,22 @@ int gemv_q8_0_fast(const uint8_t* W, const float* x, float* out, int N, int K, c
     return launch_batch<1, BPDQ_LAYOUT_BPD>(plan, s);
 }
 
+// Up to kMaxBatch Q8_0 matrices that read the same activation vector, one launch (q/k/v, gate/up).
+int gemv_q8_0_fast_multi(int n, const uint8_t* const* Ws, float* const* outs, const int* Ns, const float* x, int K,
+                         cudaStream_t s)
+{
+    if (n < 1 || n > kMaxBatch || (K % 256) != 0 || ((uintptr_t)x & 15)) return BPDQ_ERR_RANGE;
+    BatchDesc d[kMaxBatch];
+    for (int j = 0; j < n; j++) {
+        if ((uintptr_t)Ws[j] & 15) return BPDQ_ERR_RANGE;
+        d[j] = {Ws[j], x, outs[j], Ns[j], K};
+    }
+    BatchPlan plan;
+    int rc = make_batch_plan(d, n, plan, 1);
+    if (rc) return rc;
+    return launch_batch<1, BPDQ_LAYOUT_BPD>(plan, s);
+}
+
 // ---------------------------------------------------------------- scratch without an allocator
 //
 // Scratch for the quantized activation records of bpd_qmatmul_q4k_q8k_batch_static_cuda: a

@@ -267,6 +267,19 @@ static int launch_kv_write(void* cache, const float* src, const int32_t* pos_ids
     return check_cuda(cudaGetLastError());
 }
 
+// Products that read the same vector: one launch where the fast Q8_0 kernel applies (one token, K a
+// multiple of 256, aligned pointers), else one call each.  Same arithmetic either way.
+static int products_shared_input(int n, const uint8_t* const* Ws, float* const* outs, const int* Ns, const float* x,
+                                 int n_tokens, int K, cudaStream_t s)
+{
+    if (n_tokens == 1 && gemv_q8_0_fast_multi(n, Ws, outs, Ns, x, K, s) == 0) return 0;
+    for (int j = 0; j < n; j++) {
+        int rc = bpd_qmatmul_q8_0_cuda(Ws[j], x, outs[j], n_tokens, Ns[j], K, s);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
 static int check_cfg(const bpd_llama_config* c, int n_tokens, int kv_pos)
 {
     if (!c || n_tokens < 1 || kv_pos < 0) return BPDQ_ERR_ARG;
@@ -286,23 +299,35 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
     const int E = cfg->embed_dim, H = cfg->n_heads, HKV = cfg->n_kv_heads, D = cfg->head_dim, F = cfg->ffn_dim;
     const int n_kv_full = cfg->max_seq_len;
     int rc;
+    const int row = HKV * D;
+    // scratch3 holds K and, behind it, V (it is at least n_tokens * H*D floats and H*D >= 2 * HKV*D
+    // whenever two or more query heads share a KV head; otherwise V is computed after K is stored)
+    const bool kv_together = (size_t)2 * row <= (size_t)H * D;
+    float* vbuf = kv_together ? s3 + (size_t)n_tokens * row : s3;
     k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->attn_norm_w, s1, E, cfg->rms_eps);
-    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_q, s1, s2, n_tokens, H * D, E, s))) return rc;
-    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_k, s1, s3, n_tokens, HKV * D, E, s))) return rc;
+    {
+        const uint8_t* Ws[3] = {lw->w_q, lw->w_k, lw->w_v};
+        float* outs[3] = {s2, s3, vbuf};
+        const int Ns[3] = {H * D, row, row};
+        if ((rc = products_shared_input(kv_together ? 3 : 2, Ws, outs, Ns, s1, n_tokens, E, s))) return rc;
+    }
     if ((rc = launch_rope(s2, s2, pos_ids, rope_freqs, n_tokens, H, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
     if ((rc = launch_rope(s3, s3, pos_ids, rope_freqs, n_tokens, HKV, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
-    const int row = HKV * D;
     if ((rc = launch_kv_write(k_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
-    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_v, s1, s3, n_tokens, HKV * D, E, s))) return rc;
-    if ((rc = launch_kv_write(v_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
+    if (!kv_together && (rc = bpd_qmatmul_q8_0_cuda(lw->w_v, s1, vbuf, n_tokens, row, E, s))) return rc;
+    if ((rc = launch_kv_write(v_cache, vbuf, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
     if ((rc = launch_attn(s2, k_cache, v_cache, s1, n_tokens, n_kv_full, H, HKV, D, 1.0f / sqrtf((float)D), kv_pos,
                           cfg->kv_cache_f16, s)))
         return rc;
     if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_o, s1, s2, n_tokens, E, H * D, s))) return rc;
     k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s2, x, (long)n_tokens * E);
     k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->ffn_norm_w, s1, E, cfg->rms_eps);
-    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_gate, s1, s2, n_tokens, F, E, s))) return rc;
-    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_up, s1, s3, n_tokens, F, E, s))) return rc;
+    {
+        const uint8_t* Ws[2] = {lw->w_gate, lw->w_up};
+        float* outs[2] = {s2, s3};
+        const int Ns[2] = {F, F};
+        if ((rc = products_shared_input(2, Ws, outs, Ns, s1, n_tokens, E, s))) return rc;
+    }
     k_swiglu_f32<<<grid_1d((long)n_tokens * F), 256, 0, s>>>(s2, s3, s2, (long)n_tokens * F);
     if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_down, s2, s1, n_tokens, E, F, s))) return rc;
     k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s1, x, (long)n_tokens * E);
