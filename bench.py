@@ -32,11 +32,11 @@ METRIC = "Q4_K x Q8_K GEMV effective HBM bandwidth"
 UNIT = "GB/s"
 WORKLOAD = "mistral7b_layer_set_x32_q4k_decode_batch1"
 N_LAYERS = 32
-KERNEL_OF = {"batched": "k_gemv_batch_q4k_q8k", "grouped": "k_gemv_q4k_q8k", "separate": "k_gemv_q4k_q8k",
+KERNEL_OF = {"persistent": "k_gemv_stream_q4k_q8k", "batched": "k_gemv_batch_q4k_q8k", "grouped": "k_gemv_q4k_q8k", "separate": "k_gemv_q4k_q8k",
              "chain": "k_gemv_batch_q4k_q8k", "chain4": "k_gemv_batch_q4k_q8k", "chain-separate": "k_gemv_batch_q4k_q8k",
              "chain-persistent": "k_decode_chain"}
 # DRAM traffic / algorithmic bytes measured with ncu (profiles/*.md): nothing is re-read
-TRAFFIC_PER_ALGORITHMIC = {"batched": 1.03, "grouped": 1.00, "separate": 1.00, "chain": 1.03, "chain4": 1.03,
+TRAFFIC_PER_ALGORITHMIC = {"persistent": 1.03, "batched": 1.03, "grouped": 1.00, "separate": 1.00, "chain": 1.03, "chain4": 1.03,
                            "chain-separate": 1.03, "chain-persistent": 1.03}
 
 
@@ -231,7 +231,7 @@ def run_gpu(args):
     launches = ls.launches_per_step(schedule)
     # launches of the dominant kernel (the batched schedule adds one small quantizer per layer,
     # which overlaps the previous GEMV kernel and is counted in the step time)
-    main_launches = args.layers if schedule == "batched" else (
+    main_launches = 1 if schedule == "persistent" else args.layers if schedule == "batched" else (
         1 if schedule == "chain-persistent" else
         (7 if schedule == "chain-separate" else 4) * args.layers if chain else launches)
     x_host = lib.bpdq_host_alloc(ls.x_bytes)
@@ -368,8 +368,10 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--schedule", default="batched", choices=["batched", "grouped", "separate", "chain", "chain4", "chain-separate", "chain-persistent"],
-                    help="batched: the benchmark (a layer's seven independent products in one launch); grouped / "
+    ap.add_argument("--schedule", default="batched", choices=["persistent", "batched", "grouped", "separate", "chain", "chain4", "chain-separate",
+                                                                  "chain-persistent"],
+                    help="persistent: all products of the step in one persistent launch; "
+                         "batched: the benchmark (a layer's seven independent products in one launch); grouped / "
                          "separate: fewer products per launch; chain: the seven products as a dependent decode chain, "
                          "rms_norm / SwiGLU as small kernels writing quantized records, residual add in the product's "
                          "epilogue (8 launches per layer); chain4: the steps inside the product kernels (4); "

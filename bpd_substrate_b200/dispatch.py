@@ -34,7 +34,9 @@ class LayerSet:
     * ``"grouped"``  -- matrices that read the same vector in a real decoder (q/k/v, gate/up)
       share a launch and the first member's activation vector;
     * ``"batched"``  -- the seven independent products of a layer go to the device as ONE
-      launch (``bpd_qmatmul_q4k_q8k_batch_cuda``), each with its own activation vector.
+      launch (``bpd_qmatmul_q4k_q8k_batch_cuda``), each with its own activation vector;
+    * ``"persistent"`` -- all products of the step as ONE persistent launch whose weight ring never
+      drains between layers (``bpdq_gemv_stream_run``), after one launch that quantizes all vectors.
     """
 
     def __init__(self, shapes=synth.MISTRAL_LAYER, n_layers=32, seed=2000, row_shard=(0, 1), lib=None,
@@ -82,6 +84,7 @@ class LayerSet:
         self.graph = {}
         self._keep = []
         self.ws = None             # scratch for quantized activations (batched schedule)
+        self.stream_plan = self.stream_ws = None      # plan and scratch of the persistent schedule
         capi.check(lib.bpdq_last_status(), "LayerSet setup")
 
     # ---- sizes
@@ -92,6 +95,8 @@ class LayerSet:
     def launches_per_step(self, schedule):
         if self.tokens > 1:
             return 2 * self.n_layers * len(self.local)   # activation quantizer + GEMM kernel per matrix
+        if schedule == "persistent":
+            return 2                      # one quantizer launch + one persistent GEMV launch per step
         if schedule == "batched":
             return 2 * self.n_layers      # activation quantizer + GEMV kernel per layer
         return self.n_layers * len(GROUPS_DECODE if schedule == "grouped" else GROUPS_NONE)
@@ -121,6 +126,22 @@ class LayerSet:
                     capi.check(lib.bpd_qmm_q4k_q8k_cuda(self.weights[layer][m], self.d_x + self.x_off[i],
                                                         self.d_out + self.o_off[i], self.tokens, rows, cols, 0, 0,
                                                         None, s), "GEMM launch")
+            return
+        if schedule == "persistent":
+            if self.stream_plan is None:
+                nm = len(self.local)
+                descs = (capi.GemvDesc * (nm * self.n_layers))()
+                for layer in range(self.n_layers):
+                    for m, (_, rows, cols) in enumerate(self.local):
+                        i = layer * nm + m
+                        descs[i] = capi.GemvDesc(self.weights[layer][m], self.d_x + self.x_off[i],
+                                                 self.d_out + self.o_off[i], rows, cols)
+                self.stream_ws_bytes = lib.bpdq_batch_workspace_bytes(len(descs), descs)
+                self.stream_ws = lib.bpdq_alloc(self.stream_ws_bytes)
+                self.stream_plan = lib.bpdq_gemv_stream_create(len(descs), descs, self.stream_ws, self.stream_ws_bytes)
+                if not self.stream_plan:
+                    raise capi.BpdqError(f"stream plan rejected (status {lib.bpdq_last_status()})")
+            capi.check(lib.bpdq_gemv_stream_run(self.stream_plan, s), "persistent GEMV launch")
             return
         if schedule == "batched":
             nm = len(self.local)
@@ -209,6 +230,10 @@ class LayerSet:
                 lib.bpdq_free(p)
         self.weights = []
         lib.bpdq_free(self.d_x)
+        if self.stream_plan:
+            lib.bpdq_gemv_stream_destroy(self.stream_plan)
+            lib.bpdq_free(self.stream_ws)
+            self.stream_plan = None
         if self.ws is not None:
             lib.bpdq_free(self.ws)
         if self._own_out:

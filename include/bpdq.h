@@ -175,6 +175,16 @@ size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs);
  *    must be serialized by the caller. */
 int bpd_qmatmul_q4k_q8k_batch_static_cuda(int n, const bpdq_gemv_desc* descs, void* stream);
 size_t bpdq_batch_static_capacity(void);
+/* Any number of independent products as ONE persistent launch (plus one launch that quantizes all
+ * their activation vectors): the weights of all products stream through the shared-memory ring without
+ * a launch boundary in between.  bpdq_gemv_stream_create plans the products (same descriptors as the batched
+ * entries), lays the activation records out in `workspace` (bpdq_batch_workspace_bytes(n, descs) bytes,
+ * 16-byte aligned, must stay allocated) and uploads the plan (it allocates device memory); bpdq_gemv_stream_run
+ * launches it, stream-ordered like any launch; same bits as the batched entries. */
+void* bpdq_gemv_stream_create(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes);   /* NULL on error */
+int bpdq_gemv_stream_run(void* handle, void* stream);
+void bpdq_gemv_stream_destroy(void* handle);
+
 /* ---- Decode glue.  Replaces, around the products of a decoder layer, the separate elementwise
  * launches of the reference's decode loop (inference/llamatov_gpu_llama.py:119-166: gpu_rms_norm,
  * gpu_silu, gpu_mul, gpu_add; kernels lib/kernel_templates_llama.pl:529-593, :600-830): each step

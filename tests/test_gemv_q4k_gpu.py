@@ -170,3 +170,45 @@ def test_batched_rejects_bad_descriptors(lib):
     descs = (capi.GemvDesc * 1)(capi.GemvDesc(d.ptr + 8, d.ptr, d.ptr, 4, 256))
     assert lib.bpd_qmatmul_q4k_q8k_batch_cuda(1, descs, None) == -2
     lib.bpdq_clear_status()
+
+
+def test_stream_of_products_equals_batched_entries(lib):
+    """bpdq_gemv_stream_*: 19 products of mixed shapes (several phases, some sharing a vector) in one
+    persistent launch give the bits of the batched entry, run after run."""
+    from bpd_substrate_b200 import capi
+    rng = np.random.default_rng(77)
+    shapes = [(96, 4096), (40, 4096), (40, 4096), (130, 2048), (64, 14336), (7, 256), (300, 4096), (33, 14336),
+              (512, 1024), (96, 4096), (18, 8192), (200, 4096), (1, 256), (64, 14336), (128, 4096), (90, 512),
+              (256, 4096), (31, 14336), (77, 4096)]
+    Ws = [Dev(lib, synth.q4k_matrix(m, k, rng)) for m, k in shapes]
+    xs = {}
+    for j, (m, k) in enumerate(shapes):
+        if j in (1, 2):           # two products on one vector
+            xs[j] = xs.setdefault(1, Dev(lib, synth.activations(k, rng)))
+        else:
+            xs[j] = Dev(lib, synth.activations(k, rng))
+    n = len(shapes)
+
+    def run(entry):
+        outs = [Dev(lib, nbytes=m * 4, fill=0xFF) for m, _ in shapes]
+        descs = (capi.GemvDesc * n)(*[capi.GemvDesc(Ws[j].ptr, xs[j].ptr, outs[j].ptr, m, k) for j, (m, k) in enumerate(shapes)])
+        ws_bytes = lib.bpdq_batch_workspace_bytes(n, descs)
+        ws = Dev(lib, nbytes=ws_bytes)
+        if entry == "stream":
+            h = lib.bpdq_gemv_stream_create(n, descs, ws.ptr, ws_bytes)
+            assert h
+            for _ in range(3):
+                assert lib.bpdq_gemv_stream_run(h, None) == 0
+            lib.bpdq_sync()
+            lib.bpdq_gemv_stream_destroy(h)
+        else:
+            assert lib.bpd_qmatmul_q4k_q8k_batch_ws_cuda(n, descs, ws.ptr, ws_bytes, None) == 0
+            lib.bpdq_sync()
+        assert lib.bpdq_last_status() == 0
+        return [o.read(np.uint32) for o in outs]
+
+    a, b = run("batch"), run("stream")
+    for j in range(n):
+        assert np.array_equal(a[j], b[j]), j
+    assert not lib.bpdq_gemv_stream_create(0, None, None, 0)
+    lib.bpdq_clear_status()
