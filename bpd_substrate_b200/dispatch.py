@@ -114,13 +114,15 @@ class LayerSet:
         self._keep.append((wp, op, mp))
         return n, wp, op, mp, self.d_x + self.x_off[idx[0]], self.local[members[0]][2]
 
-    def enqueue_step(self, schedule="grouped", stream=None):
-        """Queues one decode step's GEMVs on ``stream`` (default: this object's stream)."""
+    def enqueue_step(self, schedule="grouped", stream=None, layers=None):
+        """Queues one decode step's GEMVs on ``stream`` (default: this object's stream); ``layers`` =
+        (first, last+1) restricts it to a range of layers."""
         lib, s = self.lib, (stream if stream is not None else self.stream)
+        first, last = layers if layers is not None else (0, self.n_layers)
         if self.tokens > 1:
             # several tokens per product: one launch per matrix (tensor-core kernel above 4 tokens)
             nm = len(self.local)
-            for layer in range(self.n_layers):
+            for layer in range(first, last):
                 for m, (_, rows, cols) in enumerate(self.local):
                     i = layer * nm + m
                     capi.check(lib.bpd_qmm_q4k_q8k_cuda(self.weights[layer][m], self.d_x + self.x_off[i],
@@ -128,6 +130,8 @@ class LayerSet:
                                                         None, s), "GEMM launch")
             return
         if schedule == "persistent":
+            if layers is not None:
+                raise ValueError("the persistent schedule covers the whole step")
             if self.stream_plan is None:
                 nm = len(self.local)
                 descs = (capi.GemvDesc * (nm * self.n_layers))()
@@ -145,7 +149,7 @@ class LayerSet:
             return
         if schedule == "batched":
             nm = len(self.local)
-            for layer in range(self.n_layers):
+            for layer in range(first, last):
                 descs = (capi.GemvDesc * nm)()
                 for m, (_, rows, cols) in enumerate(self.local):
                     i = layer * nm + m
@@ -160,7 +164,7 @@ class LayerSet:
                                                                     self.ws_stride, s), "batched GEMV launch")
             return
         groups = GROUPS_DECODE if schedule == "grouped" else GROUPS_NONE
-        for layer in range(self.n_layers):
+        for layer in range(first, last):
             for members in groups:
                 if len(members) == 1:
                     i = layer * len(self.local) + members[0]
@@ -172,23 +176,33 @@ class LayerSet:
                     rc = lib.bpd_qmatmul_q4k_q8k_multi_cuda(n, wp, op, mp, x, K, s)
                 capi.check(rc, "GEMV launch")
 
-    def capture(self, schedule="grouped"):
-        """Records a step into a CUDA graph (launch gaps disappear, PDL edges are kept)."""
-        if schedule not in self.graph:
+    def capture(self, schedule="grouped", layers=None):
+        """Records a step (or a range of its layers) into a CUDA graph (launch gaps disappear, PDL
+        edges are kept)."""
+        key = schedule if layers is None else (schedule, tuple(layers))
+        if key not in self.graph:
             lib = self.lib
-            self.enqueue_step(schedule)              # warm-up outside capture (attributes, caches)
+            self.enqueue_step(schedule, layers=layers)     # warm-up outside capture (attributes, caches)
             capi.check(lib.bpdq_stream_sync(self.stream))
             capi.check(lib.bpdq_graph_begin(self.stream), "graph capture")
-            self.enqueue_step(schedule)
+            self.enqueue_step(schedule, layers=layers)
             g = lib.bpdq_graph_end(self.stream)
             if not g:
                 raise capi.BpdqError(f"graph capture failed (status {lib.bpdq_last_status()})")
-            self.graph[schedule] = g
-        return self.graph[schedule]
+            self.graph[key] = g
+        return self.graph[key]
 
-    def step(self, schedule="grouped"):
-        """One step with inputs already on the device (asynchronous on self.stream)."""
-        capi.check(self.lib.bpdq_graph_launch(self.capture(schedule), self.stream), "graph launch")
+    def step(self, schedule="grouped", layers=None):
+        """One step (or a range of its layers) with inputs already on the device (asynchronous on
+        self.stream)."""
+        capi.check(self.lib.bpdq_graph_launch(self.capture(schedule, layers), self.stream), "graph launch")
+
+    def layer_output_range(self, first, last):
+        """(byte offset, bytes) of the outputs of layers [first, last) in the output arena."""
+        nm = len(self.local)
+        begin = self.o_off[first * nm]
+        end = self.o_off[last * nm] if last < self.n_layers else self.o_bytes
+        return begin, end - begin
 
     def step_host(self, x_host_ptr, out_host_ptr, schedule="grouped"):
         """One step from HOST buffers: copies the step's activations in, runs it, copies the
