@@ -315,12 +315,13 @@ def run_gpu(args):
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the public call with HOST buffers
+    host_kw = {} if chain else {"chunks": args.copy_chunks}
     for _ in range(min(args.warmup, 3)):
-        ls.step_host(x_host, o_host, schedule)
+        ls.step_host(x_host, o_host, schedule, **host_kw)
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        ls.step_host(x_host, o_host, schedule)
+        ls.step_host(x_host, o_host, schedule, **host_kw)
         exchange_all()
     t_e2e = time.perf_counter() - t0
 
@@ -405,6 +406,9 @@ def main():
                          "chain-separate: the reference's 13-call sequence per layer; chain-persistent: the whole token as "
                          "one cooperative launch with grid-wide barriers between dependent phases")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--copy-chunks", type=int, default=4,
+                    help="end-to-end leg: ranges of layers whose host copies run on their own streams under the other "
+                         "ranges' GEMVs (1: copy in, step, copy out in sequence)")
     ap.add_argument("--gather-chunks", type=int, default=1,
                     help="N > 1 GPUs: 1 = one all-gather after the step's GEMVs (default); more = the gather is cut into "
                          "chunks of layers, each on a second stream under the next chunk's GEMVs (measured slower at 2 GPUs: "

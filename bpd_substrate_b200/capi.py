@@ -48,6 +48,7 @@ SIGNATURES = {
     "bpdq_event_elapsed_ms": (f32, [vp, vp]),
     "bpdq_memset_async": (i32, [vp, i32, sz, vp]),
     "bpdq_stream_create": (vp, []),
+    "bpdq_stream_wait_event": (i32, [vp, vp]),
     "bpdq_stream_destroy": (None, [vp]),
     "bpdq_graph_begin": (i32, [vp]),
     "bpdq_graph_end": (vp, [vp]),

@@ -178,6 +178,11 @@ void* bpdq_stream_create(void)
     return (void*)s;
 }
 void bpdq_stream_destroy(void* s) { if (s) check_cuda(cudaStreamDestroy((cudaStream_t)s)); }
+// Work queued on `stream` after this call waits for the work that `ev` was recorded behind.
+int bpdq_stream_wait_event(void* stream, void* ev)
+{
+    return check_cuda(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)ev, 0));
+}
 
 // Capture everything launched on `stream` between begin and end into an executable graph.
 int bpdq_graph_begin(void* stream)

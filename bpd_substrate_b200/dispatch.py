@@ -85,6 +85,7 @@ class LayerSet:
         self._keep = []
         self.ws = None             # scratch for quantized activations (batched schedule)
         self.stream_plan = self.stream_ws = None      # plan and scratch of the persistent schedule
+        self.copy_streams = self.copy_events = None   # second and third stream of step_host
         capi.check(lib.bpdq_last_status(), "LayerSet setup")
 
     # ---- sizes
@@ -204,14 +205,47 @@ class LayerSet:
         end = self.o_off[last * nm] if last < self.n_layers else self.o_bytes
         return begin, end - begin
 
-    def step_host(self, x_host_ptr, out_host_ptr, schedule="grouped"):
-        """One step from HOST buffers: copies the step's activations in, runs it, copies the
-        outputs back and waits.  Pointers should be pinned (bpdq_host_alloc)."""
+    def step_host(self, x_host_ptr, out_host_ptr, schedule="grouped", chunks=4):
+        """One step from HOST buffers (pinned: bpdq_host_alloc): activations in, GEMVs, outputs back, wait.
+
+        The step is cut into ``chunks`` ranges of layers; the activations of a range are copied in on a
+        second stream and its outputs copied back on a third while other ranges compute, so that only
+        the first range's copy-in and the last range's copy-out are not hidden.  ``chunks=1`` (and the
+        persistent schedule, which is one launch) runs copy, step, copy in sequence on one stream."""
         lib = self.lib
-        capi.check(lib.bpdq_h2d_async(self.d_x, x_host_ptr, self.x_bytes, self.stream))
-        self.step(schedule)
-        capi.check(lib.bpdq_d2h_async(out_host_ptr, self.d_out, self.o_bytes, self.stream))
+        n = 1 if schedule == "persistent" else max(1, min(chunks, self.n_layers))
+        if n == 1:
+            capi.check(lib.bpdq_h2d_async(self.d_x, x_host_ptr, self.x_bytes, self.stream))
+            self.step(schedule)
+            capi.check(lib.bpdq_d2h_async(out_host_ptr, self.d_out, self.o_bytes, self.stream))
+            capi.check(lib.bpdq_stream_sync(self.stream))
+            return
+        if self.copy_streams is None:
+            self.copy_streams = (lib.bpdq_stream_create(), lib.bpdq_stream_create())
+            self.copy_events = [(lib.bpdq_event_create(), lib.bpdq_event_create()) for _ in range(self.n_layers)]
+        s_in, s_out = self.copy_streams
+        bounds = [self.n_layers * c // n for c in range(n + 1)]
+        ranges = [(bounds[c], bounds[c + 1]) for c in range(n)]
+        for c, (first, last) in enumerate(ranges):
+            begin, nbytes = self.layer_input_range(first, last)
+            capi.check(lib.bpdq_h2d_async(self.d_x + begin, x_host_ptr + begin, nbytes, s_in))
+            capi.check(lib.bpdq_event_record(self.copy_events[c][0], s_in))
+        for c, (first, last) in enumerate(ranges):
+            capi.check(lib.bpdq_stream_wait_event(self.stream, self.copy_events[c][0]))
+            self.step(schedule, (first, last))
+            capi.check(lib.bpdq_event_record(self.copy_events[c][1], self.stream))
+            capi.check(lib.bpdq_stream_wait_event(s_out, self.copy_events[c][1]))
+            begin, nbytes = self.layer_output_range(first, last)
+            capi.check(lib.bpdq_d2h_async(out_host_ptr + begin, self.d_out + begin, nbytes, s_out))
+        capi.check(lib.bpdq_stream_sync(s_out))
         capi.check(lib.bpdq_stream_sync(self.stream))
+
+    def layer_input_range(self, first, last):
+        """(byte offset, bytes) of the activations of layers [first, last) in the input arena."""
+        nm = len(self.local)
+        begin = self.x_off[first * nm]
+        end = self.x_off[last * nm] if last < self.n_layers else self.x_bytes
+        return begin, end - begin
 
     # ---- data movement helpers
     def upload_activations(self, x_all):
@@ -244,6 +278,13 @@ class LayerSet:
                 lib.bpdq_free(p)
         self.weights = []
         lib.bpdq_free(self.d_x)
+        if self.copy_streams is not None:
+            for st in self.copy_streams:
+                lib.bpdq_stream_destroy(st)
+            for a, b in self.copy_events:
+                lib.bpdq_event_destroy(a)
+                lib.bpdq_event_destroy(b)
+            self.copy_streams = None
         if self.stream_plan:
             lib.bpdq_gemv_stream_destroy(self.stream_plan)
             lib.bpdq_free(self.stream_ws)

@@ -71,6 +71,7 @@ int bpdq_event_record(void* ev, void* stream);
 float bpdq_event_elapsed_ms(void* start, void* stop);  /* waits for stop */
 int bpdq_memset_async(void* dev, int value, size_t bytes, void* stream);
 void* bpdq_stream_create(void);
+int bpdq_stream_wait_event(void* stream, void* ev);    /* later work on stream waits for the event */
 void bpdq_stream_destroy(void* stream);
 int bpdq_graph_begin(void* stream);        /* start capturing launches made on stream */
 void* bpdq_graph_end(void* stream);        /* -> executable graph handle, NULL on error */
