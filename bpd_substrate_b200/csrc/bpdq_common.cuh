@@ -47,7 +47,7 @@ struct Tuning {
 };
 Tuning& tuning();
 
-// gemv_q4k.cu: bulk-copy GEMV for Q8_0 weights (BPDQ_ERR_RANGE when the shape needs the generic kernel)
+// gemv_batch.cu: bulk-copy GEMV for Q8_0 weights (BPDQ_ERR_RANGE when the shape needs the generic kernel)
 int gemv_q8_0_fast(const uint8_t* W, const float* x, float* out, int N, int K, cudaStream_t s);
 int gemv_q8_0_fast_multi(int n, const uint8_t* const* Ws, float* const* outs, const int* Ns, const float* x, int K,
                          cudaStream_t s);

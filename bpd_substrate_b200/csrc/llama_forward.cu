@@ -1,5 +1,5 @@
 // Q8_0 Llama forward on the device: the composition of bpd_llama_block_cpu / bpd_llama_forward_cpu
-// (bench/bpd_cpu.c:5608-5798 of the reference) out of the Q8_0 products of q8_0.cu / gemv_q4k.cu and
+// (bench/bpd_cpu.c:5608-5798 of the reference) out of the Q8_0 products of q8_0.cu / gemv_batch.cu and
 // the small kernels below, which restate the reference's own steps:
 //   rms_norm with a binary64 sum of squares        bench/bpd_cpu.c:4959-4988
 //   rotary embedding, NORM pairing, freq factors   bench/bpd_cpu.c:5146-5183

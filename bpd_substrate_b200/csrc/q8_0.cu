@@ -4,7 +4,7 @@
 // int32 block dots of bpd_qdot_q8_0_q8_0_cpu (:4263-4280) for parity checks.
 //
 // A Q8_0 block is 34 bytes (fp16 scale, 32 int8) and only 2-byte aligned, so the simple kernels
-// here move 16-bit words; the GEMV fast path (gemv_q4k.cu) stages whole rows in shared memory
+// here move 16-bit words; the GEMV fast path (gemv_batch.cu) stages whole rows in shared memory
 // and realigns there.
 #include "bpdq_common.cuh"
 #include "../../include/bpdq.h"
