@@ -68,10 +68,18 @@ __global__ void __launch_bounds__(256) k_rmsnorm_records(const float* __restrict
     uint8_t* rec = records + (size_t)blockIdx.x * (cols / 256) * 2 * kXqStride;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float t = 0.0f;
-    // (data written by the launch before this one is read past L1: ld.global.cg)
-    for (int c = threadIdx.x; c < cols; c += 256) {
-        const float v = __ldcg(x + c);
-        t = fmaf(v, v, t);
+    // (data written by the launch before this one is read past L1: ld.global.cg).  The chain of FMAs
+    // is k_rms_norm's, but sixteen loads go out before the first of them is used: one L2 round trip
+    // per 4096 columns instead of sixteen.  A column past the end contributes fmaf(0, 0, t) = t.
+    for (int base = 0; base < cols; base += 16 * 256) {
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int c = base + i * 256 + (int)threadIdx.x;
+            v[i] = c < cols ? __ldcg(x + c) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) t = fmaf(v[i], v[i], t);
     }
     t = warp_sum(t);
     if (lane == 0) s_sum[warp] = t;

@@ -583,8 +583,10 @@ int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M,
     // kernels read them once per 64.  Measured on 14336x4096, 4096x14336, 4096x4096 and 1024x4096:
     // the tcgen05 kernel (128-row tiles, split K) is ahead from 24 tokens on matrices of 2^25
     // weights and more (from 33 when there are fewer than 8192 rows), mma.sync everywhere else.
-    if (tokens > 4 && layout == BPDQ_LAYOUT_BPD && xsrc == 0 && !dbg) {
-        const bool large = (long)M * K >= (1L << 25);
+    const bool large = (long)M * K >= (1L << 25);
+    // 3 and 4 tokens on such matrices: 13.3 / 18.6 us here (the dp4a work grows with the tokens)
+    // against 10.8 us for the mma.sync kernel; smaller matrices stay here (4096x4096: 9.0 against 10.2)
+    if (tokens > (large ? 2 : 4) && layout == BPDQ_LAYOUT_BPD && xsrc == 0 && !dbg) {
         if (large && (tokens >= 33 || (tokens >= 24 && M >= 8192)))
             return gemm_q4k_q8k_tc5(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s);
         return gemm_q4k_q8k_mma(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s);

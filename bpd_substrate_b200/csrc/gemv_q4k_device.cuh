@@ -352,9 +352,15 @@ __device__ __forceinline__ void cta_rmsnorm_records(const float* __restrict__ a,
     const int cols = nb * 256;
     for (int vw = warp; vw < 8; vw += nw) {
         float t = 0.0f;
-        for (int c = vw * 32 + lane; c < cols; c += 256) {
-            const float v = __ldcg(a + c);
-            t = fmaf(v, v, t);
+        for (int base = 0; base < cols; base += 16 * 256) {     // sixteen loads in flight, same chain of FMAs
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int c = base + i * 256 + vw * 32 + lane;
+                v[i] = c < cols ? __ldcg(a + c) : 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i++) t = fmaf(v[i], v[i], t);
         }
         t = warp_sum(t);
         if (lane == 0) s_sum[vw] = t;
