@@ -128,6 +128,10 @@ SIGNATURES = {
     "bpd_q8_0_block_dots_cuda": (i32, [vp, vp, vp, sz, vp]),
     "bpd_qmatmul_q8_0_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "bpd_embed_lookup_q8_0_cuda": (i32, [vp, vp, vp, i32, i32, vp]),
+    "bpd_q8_0_tiles_bytes": (sz, [i32, i32]),
+    "bpd_repack_q8_0_tiles_cuda": (i32, [vp, vp, i32, i32, vp]),
+    "bpd_unrepack_q8_0_tiles_cuda": (i32, [vp, vp, i32, i32, vp]),
+    "bpd_qmatmul_q8_0_tiles_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "gpu_vecmat_q8_0": (None, [vp, vp, vp, i32, i32]),
     "gpu_matmul_q4k": (None, [vp, vp, vp, i32, i32, i32]),
 }

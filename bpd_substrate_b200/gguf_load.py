@@ -199,3 +199,35 @@ def repack_q4k_bpd_to_ggml(raw):
     blocks = np.array(raw, np.uint8).reshape(-1, 144)
     blocks[:, 16:] = _q4k_pack(_q4k_nibbles_in_element_order(blocks[:, 16:], "bpd"), "ggml")
     return blocks.reshape(-1)
+
+
+# ---- Q8_0 rows <-> the tensor-core tiles of bpd_qmatmul_q8_0_tiles_cuda (a permutation of bytes)
+Q8_TILE_ROWS, Q8_TILE_UNIT = 128, 128 * 34
+
+
+def repack_q8_0_to_tiles(raw, rows, cols):
+    """Q8_0 rows [rows][cols/32][34] -> units [row tile][block][4352]: the 128x32 int8 quants with element
+    (r, k) at (k/16)*2048 + (r/8)*128 + (r%8)*16 + k%16, then the 128 fp16 scales.  Rows of the last tile
+    beyond ``rows`` are zero.  Host twin of bpd_repack_q8_0_tiles_cuda, for loaders that repack before upload."""
+    nb = cols // 32
+    tiles = -(-rows // Q8_TILE_ROWS)
+    src = np.zeros((tiles * Q8_TILE_ROWS, nb, 34), np.uint8)
+    src[:rows] = np.asarray(raw, np.uint8).reshape(rows, nb, 34)
+    src = src.reshape(tiles, 16, 8, nb, 34)                       # [tile][r/8][r%8][block][byte]
+    out = np.empty((tiles, nb, Q8_TILE_UNIT), np.uint8)
+    quants = src[..., 2:].reshape(tiles, 16, 8, nb, 2, 16)         # [tile][r/8][r%8][block][k/16][k%16]
+    out[:, :, :4096] = quants.transpose(0, 3, 4, 1, 2, 5).reshape(tiles, nb, 4096)
+    out[:, :, 4096:] = src[..., :2].reshape(tiles, 128, nb, 2).transpose(0, 2, 1, 3).reshape(tiles, nb, 256)
+    return out.reshape(-1)
+
+
+def repack_tiles_to_q8_0(tiles_raw, rows, cols):
+    """The inverse of :func:`repack_q8_0_to_tiles`."""
+    nb = cols // 32
+    tiles = -(-rows // Q8_TILE_ROWS)
+    units = np.asarray(tiles_raw, np.uint8).reshape(tiles, nb, Q8_TILE_UNIT)
+    out = np.empty((tiles, 16, 8, nb, 34), np.uint8)
+    quants = units[:, :, :4096].reshape(tiles, nb, 2, 16, 8, 16)   # [tile][block][k/16][r/8][r%8][k%16]
+    out[..., 2:] = quants.transpose(0, 3, 4, 1, 2, 5).reshape(tiles, 16, 8, nb, 32)
+    out[..., :2] = units[:, :, 4096:].reshape(tiles, nb, 16, 8, 2).transpose(0, 2, 3, 1, 4)
+    return out.reshape(tiles * Q8_TILE_ROWS, nb * 34)[:rows].reshape(-1)

@@ -3,6 +3,11 @@
     python -m bpd_substrate_b200.measure            # prints one JSON object per configuration
     python -m bpd_substrate_b200.measure --llama-decode [LAYERS]
                                                     # Q8_0 Llama forward, 8B-shaped layers: ms per decoded token
+    python -m bpd_substrate_b200.measure --q8-tiles [N K]
+                                                    # Q8_0 many-token product on re-tiled weights (tcgen05)
+                                                    # beside the row-layout kernel, 1..512 tokens
+    python -m bpd_substrate_b200.measure --q8-tiles-once TOKENS [N K]
+                                                    # five launches of the re-tiled product: a small case for a profiler
     python -m bpd_substrate_b200.measure --gemm-once tc5 64 [N K]
                                                     # five launches of one many-token product (kernel
                                                     # tc5 | mma | dispatch): a small case for a profiler
@@ -77,6 +82,54 @@ def gemm_once(lib, kernel, tokens, N=14336, K=4096, launches=5):
     return 0 if status == 0 else 1
 
 
+def q8_tiles(lib, N=14336, K=4096, token_counts=(1, 4, 16, 32, 64, 128, 512)):
+    """Times bpd_qmatmul_q8_0_tiles_cuda against bpd_qmatmul_q8_0_cuda (one pass over the rows per
+    token) on cold weights; prints one JSON object per token count."""
+    tm = Timer(lib)
+    s = tm.stream
+    peak = _peak()
+    W = synth.q8_0_matrix(N, K, 1)
+    n = _copies(W.nbytes)
+    rows = [_dev(lib, W) for _ in range(n)]
+    tiles = []
+    for r in rows:
+        t = lib.bpdq_alloc(lib.bpd_q8_0_tiles_bytes(N, K))
+        capi.check(lib.bpd_repack_q8_0_tiles_cuda(r, t, N, K, s))
+        tiles.append(t)
+    for tokens in token_counts:
+        x = _dev(lib, synth.activations(K, 2, rows=tokens))
+        o = lib.bpdq_alloc(tokens * N * 4)
+        us_t = tm.run(lambda i: lib.bpd_qmatmul_q8_0_tiles_cuda(tiles[i % n], x, o, tokens, N, K, s), 30)
+        us_r = tm.run(lambda i: lib.bpd_qmatmul_q8_0_cuda(rows[i % n], x, o, tokens, N, K, s), 30 if tokens <= 16 else 5)
+        nbytes = W.nbytes + tokens * (K + N) * 4
+        print(json.dumps(dict(config=f"Q8_0 x Q8_0 {N}x{K}, {tokens} tokens", tiles_us=round(us_t, 2), rows_us=round(us_r, 2),
+                              algorithmic_bytes=nbytes, tiles_gbs=round(nbytes / us_t / 1e3, 1),
+                              tiles_pct_of_measured_peak=round(100 * nbytes / us_t / 1e3 / peak, 1),
+                              tiles_tera_int8_macs_per_s=round(tokens * N * K / us_t / 1e6, 2),
+                              status=lib.bpdq_last_status())), flush=True)
+        lib.bpdq_free(x)
+        lib.bpdq_free(o)
+    for p in rows + tiles:
+        lib.bpdq_free(p)
+    return 0 if lib.bpdq_last_status() == 0 else 1
+
+
+def q8_tiles_once(lib, tokens, N=14336, K=4096, launches=5):
+    w = _dev(lib, synth.q8_0_matrix(N, K, 1))
+    t = lib.bpdq_alloc(lib.bpd_q8_0_tiles_bytes(N, K))
+    capi.check(lib.bpd_repack_q8_0_tiles_cuda(w, t, N, K, None))
+    x = _dev(lib, synth.activations(K, 2, rows=tokens))
+    o = lib.bpdq_alloc(tokens * N * 4)
+    for _ in range(launches):
+        capi.check(lib.bpd_qmatmul_q8_0_tiles_cuda(t, x, o, tokens, N, K, None))
+    lib.bpdq_sync()
+    status = lib.bpdq_last_status()
+    for p in (w, t, x, o):
+        lib.bpdq_free(p)
+    print(json.dumps({"q8_tiles_once": tokens, "N": N, "K": K, "status": status}))
+    return 0 if status == 0 else 1
+
+
 def llama_decode(lib, n_layers=4, steps=32):
     """Single-token steps of bpd_llama_forward_cuda on a synthetic model with Llama-3-8B-shaped layers
     (32 heads, 8 KV heads, head 128, FFN 14336; vocabulary cut to 32000 to keep host generation short),
@@ -140,6 +193,10 @@ def main():
     lib.bpdq_clear_status()
     if len(sys.argv) >= 2 and sys.argv[1] == "--llama-decode":
         return llama_decode(lib, *[int(v) for v in sys.argv[2:3]])
+    if len(sys.argv) >= 2 and sys.argv[1] == "--q8-tiles":
+        return q8_tiles(lib, *[int(v) for v in sys.argv[2:4]])
+    if len(sys.argv) >= 3 and sys.argv[1] == "--q8-tiles-once":
+        return q8_tiles_once(lib, *[int(v) for v in sys.argv[2:5]])
     if len(sys.argv) >= 4 and sys.argv[1] == "--gemm-once":
         extra = [int(v) for v in sys.argv[4:6]]
         return gemm_once(lib, sys.argv[2], int(sys.argv[3]), *extra)

@@ -261,6 +261,17 @@ int bpd_qmatmul_q8_0_cuda(const uint8_t* W, const float* X, float* out, int M, i
 /* bench/bpd_cpu.c:4002-4013  bpd_embed_lookup_q8_0_cpu */
 int bpd_embed_lookup_q8_0_cuda(const uint8_t* table, const int32_t* ids, float* out, int n_tokens, int embed_dim,
                                void* stream);
+/* Q8_0 re-tiled for the tensor cores: the idea of inference/llamatov_c_inference.py:88-100 ("Q8 padded 64B
+ * coalesced [nb,N,64]") as a pure permutation of the Q8_0 bytes.  Per tile of 128 rows and block of 32
+ * elements a unit of 4352 bytes: the 128x32 int8 quants, element (r,k) at (k/16)*2048 + (r/8)*128 +
+ * (r%8)*16 + k%16, then the 128 fp16 scales; units ordered [row tile][block]; rows beyond N are zero.
+ * tiles must be 16-byte aligned and bpd_q8_0_tiles_bytes(N, K) long. */
+size_t bpd_q8_0_tiles_bytes(int N, int K);
+int bpd_repack_q8_0_tiles_cuda(const uint8_t* raw, uint8_t* tiles, int N, int K, void* stream);
+int bpd_unrepack_q8_0_tiles_cuda(const uint8_t* tiles, uint8_t* raw, int N, int K, void* stream);
+/* bench/bpd_cpu.c:4295-4315  bpd_qmatmul_q8_0_cpu on re-tiled weights, any number of tokens M, on the
+ * tcgen05 tensor cores; the fp32 operations per block are the scalar reference's, in its order */
+int bpd_qmatmul_q8_0_tiles_cuda(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, void* stream);
 /* gpu_vecmat's argument order (lib/kernel_templates_llama.pl:147-158) with Q8_0 rows [n][k/32][34] */
 void gpu_vecmat_q8_0(const float* a, const uint8_t* wq, float* c, int k, int n);
 
