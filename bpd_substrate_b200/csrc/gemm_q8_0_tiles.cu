@@ -36,20 +36,18 @@ namespace bpdq {
 constexpr int kTileRows = 128;
 constexpr int kTileQuants = kTileRows * 32;              // 4096
 constexpr int kTileUnit = kTileRows * BPDQ_Q80_BYTES;    // 4352
-constexpr int kChunkBlocks = 4;                          // blocks per ring stage
-constexpr int kAccSlots = 8;                             // accumulators in flight between the MMA and the epilogue
 
 template <int T>
 struct Q8tShape {
     static constexpr int kEpiWarps = 8;
     static constexpr int kThreads = 32 * (2 + kEpiWarps);
     static constexpr int kCols = T / 2;                  // token columns per epilogue warp
+    static constexpr int kChunk = T == 64 ? 4 : 8;       // blocks per ring stage = per accumulator set = per barrier round
     static constexpr int kActUnit = 36 * T;              // T x 32 int8 (canonical order) + T fp32 scales
-    static constexpr int kStageBytes = kChunkBlocks * (kTileUnit + kActUnit);
-    static constexpr int kStages = T == 64 ? 6 : 4;
-    static constexpr int kTmemCols = kAccSlots * T;      // 128, 256 or 512: a power of two >= 32
-    static constexpr int kMinCtas = T == 64 ? 1 : 2;
-    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 8 * (2 * kStages + 2 * kAccSlots) + 16;
+    static constexpr int kStageBytes = kChunk * (kTileUnit + kActUnit);
+    static constexpr int kStages = T == 64 ? 8 : 5;      // 213, 220 and 197 KB of ring
+    static constexpr int kTmemCols = 2 * kChunk * T;     // two accumulator sets: 256 or 512 columns
+    static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 8 * (2 * kStages + 4) + 16;
 };
 
 // ------------------------------------------------------------------ re-tiling (and its inverse)
@@ -133,25 +131,53 @@ __global__ void __launch_bounds__(256) k_quant_q8_0_tiles(const float* __restric
 
 // ------------------------------------------------------------------ the product
 
+// Packed pairs of fp32 (add/mul.rn.f32x2): each half is the IEEE operation of the scalar instruction.
+__device__ __forceinline__ uint64_t pack2(float a, float b)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t r, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r)); }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 template <int T>
-__global__ void __launch_bounds__(Q8tShape<T>::kThreads, Q8tShape<T>::kMinCtas)
+__global__ void __launch_bounds__(Q8tShape<T>::kThreads, 1)
 k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__ acts, float* __restrict__ out, int M, int N,
                   int nb, int* err)
 {
     using S = Q8tShape<T>;
-    constexpr int kStages = S::kStages;
+    constexpr int kStages = S::kStages, G = S::kChunk;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)kStages * S::kStageBytes);   // [kStages] bulk copies landed
     uint64_t* empty = full + kStages;                 // [kStages] all epilogue warps are done with the stage
-    uint64_t* acc_full = empty + kStages;             // [kAccSlots] MMA commit
-    uint64_t* acc_empty = acc_full + kAccSlots;       // [kAccSlots] all epilogue warps have read the accumulator
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccSlots);
+    uint64_t* acc_full = empty + kStages;             // [2] MMA commit: the accumulators of a chunk are complete
+    uint64_t* acc_empty = acc_full + 2;               // [2] all epilogue warps have read them
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], S::kEpiWarps); }
-        for (int s = 0; s < kAccSlots; s++) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], S::kEpiWarps); }
+        for (int s = 0; s < 2; s++) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], S::kEpiWarps); }
         mbar_init_fence();
     }
     if (warp == 1) {
@@ -166,9 +192,9 @@ k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__
     const uint32_t tmem_base = *tmem_slot;
     pdl_launch_dependents();
 
-    const int n_chunks = (nb + kChunkBlocks - 1) / kChunkBlocks;
-    auto blocks_in = [nb](int c) { const int g = nb - c * kChunkBlocks; return g < kChunkBlocks ? g : kChunkBlocks; };
-    constexpr int kActOff = kChunkBlocks * kTileUnit;     // activation units follow the weight units of a stage
+    const int n_chunks = (nb + G - 1) / G;
+    auto blocks_in = [nb](int c) { const int g = nb - c * G; return g < G ? g : G; };
+    constexpr int kActOff = G * kTileUnit;            // activation units follow the weight units of a stage
 
     if (warp == 0) {
         // ---------------- producer.  The weights of the first ring round are requested before the
@@ -180,96 +206,108 @@ k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__
             for (int i = 0; i < ahead; i++) {
                 const uint32_t g = (uint32_t)blocks_in(i);
                 mbar_expect_tx(&full[i], g * (uint32_t)(kTileUnit + S::kActUnit));
-                bulk_g2s(ring + (size_t)i * S::kStageBytes, wsrc + (size_t)i * kChunkBlocks * kTileUnit, g * kTileUnit, &full[i]);
+                bulk_g2s(ring + (size_t)i * S::kStageBytes, wsrc + (size_t)i * G * kTileUnit, g * kTileUnit, &full[i]);
             }
             pdl_wait();
             for (int i = 0; i < ahead; i++)
-                bulk_g2s(ring + (size_t)i * S::kStageBytes + kActOff, asrc + (size_t)i * kChunkBlocks * S::kActUnit,
+                bulk_g2s(ring + (size_t)i * S::kStageBytes + kActOff, asrc + (size_t)i * G * S::kActUnit,
                          (uint32_t)blocks_in(i) * S::kActUnit, &full[i]);
             int s = 0;
             uint32_t par = 0;      // parity of the epilogue's release one ring round back
             for (int i = kStages; i < n_chunks; i++) {
-                if (!mbar_wait_sleepy(&empty[s], par, err, 31)) break;
+                if (!mbar_wait_bounded(&empty[s], par, err, 31)) break;
                 const uint32_t g = (uint32_t)blocks_in(i);
                 uint8_t* stage = ring + (size_t)s * S::kStageBytes;
                 mbar_expect_tx(&full[s], g * (uint32_t)(kTileUnit + S::kActUnit));
-                bulk_g2s(stage, wsrc + (size_t)i * kChunkBlocks * kTileUnit, g * kTileUnit, &full[s]);
-                bulk_g2s(stage + kActOff, asrc + (size_t)i * kChunkBlocks * S::kActUnit, g * S::kActUnit, &full[s]);
+                bulk_g2s(stage, wsrc + (size_t)i * G * kTileUnit, g * kTileUnit, &full[s]);
+                bulk_g2s(stage + kActOff, asrc + (size_t)i * G * S::kActUnit, g * S::kActUnit, &full[s]);
                 if (++s == kStages) { s = 0; par ^= 1u; }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer.  The whole warp walks the loop so that descriptors and ring
-        // counters stay warp-uniform; one elected lane issues.
+        // counters stay warp-uniform; one elected lane issues a chunk's MMAs and one commit.
         const uint32_t idesc = umma_i8_idesc(kTileRows, T);
-        int s = 0, slot = 0;
-        uint32_t full_par = 0, slot_par = 1;    // slot_par: parity of "accumulator free", first round passes
-        bool gave_up = false;
-        for (int c = 0; c < n_chunks && !gave_up; c++) {
+        int s = 0;
+        uint32_t full_par = 0;
+        for (int c = 0; c < n_chunks; c++) {
+            const int a = c & 1;
             if (!mbar_wait_bounded(&full[s], full_par, err, 32)) break;
+            if (c >= 2 && !mbar_wait_bounded(&acc_empty[a], (uint32_t)((c >> 1) - 1) & 1u, err, 33)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t stage = smem_addr(ring + (size_t)s * S::kStageBytes);
             const int g_n = blocks_in(c);
-            for (int g = 0; g < g_n; g++) {
-                if (c * kChunkBlocks + g >= kAccSlots) {
-                    if (!mbar_wait_bounded(&acc_empty[slot], slot_par, err, 33)) { gave_up = true; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                }
-                if (elect_one()) {
+            if (elect_one()) {
+                for (int g = 0; g < g_n; g++) {
                     const uint64_t adesc = umma_desc(stage + (uint32_t)g * kTileUnit, 2048, 128);
                     const uint64_t bdesc = umma_desc(stage + kActOff + (uint32_t)g * S::kActUnit, 16 * T, 128);
-                    umma_i8_ss<0>(tmem_base + (uint32_t)(slot * T), adesc, bdesc, idesc);
-                    umma_commit(&acc_full[slot]);
+                    umma_i8_ss<0>(tmem_base + (uint32_t)((a * G + g) * T), adesc, bdesc, idesc);
                 }
-                __syncwarp();
-                if (++slot == kAccSlots) { slot = 0; slot_par ^= 1u; }
+                umma_commit(&acc_full[a]);
             }
+            __syncwarp();
             if (++s == kStages) { s = 0; full_par ^= 1u; }
         }
     } else {
         // ---------------- epilogue
-        constexpr int kCols = S::kCols;
+        constexpr int kCols = S::kCols, kPairs = kCols / 2;
         const int e = warp - 2;
         const int quarter = warp & 3;                     // the TMEM lanes this warp may read: 32*(warp%4)..
         const int c0 = (e >> 2) * kCols;                  // first token column of this warp
         const int r = 32 * quarter + lane;
         const uint32_t taddr0 = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0;
-        float acc[kCols];
+        const uint64_t unmagic = pack2(-12582912.0f, -12582912.0f);
+        uint64_t acc[kPairs];
 #pragma unroll
-        for (int t = 0; t < kCols; t++) acc[t] = 0.0f;
-        int s = 0, slot = 0;
-        uint32_t full_par = 0, slot_par = 0;
+        for (int t = 0; t < kPairs; t++) acc[t] = 0ull;
+        int s = 0;
+        uint32_t full_par = 0;
         bool gave_up = false;
         pdl_wait();
-        for (int c = 0; c < n_chunks && !gave_up; c++) {
-            if (!mbar_wait_sleepy(&full[s], full_par, err, 34)) break;
+        for (int c = 0; c < n_chunks; c++) {
+            const int a = c & 1;
+            if (!mbar_wait_bounded(&full[s], full_par, err, 34)) { gave_up = true; break; }
+            if (!mbar_wait_bounded(&acc_full[a], (uint32_t)(c >> 1) & 1u, err, 35)) { gave_up = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint8_t* stage = ring + (size_t)s * S::kStageBytes;
             const int g_n = blocks_in(c);
-            for (int g = 0; g < g_n; g++) {
-                if (!mbar_wait_sleepy(&acc_full[slot], slot_par, err, 35)) { gave_up = true; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                int v[kCols];
+            int v[G][kCols];
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                const uint32_t ta = taddr0 + (uint32_t)((a * G + g) * T);
                 if constexpr (kCols >= 16) {
 #pragma unroll
-                    for (int j = 0; j < kCols / 16; j++) tmem_ld(taddr0 + (uint32_t)(slot * T + 16 * j), *reinterpret_cast<int(*)[16]>(&v[16 * j]));
+                    for (int j = 0; j < kCols / 16; j++) tmem_ld(ta + 16 * j, *reinterpret_cast<int(*)[16]>(&v[g][16 * j]));
                 } else {
-                    tmem_ld(taddr0 + (uint32_t)(slot * T), *reinterpret_cast<int(*)[8]>(&v[0]));
+                    tmem_ld(ta, *reinterpret_cast<int(*)[8]>(&v[g][0]));
                 }
-                const float wd = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(stage + g * kTileUnit + kTileQuants + 2 * r));
-                const float* ad = reinterpret_cast<const float*>(stage + kActOff + g * S::kActUnit + 32 * T) + c0;
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[slot]);
+            }
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[a]);
 #pragma unroll
-                for (int t4 = 0; t4 < kCols / 4; t4++) {
-                    const float4 a4 = *reinterpret_cast<const float4*>(ad + 4 * t4);
-                    acc[4 * t4 + 0] = __fadd_rn(acc[4 * t4 + 0], __fmul_rn((float)v[4 * t4 + 0], __fmul_rn(wd, a4.x)));
-                    acc[4 * t4 + 1] = __fadd_rn(acc[4 * t4 + 1], __fmul_rn((float)v[4 * t4 + 1], __fmul_rn(wd, a4.y)));
-                    acc[4 * t4 + 2] = __fadd_rn(acc[4 * t4 + 2], __fmul_rn((float)v[4 * t4 + 2], __fmul_rn(wd, a4.z)));
-                    acc[4 * t4 + 3] = __fadd_rn(acc[4 * t4 + 3], __fmul_rn((float)v[4 * t4 + 3], __fmul_rn(wd, a4.w)));
+            for (int g = 0; g < G; g++) {
+                if (g < g_n) {
+                    const float wd = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(stage + g * kTileUnit + kTileQuants + 2 * r));
+                    const uint64_t wd2 = pack2(wd, wd);
+                    const float* ad = reinterpret_cast<const float*>(stage + kActOff + g * S::kActUnit + 32 * T) + c0;
+#pragma unroll
+                    for (int t4 = 0; t4 < kCols / 4; t4++) {
+                        const float4 a4 = *reinterpret_cast<const float4*>(ad + 4 * t4);
+                        // term = RN((float)sumi * scale) with one fused operation and no conversion: the integer
+                        // add on the bits gives x = 1.5*2^23 + sumi exactly (|sumi| < 2^22); scale = wd*ad is exact
+                        // (two 11-bit significands), so is 1.5*2^23 * scale (24 bits); hence
+                        // fma(x, scale, -1.5*2^23*scale) rounds the exact sumi*scale once, as the reference's
+                        // multiplication does.  Being an fma it also cannot be merged with the add that follows
+                        // (the assembler does merge mul.rn.f32x2 + add.rn.f32x2 into one fma).
+                        const uint64_t x0 = pack2(__int_as_float(v[g][4 * t4 + 0] + 0x4B400000), __int_as_float(v[g][4 * t4 + 1] + 0x4B400000));
+                        const uint64_t x1 = pack2(__int_as_float(v[g][4 * t4 + 2] + 0x4B400000), __int_as_float(v[g][4 * t4 + 3] + 0x4B400000));
+                        const uint64_t s0 = mul2(wd2, pack2(a4.x, a4.y)), s1 = mul2(wd2, pack2(a4.z, a4.w));
+                        acc[2 * t4 + 0] = add2(acc[2 * t4 + 0], fma2(x0, s0, mul2(s0, unmagic)));
+                        acc[2 * t4 + 1] = add2(acc[2 * t4 + 1], fma2(x1, s1, mul2(s1, unmagic)));
+                    }
                 }
-                if (++slot == kAccSlots) { slot = 0; slot_par ^= 1u; }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
@@ -278,9 +316,12 @@ k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__
         const long n = (long)blockIdx.x * kTileRows + r;
         if (!gave_up && n < N) {
 #pragma unroll
-            for (int t = 0; t < kCols; t++) {
-                const long tok = (long)blockIdx.y * T + c0 + t;
-                if (tok < M) out[(size_t)tok * N + n] = acc[t];
+            for (int t = 0; t < kPairs; t++) {
+                float lo, hi;
+                unpack2(acc[t], lo, hi);
+                const long tok = (long)blockIdx.y * T + c0 + 2 * t;
+                if (tok < M) out[(size_t)tok * N + n] = lo;
+                if (tok + 1 < M) out[(size_t)(tok + 1) * N + n] = hi;
             }
         }
     }
