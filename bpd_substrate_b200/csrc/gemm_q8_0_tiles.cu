@@ -19,12 +19,13 @@
 // bytes land in shared memory exactly as the MMA's A descriptor reads them: no transform warps, no
 // per-weight instructions.  Rows beyond N in the last tile are zero.
 //
-// Kernel: one CTA = one tile of 128 rows x one tile of T tokens (16, 32 or 64), ten warps:
+// Kernel: one CTA = one tile of 128 rows x one tile of T tokens (16, 32 or 64), ten or eighteen warps:
 //   warp 0     producer: per ring stage one bulk copy of four weight units and one of four activation units
 //   warp 1     allocates tensor memory; one lane issues one MMA per block into a ring of eight
 //              accumulators (T columns each) and commits each to an mbarrier
-//   warps 2-9  epilogue: thread r of a TMEM lane quarter owns row r; two warps per quarter split the
-//              tokens; tcgen05.ld, then the three fp32 operations above per (row, token, block)
+//   warps 2-   epilogue (8 warps at 16 tokens, else 16): thread r of a TMEM lane quarter owns row r; the two
+//              or four warps of a quarter split the tokens; tcgen05.ld, then the fp32 operations above per
+//              (row, token, block)
 // All mbarrier waits are bounded; on a timeout the role records an error code and leaves, the others
 // time out in turn, and warp 1 frees the tensor memory before it returns.
 #include "bpdq_common.cuh"
@@ -39,9 +40,10 @@ constexpr int kTileUnit = kTileRows * BPDQ_Q80_BYTES;    // 4352
 
 template <int T>
 struct Q8tShape {
-    static constexpr int kEpiWarps = 8;
+    static constexpr int kEpiWarps = T == 16 ? 8 : 16;   // two or four per TMEM lane quarter (per scheduler): the
+                                                         // epilogue's dependent fp32 chains need that many to keep issuing
     static constexpr int kThreads = 32 * (2 + kEpiWarps);
-    static constexpr int kCols = T / 2;                  // token columns per epilogue warp
+    static constexpr int kCols = T / (kEpiWarps / 4);    // token columns per epilogue warp: 8, 8, 16
     static constexpr int kChunk = T == 64 ? 4 : 8;       // blocks per ring stage = per accumulator set = per barrier round
     static constexpr int kActUnit = 36 * T;              // T x 32 int8 (canonical order) + T fp32 scales
     static constexpr int kStageBytes = kChunk * (kTileUnit + kActUnit);
@@ -130,34 +132,6 @@ __global__ void __launch_bounds__(256) k_quant_q8_0_tiles(const float* __restric
 }
 
 // ------------------------------------------------------------------ the product
-
-// Packed pairs of fp32 (add/mul.rn.f32x2): each half is the IEEE operation of the scalar instruction.
-__device__ __forceinline__ uint64_t pack2(float a, float b)
-{
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t r, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(r)); }
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b)
-{
-    uint64_t r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
-{
-    uint64_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
-{
-    uint64_t r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
 
 template <int T>
 __global__ void __launch_bounds__(Q8tShape<T>::kThreads, 1)
@@ -250,16 +224,15 @@ k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__
         }
     } else {
         // ---------------- epilogue
-        constexpr int kCols = S::kCols, kPairs = kCols / 2;
+        constexpr int kCols = S::kCols;
         const int e = warp - 2;
         const int quarter = warp & 3;                     // the TMEM lanes this warp may read: 32*(warp%4)..
         const int c0 = (e >> 2) * kCols;                  // first token column of this warp
         const int r = 32 * quarter + lane;
         const uint32_t taddr0 = tmem_base + ((uint32_t)(32 * quarter) << 16) + (uint32_t)c0;
-        const uint64_t unmagic = pack2(-12582912.0f, -12582912.0f);
-        uint64_t acc[kPairs];
+        float acc[kCols];
 #pragma unroll
-        for (int t = 0; t < kPairs; t++) acc[t] = 0ull;
+        for (int t = 0; t < kCols; t++) acc[t] = 0.0f;
         int s = 0;
         uint32_t full_par = 0;
         bool gave_up = false;
@@ -286,28 +259,34 @@ k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[a]);
+            // one block: the reference's three roundings as scalar instructions (the packed f32x2 forms run on
+            // half of the fp32 lanes only, and the assembler merges mul.rn.f32x2 + add.rn.f32x2 into one fma,
+            // which rounds once where the reference rounds twice).  (float)sumi without the slow conversion
+            // instruction: an integer add on the bits gives 1.5*2^23 + sumi exactly (|sumi| < 2^22), and taking
+            // 1.5*2^23 off again is exact too.
+            auto block = [&](int g) {
+                const float wd = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(stage + g * kTileUnit + kTileQuants + 2 * r));
+                const float* ad = reinterpret_cast<const float*>(stage + kActOff + g * S::kActUnit + 32 * T) + c0;
 #pragma unroll
-            for (int g = 0; g < G; g++) {
-                if (g < g_n) {
-                    const float wd = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(stage + g * kTileUnit + kTileQuants + 2 * r));
-                    const uint64_t wd2 = pack2(wd, wd);
-                    const float* ad = reinterpret_cast<const float*>(stage + kActOff + g * S::kActUnit + 32 * T) + c0;
+                for (int t4 = 0; t4 < kCols / 4; t4++) {
+                    const float4 a4 = *reinterpret_cast<const float4*>(ad + 4 * t4);
+                    const float a[4] = {a4.x, a4.y, a4.z, a4.w};
 #pragma unroll
-                    for (int t4 = 0; t4 < kCols / 4; t4++) {
-                        const float4 a4 = *reinterpret_cast<const float4*>(ad + 4 * t4);
-                        // term = RN((float)sumi * scale) with one fused operation and no conversion: the integer
-                        // add on the bits gives x = 1.5*2^23 + sumi exactly (|sumi| < 2^22); scale = wd*ad is exact
-                        // (two 11-bit significands), so is 1.5*2^23 * scale (24 bits); hence
-                        // fma(x, scale, -1.5*2^23*scale) rounds the exact sumi*scale once, as the reference's
-                        // multiplication does.  Being an fma it also cannot be merged with the add that follows
-                        // (the assembler does merge mul.rn.f32x2 + add.rn.f32x2 into one fma).
-                        const uint64_t x0 = pack2(__int_as_float(v[g][4 * t4 + 0] + 0x4B400000), __int_as_float(v[g][4 * t4 + 1] + 0x4B400000));
-                        const uint64_t x1 = pack2(__int_as_float(v[g][4 * t4 + 2] + 0x4B400000), __int_as_float(v[g][4 * t4 + 3] + 0x4B400000));
-                        const uint64_t s0 = mul2(wd2, pack2(a4.x, a4.y)), s1 = mul2(wd2, pack2(a4.z, a4.w));
-                        acc[2 * t4 + 0] = add2(acc[2 * t4 + 0], fma2(x0, s0, mul2(s0, unmagic)));
-                        acc[2 * t4 + 1] = add2(acc[2 * t4 + 1], fma2(x1, s1, mul2(s1, unmagic)));
+                    for (int j = 0; j < 4; j++) {
+                        const float f = __fadd_rn(__int_as_float(v[g][4 * t4 + j] + 0x4B400000), -12582912.0f);
+                        acc[4 * t4 + j] = __fadd_rn(acc[4 * t4 + j], __fmul_rn(f, __fmul_rn(wd, a[j])));
                     }
                 }
+            };
+            if (g_n == G) {
+                // whole chunk: no conditions between the blocks, so that the scale loads of all of them can be
+                // issued ahead of the arithmetic
+#pragma unroll
+                for (int g = 0; g < G; g++) block(g);
+            } else {
+#pragma unroll
+                for (int g = 0; g < G; g++)
+                    if (g < g_n) block(g);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
@@ -316,12 +295,9 @@ k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__
         const long n = (long)blockIdx.x * kTileRows + r;
         if (!gave_up && n < N) {
 #pragma unroll
-            for (int t = 0; t < kPairs; t++) {
-                float lo, hi;
-                unpack2(acc[t], lo, hi);
-                const long tok = (long)blockIdx.y * T + c0 + 2 * t;
-                if (tok < M) out[(size_t)tok * N + n] = lo;
-                if (tok + 1 < M) out[(size_t)(tok + 1) * N + n] = hi;
+            for (int t = 0; t < kCols; t++) {
+                const long tok = (long)blockIdx.y * T + c0 + t;
+                if (tok < M) out[(size_t)tok * N + n] = acc[t];
             }
         }
     }
@@ -415,7 +391,22 @@ int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int
     if (!tiles || !X || !out) return latch(BPDQ_ERR_ARG);
     if (((uintptr_t)tiles & 15) || ((uintptr_t)X & 15) || ((uintptr_t)out & 3)) return latch(BPDQ_ERR_ALIGN);
     const int nb = K / 32;
-    const int T = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    // Token tile: 16, 32 or 64, whichever needs the least time by a model of waves of CTAs over the SMs
+    // times the measured cost of one block at that width (1 : 1.45 : 2.7); a narrower tile re-reads the
+    // weights once more per tile, from L2, and spreads the epilogue's work over more SMs.
+    int T = 16;
+    {
+        const long row_tiles = (N + kTileRows - 1) / kTileRows;
+        const int widths[3] = {16, 32, 64};
+        const double rel[3] = {1.0, 1.45, 2.7};
+        double best = -1.0;
+        for (int i = 0; i < 3; i++) {
+            if (i > 0 && M <= widths[i - 1]) break;
+            const long ctas = row_tiles * ((M + widths[i] - 1) / widths[i]);
+            const double cost = (double)((ctas + sm_count() - 1) / sm_count()) * rel[i];
+            if (best < 0.0 || cost <= best) { best = cost; T = widths[i]; }
+        }
+    }
     const long token_tiles = (M + T - 1) / T;
     if (token_tiles > 65535) return latch(BPDQ_ERR_RANGE);
     uint8_t* acts = tiles_scratch((size_t)token_tiles * nb * 36 * T);
