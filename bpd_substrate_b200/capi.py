@@ -96,6 +96,7 @@ SIGNATURES = {
     "bpd_argmax_dim_cuda": (i32, [vp, vp, i32, i32, i32, vp]),
     "bpd_llama_block_cuda": (i32, [vp, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "bpd_llama_forward_cuda": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp]),
+    "bpd_llama_forward_tiles_cuda": (i32, [vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "bpdq_gemv_stream_create": (vp, [i32, vp, vp, sz]),
     "bpdq_gemv_stream_run": (i32, [vp, vp]),
     "bpdq_gemv_stream_destroy": (None, [vp]),

@@ -54,6 +54,8 @@ int gemv_q8_0_fast_multi(int n, const uint8_t* const* Ws, float* const* outs, co
 // gemm_q4k_mma.cu: tensor-core path for many tokens, out[tokens][N], C-ABI nibble order
 int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s);
 int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s);
+// gemm_q8_0_tiles.cu: tcgen05 product on re-tiled Q8_0 weights, out[m*N + n], the scalar reference's fp32 order
+int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, cudaStream_t s);
 
 #ifdef __CUDACC__
 

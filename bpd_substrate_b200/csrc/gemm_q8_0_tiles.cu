@@ -189,7 +189,7 @@ k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__
             int s = 0;
             uint32_t par = 0;      // parity of the epilogue's release one ring round back
             for (int i = kStages; i < n_chunks; i++) {
-                if (!mbar_wait_bounded(&empty[s], par, err, 31)) break;
+                if (!mbar_wait_sleepy(&empty[s], par, err, 31)) break;   // the ring has slack: poll gently
                 const uint32_t g = (uint32_t)blocks_in(i);
                 uint8_t* stage = ring + (size_t)s * S::kStageBytes;
                 mbar_expect_tx(&full[s], g * (uint32_t)(kTileUnit + S::kActUnit));
@@ -209,13 +209,24 @@ k_gemm_q8_0_tiles(const uint8_t* __restrict__ tiles, const uint8_t* __restrict__
             if (!mbar_wait_bounded(&full[s], full_par, err, 32)) break;
             if (c >= 2 && !mbar_wait_bounded(&acc_empty[a], (uint32_t)((c >> 1) - 1) & 1u, err, 33)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // Few instructions per MMA: this warp shares its scheduler with four busy epilogue warps and gets
+            // about one issue slot in five.  Descriptors differ between blocks only in their address field
+            // (low word, no carry: shared memory addresses / 16 stay below 2^14).
             const uint32_t stage = smem_addr(ring + (size_t)s * S::kStageBytes);
+            const uint64_t a0 = umma_desc(stage, 2048, 128), b0 = umma_desc(stage + kActOff, 16 * T, 128);
+            const uint32_t a_lo = (uint32_t)a0, a_hi = (uint32_t)(a0 >> 32), b_lo = (uint32_t)b0, b_hi = (uint32_t)(b0 >> 32);
+            const uint32_t d0 = tmem_base + (uint32_t)(a * G * T);
             const int g_n = blocks_in(c);
             if (elect_one()) {
-                for (int g = 0; g < g_n; g++) {
-                    const uint64_t adesc = umma_desc(stage + (uint32_t)g * kTileUnit, 2048, 128);
-                    const uint64_t bdesc = umma_desc(stage + kActOff + (uint32_t)g * S::kActUnit, 16 * T, 128);
-                    umma_i8_ss<0>(tmem_base + (uint32_t)((a * G + g) * T), adesc, bdesc, idesc);
+                if (g_n == G) {
+#pragma unroll
+                    for (int g = 0; g < G; g++)
+                        umma_i8_ss<0>(d0 + (uint32_t)(g * T), ((uint64_t)a_hi << 32) | (a_lo + (uint32_t)(g * (kTileUnit >> 4))),
+                                      ((uint64_t)b_hi << 32) | (b_lo + (uint32_t)(g * (S::kActUnit >> 4))), idesc);
+                } else {
+                    for (int g = 0; g < g_n; g++)
+                        umma_i8_ss<0>(d0 + (uint32_t)(g * T), ((uint64_t)a_hi << 32) | (a_lo + (uint32_t)(g * (kTileUnit >> 4))),
+                                      ((uint64_t)b_hi << 32) | (b_lo + (uint32_t)(g * (S::kActUnit >> 4))), idesc);
                 }
                 umma_commit(&acc_full[a]);
             }

@@ -267,14 +267,24 @@ static int launch_kv_write(void* cache, const float* src, const int32_t* pos_ids
     return check_cuda(cudaGetLastError());
 }
 
+// One product: on the re-tiled copy of the matrix (tensor cores, every token in one pass over the weights)
+// when there is one and enough tokens to pay for it, else on the rows (one pass per token).
+constexpr int kTilesMinTokens = 3;
+static int product(const uint8_t* rows, const uint8_t* tiles, const float* x, float* out, int n_tokens, int N, int K,
+                   cudaStream_t s)
+{
+    if (tiles && n_tokens >= kTilesMinTokens) return gemm_q8_0_tiles(tiles, x, out, n_tokens, N, K, s);
+    return bpd_qmatmul_q8_0_cuda(rows, x, out, n_tokens, N, K, s);
+}
+
 // Products that read the same vector: one launch where the fast Q8_0 kernel applies (one token, K a
 // multiple of 256, aligned pointers), else one call each.  Same arithmetic either way.
-static int products_shared_input(int n, const uint8_t* const* Ws, float* const* outs, const int* Ns, const float* x,
-                                 int n_tokens, int K, cudaStream_t s)
+static int products_shared_input(int n, const uint8_t* const* Ws, const uint8_t* const* Ts, float* const* outs, const int* Ns,
+                                 const float* x, int n_tokens, int K, cudaStream_t s)
 {
     if (n_tokens == 1 && gemv_q8_0_fast_multi(n, Ws, outs, Ns, x, K, s) == 0) return 0;
     for (int j = 0; j < n; j++) {
-        int rc = bpd_qmatmul_q8_0_cuda(Ws[j], x, outs[j], n_tokens, Ns[j], K, s);
+        int rc = product(Ws[j], Ts[j], x, outs[j], n_tokens, Ns[j], K, s);
         if (rc) return rc;
     }
     return 0;
@@ -292,7 +302,8 @@ static int check_cfg(const bpd_llama_config* c, int n_tokens, int kv_pos)
     return 0;
 }
 
-static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_llama_config* cfg, const int32_t* pos_ids,
+static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_llama_layer_weights* lt,
+                         const bpd_llama_config* cfg, const int32_t* pos_ids,
                          int n_tokens, int kv_pos, void* k_cache, void* v_cache, float* s1, float* s2, float* s3,
                          const float* rope_freqs, cudaStream_t s)
 {
@@ -307,29 +318,31 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
     k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->attn_norm_w, s1, E, cfg->rms_eps);
     {
         const uint8_t* Ws[3] = {lw->w_q, lw->w_k, lw->w_v};
+        const uint8_t* Ts[3] = {lt ? lt->w_q : nullptr, lt ? lt->w_k : nullptr, lt ? lt->w_v : nullptr};
         float* outs[3] = {s2, s3, vbuf};
         const int Ns[3] = {H * D, row, row};
-        if ((rc = products_shared_input(kv_together ? 3 : 2, Ws, outs, Ns, s1, n_tokens, E, s))) return rc;
+        if ((rc = products_shared_input(kv_together ? 3 : 2, Ws, Ts, outs, Ns, s1, n_tokens, E, s))) return rc;
     }
     if ((rc = launch_rope(s2, s2, pos_ids, rope_freqs, n_tokens, H, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
     if ((rc = launch_rope(s3, s3, pos_ids, rope_freqs, n_tokens, HKV, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
     if ((rc = launch_kv_write(k_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
-    if (!kv_together && (rc = bpd_qmatmul_q8_0_cuda(lw->w_v, s1, vbuf, n_tokens, row, E, s))) return rc;
+    if (!kv_together && (rc = product(lw->w_v, lt ? lt->w_v : nullptr, s1, vbuf, n_tokens, row, E, s))) return rc;
     if ((rc = launch_kv_write(v_cache, vbuf, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
     if ((rc = launch_attn(s2, k_cache, v_cache, s1, n_tokens, n_kv_full, H, HKV, D, 1.0f / sqrtf((float)D), kv_pos,
                           cfg->kv_cache_f16, s)))
         return rc;
-    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_o, s1, s2, n_tokens, E, H * D, s))) return rc;
+    if ((rc = product(lw->w_o, lt ? lt->w_o : nullptr, s1, s2, n_tokens, E, H * D, s))) return rc;
     k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s2, x, (long)n_tokens * E);
     k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->ffn_norm_w, s1, E, cfg->rms_eps);
     {
         const uint8_t* Ws[2] = {lw->w_gate, lw->w_up};
+        const uint8_t* Ts[2] = {lt ? lt->w_gate : nullptr, lt ? lt->w_up : nullptr};
         float* outs[2] = {s2, s3};
         const int Ns[2] = {F, F};
-        if ((rc = products_shared_input(2, Ws, outs, Ns, s1, n_tokens, E, s))) return rc;
+        if ((rc = products_shared_input(2, Ws, Ts, outs, Ns, s1, n_tokens, E, s))) return rc;
     }
     k_swiglu_f32<<<grid_1d((long)n_tokens * F), 256, 0, s>>>(s2, s3, s2, (long)n_tokens * F);
-    if ((rc = bpd_qmatmul_q8_0_cuda(lw->w_down, s2, s1, n_tokens, E, F, s))) return rc;
+    if ((rc = product(lw->w_down, lt ? lt->w_down : nullptr, s2, s1, n_tokens, E, F, s))) return rc;
     k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s1, x, (long)n_tokens * E);
     return check_cuda(cudaGetLastError());
 }
@@ -413,14 +426,15 @@ int bpd_llama_block_cuda(float* x, const bpd_llama_layer_weights* lw, const bpd_
     int rc = check_cfg(cfg, n_tokens, kv_pos);
     if (rc) return latch(rc);
     if (!x || !lw || !pos_ids || !k_cache || !v_cache || !scratch1 || !scratch2 || !scratch3) return latch(BPDQ_ERR_ARG);
-    rc = block_forward(x, lw, cfg, pos_ids, n_tokens, kv_pos, k_cache, v_cache, scratch1, scratch2, scratch3, rope_freqs,
+    rc = block_forward(x, lw, nullptr, cfg, pos_ids, n_tokens, kv_pos, k_cache, v_cache, scratch1, scratch2, scratch3, rope_freqs,
                        (cudaStream_t)stream);
     return rc ? latch(rc) : 0;
 }
 
-int bpd_llama_forward_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
-                           const bpd_llama_config* cfg, const int32_t* pos_ids, int kv_pos, void* k_cache, void* v_cache,
-                           float* logits_out, long long* token_out, void* stream)
+int bpd_llama_forward_tiles_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
+                                 const bpd_llama_weights* tiles, const bpd_llama_config* cfg, const int32_t* pos_ids,
+                                 int kv_pos, void* k_cache, void* v_cache, float* logits_out, long long* token_out,
+                                 void* stream)
 {
     int rc = check_cfg(cfg, n_tokens, kv_pos);
     if (rc) return latch(rc);
@@ -438,15 +452,25 @@ int bpd_llama_forward_cuda(const int32_t* token_ids, int n_tokens, const bpd_lla
     if ((rc = bpd_embed_lookup_q8_0_cuda(weights->token_embd, token_ids, x, n_tokens, E, s))) return rc;
     const size_t kv_layer = (size_t)cfg->max_seq_len * HKV * D * (cfg->kv_cache_f16 ? 2 : 4);
     for (int layer = 0; layer < cfg->n_layers; layer++) {
-        rc = block_forward(x, &weights->layers[layer], cfg, pos_ids, n_tokens, kv_pos, (uint8_t*)k_cache + layer * kv_layer,
+        rc = block_forward(x, &weights->layers[layer], tiles && tiles->layers ? &tiles->layers[layer] : nullptr, cfg, pos_ids,
+                           n_tokens, kv_pos, (uint8_t*)k_cache + layer * kv_layer,
                            (uint8_t*)v_cache + layer * kv_layer, s1, s2, s3, weights->rope_freqs, s);
         if (rc) return latch(rc);
     }
     k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, weights->output_norm_w, s1, E, cfg->rms_eps);
-    if ((rc = bpd_qmatmul_q8_0_cuda(weights->output_w, s1, logits_out, n_tokens, cfg->vocab_size, E, s))) return rc;
+    if ((rc = product(weights->output_w, tiles ? tiles->output_w : nullptr, s1, logits_out, n_tokens, cfg->vocab_size, E, s)))
+        return rc;
     if (token_out) k_argmax_rows<<<n_tokens, 256, 0, s>>>(logits_out, token_out, cfg->vocab_size);
     rc = check_cuda(cudaGetLastError());
     return rc ? latch(rc) : 0;
+}
+
+int bpd_llama_forward_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
+                           const bpd_llama_config* cfg, const int32_t* pos_ids, int kv_pos, void* k_cache, void* v_cache,
+                           float* logits_out, long long* token_out, void* stream)
+{
+    return bpd_llama_forward_tiles_cuda(token_ids, n_tokens, weights, nullptr, cfg, pos_ids, kv_pos, k_cache, v_cache, logits_out,
+                                        token_out, stream);
 }
 
 }  // extern "C"

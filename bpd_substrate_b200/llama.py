@@ -97,6 +97,26 @@ class DeviceLlama:
         self._allocs.append(p)
         return p
 
+    def retile(self):
+        """Makes the re-tiled copy of every Q8_0 matrix (device-side permutation); prefills then run each
+        product once over the weights on the tensor cores.  Costs a second copy of the matrices."""
+        lib, c = self.lib, self.cfg
+        E, F, kv = c.embed_dim, c.ffn_dim, c.n_kv_heads * c.head_dim
+        shapes = dict(w_q=(E, E), w_k=(kv, E), w_v=(kv, E), w_o=(E, E), w_gate=(F, E), w_up=(F, E), w_down=(E, F))
+
+        def tile(ptr, rows, cols):
+            t = lib.bpdq_alloc(lib.bpd_q8_0_tiles_bytes(rows, cols))
+            capi.check(lib.bpd_repack_q8_0_tiles_cuda(ptr, t, rows, cols, self.stream), "bpd_repack_q8_0_tiles_cuda")
+            self._allocs.append(t)
+            return t
+
+        self.tile_layers = (capi.LlamaLayerWeights * max(1, len(self.model.layers)))()
+        for i in range(len(self.model.layers)):
+            for f, (rows, cols) in shapes.items():
+                setattr(self.tile_layers[i], f, tile(getattr(self.layers[i], f), rows, cols))
+        self.tiles = capi.LlamaWeights(None, self.tile_layers, None, tile(self.weights.output_w, c.vocab_size, E), None)
+        capi.check(lib.bpdq_stream_sync(self.stream))
+
     def reset_cache(self):
         capi.check(self.lib.bpdq_memset_async(self.d_k, 0, self.kv_bytes, self.stream))
         capi.check(self.lib.bpdq_memset_async(self.d_v, 0, self.kv_bytes, self.stream))
@@ -112,8 +132,10 @@ class DeviceLlama:
         try:
             lib.bpdq_h2d(d_tok, token_ids.ctypes.data, 4 * n)
             lib.bpdq_h2d(d_pos, pos_ids.ctypes.data, 4 * n)
-            capi.check(lib.bpd_llama_forward_cuda(d_tok, n, C.byref(self.weights), C.byref(self.cfg), d_pos, kv_pos, self.d_k,
-                                                  self.d_v, d_logits, d_out, self.stream), "bpd_llama_forward_cuda")
+            tiles = C.byref(self.tiles) if getattr(self, "tiles", None) is not None else None
+            capi.check(lib.bpd_llama_forward_tiles_cuda(d_tok, n, C.byref(self.weights), tiles, C.byref(self.cfg), d_pos, kv_pos,
+                                                        self.d_k, self.d_v, d_logits, d_out, self.stream),
+                       "bpd_llama_forward_tiles_cuda")
             capi.check(lib.bpdq_stream_sync(self.stream))
             logits = np.empty((n, self.cfg.vocab_size), np.float32)
             tokens = np.empty(n, np.int64)

@@ -3,6 +3,8 @@
     python -m bpd_substrate_b200.measure            # prints one JSON object per configuration
     python -m bpd_substrate_b200.measure --llama-decode [LAYERS]
                                                     # Q8_0 Llama forward, 8B-shaped layers: ms per decoded token
+    python -m bpd_substrate_b200.measure --llama-prefill [LAYERS] [TOKENS]
+                                                    # the same layers, a prefill: rows against re-tiled weights
     python -m bpd_substrate_b200.measure --q8-tiles [N K]
                                                     # Q8_0 many-token product on re-tiled weights (tcgen05)
                                                     # beside the row-layout kernel, 1..512 tokens
@@ -80,6 +82,35 @@ def gemm_once(lib, kernel, tokens, N=14336, K=4096, launches=5):
         lib.bpdq_free(p)
     print(json.dumps({"gemm_once": kernel, "tokens": tokens, "N": N, "K": K, "status": status}))
     return 0 if status == 0 else 1
+
+
+def llama_prefill(lib, n_layers=4, tokens=128):
+    """Prefill of `tokens` tokens through `n_layers` 8B-shaped Q8_0 layers, on the rows (one pass over each
+    matrix per token) and on the re-tiled copies (one pass on the tensor cores)."""
+    import ctypes as C
+    from . import llama
+    cfg = llama.make_config(n_layers=n_layers, n_heads=32, n_kv_heads=8, head_dim=128, ffn_dim=14336, vocab_size=32000,
+                            max_seq_len=max(256, tokens))
+    model = llama.SyntheticLlama(cfg, seed=3)
+    dev = llama.DeviceLlama(model, lib)
+    tm = Timer(lib)
+    toks = np.arange(tokens, dtype=np.int32) % cfg.vocab_size
+    pos = np.arange(tokens, dtype=np.int32)
+    d_tok, d_pos = _dev(lib, toks), _dev(lib, pos)
+    d_logits, d_out = lib.bpdq_alloc(4 * tokens * cfg.vocab_size), lib.bpdq_alloc(8 * tokens)
+    dev.retile()
+    res = {}
+    for name, tiles in (("rows", None), ("tiles", C.byref(dev.tiles))):
+        def step(i):
+            capi.check(lib.bpd_llama_forward_tiles_cuda(d_tok, tokens, C.byref(dev.weights), tiles, C.byref(cfg), d_pos, 0, dev.d_k,
+                                                        dev.d_v, d_logits, d_out, tm.stream))
+        res[name] = tm.run(step, 5, warm=2) / 1e3
+    print(json.dumps(dict(config=f"Q8_0 Llama prefill, {n_layers} layers of 8B shape + 32000-row head, {tokens} tokens",
+                          rows_ms=round(res["rows"], 3), tiles_ms=round(res["tiles"], 3),
+                          tiles_tokens_per_s=round(tokens / res["tiles"] * 1e3), weight_bytes=model.weight_bytes(),
+                          status=lib.bpdq_last_status())), flush=True)
+    dev.close()
+    return 0 if lib.bpdq_last_status() == 0 else 1
 
 
 def q8_tiles(lib, N=14336, K=4096, token_counts=(1, 4, 16, 32, 64, 128, 512)):
@@ -193,6 +224,8 @@ def main():
     lib.bpdq_clear_status()
     if len(sys.argv) >= 2 and sys.argv[1] == "--llama-decode":
         return llama_decode(lib, *[int(v) for v in sys.argv[2:3]])
+    if len(sys.argv) >= 2 and sys.argv[1] == "--llama-prefill":
+        return llama_prefill(lib, *[int(v) for v in sys.argv[2:4]])
     if len(sys.argv) >= 2 and sys.argv[1] == "--q8-tiles":
         return q8_tiles(lib, *[int(v) for v in sys.argv[2:4]])
     if len(sys.argv) >= 3 and sys.argv[1] == "--q8-tiles-once":

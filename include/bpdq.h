@@ -333,6 +333,15 @@ int bpd_llama_block_cuda(float* x, const bpd_llama_layer_weights* lw, const bpd_
 int bpd_llama_forward_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
                            const bpd_llama_config* cfg, const int32_t* pos_ids, int kv_pos, void* k_cache, void* v_cache,
                            float* logits_out, long long* token_out, void* stream);
+/* The same forward with a second set of weights: `tiles` has the layout of `weights`, its Q8_0 matrix
+ * pointers (w_q .. w_down of every layer, output_w) refer to copies re-tiled by bpd_repack_q8_0_tiles_cuda, or
+ * are NULL; its other fields are not read.  With three or more tokens (a prefill) every product that has a
+ * re-tiled copy runs once over the weights on the tensor cores (bpd_qmatmul_q8_0_tiles_cuda) instead of once
+ * per token; single tokens use the rows as before.  tiles == NULL is bpd_llama_forward_cuda. */
+int bpd_llama_forward_tiles_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
+                                 const bpd_llama_weights* tiles, const bpd_llama_config* cfg, const int32_t* pos_ids,
+                                 int kv_pos, void* k_cache, void* v_cache, float* logits_out, long long* token_out,
+                                 void* stream);
 
 #ifdef __cplusplus
 }

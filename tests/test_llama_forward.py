@@ -96,10 +96,14 @@ def test_checker_steps_equal_compiled_reference(oracle):
 # --------------------------------------------------------------------------- GPU
 
 @pytest.mark.gpu
-def test_forward_tiny_against_reference_fixture(lib, tiny):
+@pytest.mark.parametrize("retiled", [False, True])
+def test_forward_tiny_against_reference_fixture(lib, tiny, retiled):
+    """retiled: the prefill's products run on the re-tiled copies of the matrices (tensor cores)."""
     g = np.load(GOLDEN)
     dev = llama.DeviceLlama(tiny, lib)
     try:
+        if retiled:
+            dev.retile()
         got = run_steps(dev.forward, tiny)
         for name, (logits, tokens) in got.items():
             want = g[f"{name}_logits"].view(np.float32)
@@ -198,8 +202,8 @@ def test_steps_against_checker(lib, oracle):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("f16", [1, 0])
-def test_forward_larger_model_against_checker(lib, oracle, f16):
+@pytest.mark.parametrize("f16,retiled", [(1, False), (0, False), (1, True), (0, True)])
+def test_forward_larger_model_against_checker(lib, oracle, f16, retiled):
     """Shapes that take the fast Q8_0 kernel (K multiple of 256), GQA group of 4, partial rotary
     dimension, both cache types; prefill of 9 tokens and three single-token steps.
 
@@ -216,6 +220,8 @@ def test_forward_larger_model_against_checker(lib, oracle, f16):
     k, v = model.kv_cache()
     dev = llama.DeviceLlama(model, lib)
     try:
+        if retiled:
+            dev.retile()
         rng = np.random.default_rng(9)
         kv_pos = 0
         for n in (9, 1, 1, 1):
