@@ -403,13 +403,13 @@ int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int
     if (((uintptr_t)tiles & 15) || ((uintptr_t)X & 15) || ((uintptr_t)out & 3)) return latch(BPDQ_ERR_ALIGN);
     const int nb = K / 32;
     // Token tile: 16, 32 or 64, whichever needs the least time by a model of waves of CTAs over the SMs
-    // times the measured cost of one block at that width (1 : 1.45 : 2.7); a narrower tile re-reads the
+    // times the measured cost of one block at that width (1 : 1.5 : 2.95); a narrower tile re-reads the
     // weights once more per tile, from L2, and spreads the epilogue's work over more SMs.
     int T = 16;
     {
         const long row_tiles = (N + kTileRows - 1) / kTileRows;
         const int widths[3] = {16, 32, 64};
-        const double rel[3] = {1.0, 1.45, 2.7};
+        const double rel[3] = {1.0, 1.5, 2.95};
         double best = -1.0;
         for (int i = 0; i < 3; i++) {
             if (i > 0 && M <= widths[i - 1]) break;
