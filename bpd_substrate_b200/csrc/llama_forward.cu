@@ -99,11 +99,13 @@ __global__ void __launch_bounds__(256) k_kv_write(void* __restrict__ cache, cons
     }
 }
 
-// One CTA per (query token, query head).  As in the reference, ALL n_kv cache rows take part: rows
-// past the query's position score -1e38 and contribute exp(-huge) = 0.  Scores: raw dot products
-// (multiply, then add, in index order, one thread per cache row), scaled afterwards; maximum; exp and
-// sum (added in index order by one thread, as the reference adds them); normalisation by the
-// reciprocal; then thread d adds v[ic][d] * w[ic] over the rows in order.
+// One CTA per (query token, query head).  In the reference ALL n_kv cache rows take part: rows past
+// the query's position score -1e38 and weigh exp(-huge) = 0, so they add exact zeros to the sum and to
+// the output (the cache holds finite values); they are skipped here, which leaves every bit as it is.
+// Scores: raw dot products (multiply, then add, in index order, one thread per cache row, the row read
+// 16 bytes at a time), scaled afterwards; maximum; exp and sum (added in index order by one thread, as
+// the reference adds them); normalisation by the reciprocal; then thread d adds v[ic][d] * w[ic] over
+// the rows in order.
 template <int F16>
 __global__ void __launch_bounds__(256) k_gqa_attn(const float* __restrict__ q, const void* __restrict__ kc,
                                                    const void* __restrict__ vc, float* __restrict__ dst, int n_kv,
@@ -124,12 +126,37 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const float* __restrict__ q, c
     auto load = [&](const void* base, size_t idx) -> float {
         return F16 ? __half2float(reinterpret_cast<const __half*>(base)[idx]) : reinterpret_cast<const float*>(base)[idx];
     };
+    n_kv = n_kv < q_pos + 1 ? n_kv : q_pos + 1;      // the rows that can weigh more than zero
+    constexpr int kVec = F16 ? 8 : 4;                 // elements per 16-byte load
+    const bool vec_ok = (head_dim % kVec) == 0 && ((uintptr_t)kc & 15) == 0;
     float mx = -1e38f;
     for (int ic = tid; ic < n_kv; ic += 256) {
         const size_t row = ((size_t)ic * n_kv_heads + kv_head) * head_dim;
         float s = 0.0f;
-        for (int d = 0; d < head_dim; d++) s = __fadd_rn(s, __fmul_rn(sq[d], load(kc, row + d)));
-        const float sv = (ic <= q_pos) ? __fmul_rn(s, scale) : -1e38f;
+        if (vec_ok) {
+            const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(kc) + row * (F16 ? 2 : 4));
+            for (int j = 0; j < head_dim / kVec; j++) {
+                const uint4 w = __ldg(p + j);
+                float kf[kVec];
+                if (F16) {
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&ww[i]));
+                        kf[(2 * i) % kVec] = f2.x;
+                        kf[(2 * i + 1) % kVec] = f2.y;
+                    }
+                } else {
+                    kf[0] = __uint_as_float(w.x); kf[1] = __uint_as_float(w.y);
+                    kf[2] = __uint_as_float(w.z); kf[3] = __uint_as_float(w.w);
+                }
+#pragma unroll
+                for (int i = 0; i < kVec; i++) s = __fadd_rn(s, __fmul_rn(sq[j * kVec + i], kf[i]));
+            }
+        } else {
+            for (int d = 0; d < head_dim; d++) s = __fadd_rn(s, __fmul_rn(sq[d], load(kc, row + d)));
+        }
+        const float sv = __fmul_rn(s, scale);
         scores[ic] = sv;
         mx = fmaxf(mx, sv);
     }
