@@ -20,17 +20,10 @@ namespace bpdq {
 // to fp32; here 256 threads add strided partial sums in binary64 and a tree joins them.  The
 // binary64 sums differ by ~1e-16 relative, which vanishes in the rounding to fp32 except when the
 // mean sits within that distance of a rounding boundary.
-__global__ void __launch_bounds__(256) k_rmsnorm_llama(const float* __restrict__ in, const float* __restrict__ w,
-                                                        float* __restrict__ out, int cols, float eps)
+__device__ __forceinline__ void cta_rmsnorm_row(const float* x, const float* __restrict__ w, float* y, int cols, float eps,
+                                                double t)
 {
     __shared__ double s_part[8];
-    const float* x = in + (size_t)blockIdx.x * cols;
-    float* y = out + (size_t)blockIdx.x * cols;
-    double t = 0.0;
-    for (int c = threadIdx.x; c < cols; c += 256) {
-        const double v = (double)x[c];
-        t += v * v;
-    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
     if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = t;
@@ -40,10 +33,66 @@ __global__ void __launch_bounds__(256) k_rmsnorm_llama(const float* __restrict__
     for (int i = 0; i < 8; i++) tot += s_part[i];
     const float mean = (float)(tot / (double)cols);
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-    for (int c = threadIdx.x; c < cols; c += 256) {
-        const float v = __fmul_rn(x[c], scale);
-        y[c] = w ? __fmul_rn(v, w[c]) : v;
+    // eight loads in flight before the stores (x, y and, in the fused kernel, the residual may be the same memory,
+    // so the compiler would otherwise wait for every store before the next load)
+    for (int c0 = threadIdx.x; c0 < cols; c0 += 256 * 8) {
+        float xv[8], wv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int c = c0 + 256 * j;
+            xv[j] = c < cols ? x[c] : 0.0f;
+            wv[j] = (w && c < cols) ? w[c] : 1.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int c = c0 + 256 * j;
+            if (c < cols) {
+                const float v = __fmul_rn(xv[j], scale);
+                y[c] = w ? __fmul_rn(v, wv[j]) : v;
+            }
+        }
     }
+}
+
+__global__ void __launch_bounds__(256) k_rmsnorm_llama(const float* __restrict__ in, const float* __restrict__ w,
+                                                        float* __restrict__ out, int cols, float eps)
+{
+    const float* x = in + (size_t)blockIdx.x * cols;
+    double t = 0.0;
+    for (int c = threadIdx.x; c < cols; c += 256) {
+        const double v = (double)x[c];
+        t += v * v;
+    }
+    cta_rmsnorm_row(x, w, out + (size_t)blockIdx.x * cols, cols, eps, t);
+}
+
+// The residual add and the norm that follows it in one launch: x = x + r (kept), out = rms_norm(x) * w.
+// Every thread squares and later re-reads the elements it has just written, in k_rmsnorm_llama's order.
+__global__ void __launch_bounds__(256) k_add_rmsnorm_llama(float* x_io, const float* r, const float* __restrict__ w, float* out,
+                                                            int cols, float eps)   // out may be r
+{
+    float* x = x_io + (size_t)blockIdx.x * cols;
+    const float* rr = r + (size_t)blockIdx.x * cols;
+    double t = 0.0;
+    for (int c0 = threadIdx.x; c0 < cols; c0 += 256 * 8) {
+        float xv[8], rv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int c = c0 + 256 * j;
+            xv[j] = c < cols ? x[c] : 0.0f;
+            rv[j] = c < cols ? rr[c] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int c = c0 + 256 * j;
+            if (c < cols) {
+                const float v = __fadd_rn(xv[j], rv[j]);
+                x[c] = v;
+                t += (double)v * (double)v;
+            }
+        }
+    }
+    cta_rmsnorm_row(x, w, out + (size_t)blockIdx.x * cols, cols, eps, t);
 }
 
 // The reference's libm returns the correctly rounded fp32 value of expf / cosf / sinf for all but
@@ -57,6 +106,23 @@ __device__ __forceinline__ float sin_rounded(float x) { return (float)sin((doubl
 
 // In place or out of place.  Thread = (token, head, pair).  theta is reached as the reference reaches
 // it, by repeated multiplication from (float)pos, so that the angle has the same bits.
+__device__ __forceinline__ void rope_pair(float x0, float x1, int pair, int half, int pos, const float* __restrict__ freq_factors,
+                                          float theta_scale, float& y0, float& y1)
+{
+    if (pair < half) {
+        float theta = (float)pos;
+        for (int i = 0; i < pair; i++) theta = __fmul_rn(theta, theta_scale);
+        const float ff = freq_factors ? freq_factors[pair] : 1.0f;
+        const float te = __fdiv_rn(theta, ff);
+        const float c = cos_rounded(te), s = sin_rounded(te);
+        y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+    } else {
+        y0 = x0;
+        y1 = x1;
+    }
+}
+
 __global__ void __launch_bounds__(256) k_rope_norm(const float* __restrict__ in, float* __restrict__ out,
                                                     const int32_t* __restrict__ pos_ids, const float* __restrict__ freq_factors,
                                                     int n_tokens, int n_heads, int head_dim, int n_dims, float theta_scale)
@@ -69,18 +135,51 @@ __global__ void __launch_bounds__(256) k_rope_norm(const float* __restrict__ in,
         const int t = (int)(th / n_heads);
         const float* src = in + th * head_dim;
         float* dst = out + th * head_dim;
-        const float x0 = src[2 * pair], x1 = src[2 * pair + 1];
-        if (pair < half) {
-            float theta = (float)pos_ids[t];
-            for (int i = 0; i < pair; i++) theta = __fmul_rn(theta, theta_scale);
-            const float ff = freq_factors ? freq_factors[pair] : 1.0f;
-            const float te = __fdiv_rn(theta, ff);
-            const float c = cos_rounded(te), s = sin_rounded(te);
-            dst[2 * pair] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-            dst[2 * pair + 1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+        float y0, y1;
+        rope_pair(src[2 * pair], src[2 * pair + 1], pair, half, pos_ids[t], freq_factors, theta_scale, y0, y1);
+        dst[2 * pair] = y0;
+        dst[2 * pair + 1] = y1;
+    }
+}
+
+// The three steps between the q/k/v products and attention in one launch: q rotated in place, k rotated
+// and stored to its cache row, v stored to its cache row (f16 rounding of the same fp32 values the separate
+// steps round).  Thread = (token, head of q|k|v, pair).
+template <int F16>
+__global__ void __launch_bounds__(256) k_rope_qk_store_kv(float* __restrict__ q, const float* __restrict__ k,
+                                                           const float* __restrict__ v, void* __restrict__ k_cache,
+                                                           void* __restrict__ v_cache, const int32_t* __restrict__ pos_ids,
+                                                           const float* __restrict__ freq_factors, int n_tokens, int n_heads,
+                                                           int n_kv_heads, int head_dim, int n_dims, float theta_scale)
+{
+    const int half = n_dims / 2, pairs = head_dim / 2, heads = n_heads + 2 * n_kv_heads;
+    const long total = (long)n_tokens * heads * pairs;
+    for (long u = (long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long)gridDim.x * blockDim.x) {
+        const int pair = (int)(u % pairs);
+        const long th = u / pairs;
+        const int t = (int)(th / heads), h = (int)(th - (long)t * heads);
+        const int pos = pos_ids[t];
+        if (h < n_heads) {
+            float* p = q + ((size_t)t * n_heads + h) * head_dim + 2 * pair;
+            float y0, y1;
+            rope_pair(p[0], p[1], pair, half, pos, freq_factors, theta_scale, y0, y1);
+            p[0] = y0;
+            p[1] = y1;
         } else {
-            dst[2 * pair] = x0;
-            dst[2 * pair + 1] = x1;
+            const bool is_k = h < n_heads + n_kv_heads;
+            const int hk = h - n_heads - (is_k ? 0 : n_kv_heads);
+            const float* p = (is_k ? k : v) + ((size_t)t * n_kv_heads + hk) * head_dim + 2 * pair;
+            float y0 = p[0], y1 = p[1];
+            if (is_k) rope_pair(p[0], p[1], pair, half, pos, freq_factors, theta_scale, y0, y1);
+            const size_t at = ((size_t)pos * n_kv_heads + hk) * head_dim + 2 * pair;
+            void* cache = is_k ? k_cache : v_cache;
+            if (F16) {
+                reinterpret_cast<__half*>(cache)[at] = __float2half_rn(y0);
+                reinterpret_cast<__half*>(cache)[at + 1] = __float2half_rn(y1);
+            } else {
+                reinterpret_cast<float*>(cache)[at] = y0;
+                reinterpret_cast<float*>(cache)[at + 1] = y1;
+            }
         }
     }
 }
@@ -329,10 +428,24 @@ static int check_cfg(const bpd_llama_config* c, int n_tokens, int kv_pos)
     return 0;
 }
 
+static int launch_rope_qk_store_kv(float* q, const float* k, const float* v, void* k_cache, void* v_cache, const int32_t* pos_ids,
+                                   const float* ff, int n_tokens, int H, int HKV, int D, int n_dims, float freq_base, int f16,
+                                   cudaStream_t s)
+{
+    const float theta_scale = powf(freq_base, -2.0f / (float)n_dims);
+    const int grid = grid_1d((long)n_tokens * (H + 2 * HKV) * (D / 2));
+    if (f16) k_rope_qk_store_kv<1><<<grid, 256, 0, s>>>(q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale);
+    else k_rope_qk_store_kv<0><<<grid, 256, 0, s>>>(q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale);
+    return check_cuda(cudaGetLastError());
+}
+
+// One transformer block.  x_normed: s1 already holds rms_norm(x) * attn_norm_w (the block before fused it
+// with its last residual add).  fuse_next: the last residual add also writes rms_norm(x) * next_norm_w to s1.
+// The fused launches do the same operations on the same values as the separate steps.
 static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_llama_layer_weights* lt,
                          const bpd_llama_config* cfg, const int32_t* pos_ids,
                          int n_tokens, int kv_pos, void* k_cache, void* v_cache, float* s1, float* s2, float* s3,
-                         const float* rope_freqs, cudaStream_t s)
+                         const float* rope_freqs, bool x_normed, bool fuse_next, const float* next_norm_w, cudaStream_t s)
 {
     const int E = cfg->embed_dim, H = cfg->n_heads, HKV = cfg->n_kv_heads, D = cfg->head_dim, F = cfg->ffn_dim;
     const int n_kv_full = cfg->max_seq_len;
@@ -342,7 +455,7 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
     // whenever two or more query heads share a KV head; otherwise V is computed after K is stored)
     const bool kv_together = (size_t)2 * row <= (size_t)H * D;
     float* vbuf = kv_together ? s3 + (size_t)n_tokens * row : s3;
-    k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->attn_norm_w, s1, E, cfg->rms_eps);
+    if (!x_normed) k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->attn_norm_w, s1, E, cfg->rms_eps);
     {
         const uint8_t* Ws[3] = {lw->w_q, lw->w_k, lw->w_v};
         const uint8_t* Ts[3] = {lt ? lt->w_q : nullptr, lt ? lt->w_k : nullptr, lt ? lt->w_v : nullptr};
@@ -350,17 +463,22 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
         const int Ns[3] = {H * D, row, row};
         if ((rc = products_shared_input(kv_together ? 3 : 2, Ws, Ts, outs, Ns, s1, n_tokens, E, s))) return rc;
     }
-    if ((rc = launch_rope(s2, s2, pos_ids, rope_freqs, n_tokens, H, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
-    if ((rc = launch_rope(s3, s3, pos_ids, rope_freqs, n_tokens, HKV, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
-    if ((rc = launch_kv_write(k_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
-    if (!kv_together && (rc = product(lw->w_v, lt ? lt->w_v : nullptr, s1, vbuf, n_tokens, row, E, s))) return rc;
-    if ((rc = launch_kv_write(v_cache, vbuf, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
+    if (kv_together) {
+        if ((rc = launch_rope_qk_store_kv(s2, s3, vbuf, k_cache, v_cache, pos_ids, rope_freqs, n_tokens, H, HKV, D, cfg->rope_dim,
+                                          cfg->rope_base, cfg->kv_cache_f16, s)))
+            return rc;
+    } else {
+        if ((rc = launch_rope(s2, s2, pos_ids, rope_freqs, n_tokens, H, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
+        if ((rc = launch_rope(s3, s3, pos_ids, rope_freqs, n_tokens, HKV, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
+        if ((rc = launch_kv_write(k_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
+        if ((rc = product(lw->w_v, lt ? lt->w_v : nullptr, s1, vbuf, n_tokens, row, E, s))) return rc;
+        if ((rc = launch_kv_write(v_cache, vbuf, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
+    }
     if ((rc = launch_attn(s2, k_cache, v_cache, s1, n_tokens, n_kv_full, H, HKV, D, 1.0f / sqrtf((float)D), kv_pos,
                           cfg->kv_cache_f16, s)))
         return rc;
     if ((rc = product(lw->w_o, lt ? lt->w_o : nullptr, s1, s2, n_tokens, E, H * D, s))) return rc;
-    k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s2, x, (long)n_tokens * E);
-    k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->ffn_norm_w, s1, E, cfg->rms_eps);
+    k_add_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, s2, lw->ffn_norm_w, s1, E, cfg->rms_eps);
     {
         const uint8_t* Ws[2] = {lw->w_gate, lw->w_up};
         const uint8_t* Ts[2] = {lt ? lt->w_gate : nullptr, lt ? lt->w_up : nullptr};
@@ -370,7 +488,8 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
     }
     k_swiglu_f32<<<grid_1d((long)n_tokens * F), 256, 0, s>>>(s2, s3, s2, (long)n_tokens * F);
     if ((rc = product(lw->w_down, lt ? lt->w_down : nullptr, s2, s1, n_tokens, E, F, s))) return rc;
-    k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s1, x, (long)n_tokens * E);
+    if (fuse_next) k_add_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, s1, next_norm_w, s1, E, cfg->rms_eps);
+    else k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s1, x, (long)n_tokens * E);
     return check_cuda(cudaGetLastError());
 }
 
@@ -454,7 +573,7 @@ int bpd_llama_block_cuda(float* x, const bpd_llama_layer_weights* lw, const bpd_
     if (rc) return latch(rc);
     if (!x || !lw || !pos_ids || !k_cache || !v_cache || !scratch1 || !scratch2 || !scratch3) return latch(BPDQ_ERR_ARG);
     rc = block_forward(x, lw, nullptr, cfg, pos_ids, n_tokens, kv_pos, k_cache, v_cache, scratch1, scratch2, scratch3, rope_freqs,
-                       (cudaStream_t)stream);
+                       false, false, nullptr, (cudaStream_t)stream);
     return rc ? latch(rc) : 0;
 }
 
@@ -478,13 +597,16 @@ int bpd_llama_forward_tiles_cuda(const int32_t* token_ids, int n_tokens, const b
     float *x = base, *s1 = x + nx, *s2 = s1 + n1, *s3 = s2 + n2;
     if ((rc = bpd_embed_lookup_q8_0_cuda(weights->token_embd, token_ids, x, n_tokens, E, s))) return rc;
     const size_t kv_layer = (size_t)cfg->max_seq_len * HKV * D * (cfg->kv_cache_f16 ? 2 : 4);
+    // every block's last residual add also computes the norm that follows it: the next block's, or the output norm
     for (int layer = 0; layer < cfg->n_layers; layer++) {
+        const bool last = layer + 1 == cfg->n_layers;
         rc = block_forward(x, &weights->layers[layer], tiles && tiles->layers ? &tiles->layers[layer] : nullptr, cfg, pos_ids,
-                           n_tokens, kv_pos, (uint8_t*)k_cache + layer * kv_layer,
-                           (uint8_t*)v_cache + layer * kv_layer, s1, s2, s3, weights->rope_freqs, s);
+                           n_tokens, kv_pos, (uint8_t*)k_cache + layer * kv_layer, (uint8_t*)v_cache + layer * kv_layer, s1, s2, s3,
+                           weights->rope_freqs, layer > 0, true,
+                           last ? weights->output_norm_w : weights->layers[layer + 1].attn_norm_w, s);
         if (rc) return latch(rc);
     }
-    k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, weights->output_norm_w, s1, E, cfg->rms_eps);
+    if (cfg->n_layers == 0) k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, weights->output_norm_w, s1, E, cfg->rms_eps);
     if ((rc = product(weights->output_w, tiles ? tiles->output_w : nullptr, s1, logits_out, n_tokens, cfg->vocab_size, E, s)))
         return rc;
     if (token_out) k_argmax_rows<<<n_tokens, 256, 0, s>>>(logits_out, token_out, cfg->vocab_size);

@@ -214,7 +214,7 @@ def llama_decode(lib, n_layers=4, steps=32):
     print(json.dumps({"config": f"Q8_0 Llama forward, {n_layers} layers of 8B shape, decode", "ms_per_token": round(ms, 4),
                       "ms_per_token_graph": round(ms_graph, 4) if ms_graph else None,
                       "bytes_per_token": per_token, "gbs": round(per_token / (ms_graph or ms) / 1e6, 1),
-                      "launches_per_token": 14 * n_layers + 4, "status": status}))
+                      "launches_per_token": 9 * n_layers + 4, "status": status}))
     dev.close()
     return 0 if status == 0 else 1
 

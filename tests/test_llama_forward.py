@@ -8,7 +8,7 @@ integer and format steps (f16 cache write, argmax, quantization inside the produ
 import numpy as np
 import pytest
 
-from bpd_substrate_b200 import llama
+from bpd_substrate_b200 import capi, llama
 from oracle import binding
 from tests.golden.make_golden import LLAMA_TINY, LLAMA_TINY_SEED, LLAMA_TINY_STEPS
 from tests.util import normwise
@@ -256,5 +256,90 @@ def test_forward_rejects_bad_configurations(lib, tiny):
         lib.bpdq_free(d)
         lib.bpdq_clear_status()
         assert capi.check(0) == 0
+    finally:
+        dev.close()
+
+
+def _block_by_twins(lib, dev, layer, d_x, d_pos, n, kv_pos, d_k, d_v, scr):
+    """One block as the sequence of separate entry points (the reference's call order, bench/bpd_cpu.c:5608-5738)."""
+    c, lw = dev.cfg, dev.layers[layer]
+    E, H, HKV, D, F = c.embed_dim, c.n_heads, c.n_kv_heads, c.head_dim, c.ffn_dim
+    row = HKV * D
+    s1, s2, s3, sv = scr
+    ok = lambda rc: capi.check(rc)
+    ok(lib.bpd_rmsnorm_llama_cuda(d_x, lw.attn_norm_w, s1, n, E, c.rms_eps, None))
+    ok(lib.bpd_qmatmul_q8_0_cuda(lw.w_q, s1, s2, n, H * D, E, None))
+    ok(lib.bpd_qmatmul_q8_0_cuda(lw.w_k, s1, s3, n, row, E, None))
+    ok(lib.bpd_qmatmul_q8_0_cuda(lw.w_v, s1, sv, n, row, E, None))
+    ff = dev.weights.rope_freqs
+    ok(lib.bpd_rope_norm_freqs_cuda(s2, s2, d_pos, ff, n, H, D, c.rope_dim, c.rope_base, None))
+    ok(lib.bpd_rope_norm_freqs_cuda(s3, s3, d_pos, ff, n, HKV, D, c.rope_dim, c.rope_base, None))
+    write = lib.bpd_kv_cache_write_f16_cuda if c.kv_cache_f16 else lib.bpd_kv_cache_write_cuda
+    ok(write(d_k, s3, d_pos, n, HKV, D, c.max_seq_len, None))
+    ok(write(d_v, sv, d_pos, n, HKV, D, c.max_seq_len, None))
+    ok(lib.bpd_gqa_attn_cuda(s2, d_k, d_v, s1, n, c.max_seq_len, H, HKV, D, 1.0 / np.sqrt(np.float32(D)), kv_pos,
+                             c.kv_cache_f16, None))
+    ok(lib.bpd_qmatmul_q8_0_cuda(lw.w_o, s1, s2, n, E, H * D, None))
+    lib.gpu_add(d_x, s2, d_x, n * E)
+    ok(lib.bpd_rmsnorm_llama_cuda(d_x, lw.ffn_norm_w, s1, n, E, c.rms_eps, None))
+    ok(lib.bpd_qmatmul_q8_0_cuda(lw.w_gate, s1, s2, n, F, E, None))
+    ok(lib.bpd_qmatmul_q8_0_cuda(lw.w_up, s1, s3, n, F, E, None))
+    ok(lib.bpd_swiglu_fuse_cuda(s2, s3, s2, n * F, None))
+    ok(lib.bpd_qmatmul_q8_0_cuda(lw.w_down, s2, s1, n, E, F, None))
+    lib.gpu_add(d_x, s1, d_x, n * E)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1, 6])
+def test_block_and_forward_equal_their_separate_steps_bit_for_bit(lib, n):
+    """The block fuses steps into shared launches (rotary embedding of q and k with the cache stores, residual
+    adds with the norms that follow them, products that share an input); the forward also fuses across blocks.
+    Both must give the bits of the separate entry points called in the reference's order."""
+    import ctypes as C
+    from tests.util import Dev
+    cfg = llama.make_config(n_layers=2, n_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=1024, vocab_size=300, max_seq_len=24,
+                            rope_dim=48, kv_cache_f16=1)
+    model = llama.SyntheticLlama(cfg, seed=77)
+    dev = llama.DeviceLlama(model, lib)
+    try:
+        E, F, row = cfg.embed_dim, cfg.ffn_dim, cfg.n_kv_heads * cfg.head_dim
+        kv_pos = 5
+        rng = np.random.default_rng(n)
+        toks = rng.integers(0, cfg.vocab_size, n).astype(np.int32)
+        pos = np.arange(kv_pos, kv_pos + n, dtype=np.int32)
+        kc, vc = model.kv_cache()
+        kc[:, :kv_pos] = rng.standard_normal((cfg.n_layers, kv_pos, row)).astype(np.float16).view(np.uint16)
+        vc[:, :kv_pos] = rng.standard_normal((cfg.n_layers, kv_pos, row)).astype(np.float16).view(np.uint16)
+        d_tok, d_pos = Dev(lib, toks), Dev(lib, pos)
+        scr = [Dev(lib, nbytes=4 * n * max(E, F)) for _ in range(4)]
+        ptrs = [d.ptr for d in scr]
+        layer_bytes = kc[0].nbytes
+
+        def run(kind):
+            d_k, d_v, d_x = Dev(lib, kc), Dev(lib, vc), Dev(lib, nbytes=4 * n * E)
+            d_logits = Dev(lib, nbytes=4 * n * cfg.vocab_size)
+            if kind == "forward":
+                capi.check(lib.bpd_llama_forward_cuda(d_tok.ptr, n, C.byref(dev.weights), C.byref(cfg), d_pos.ptr, kv_pos, d_k.ptr,
+                                                      d_v.ptr, d_logits.ptr, None, None))
+            else:
+                capi.check(lib.bpd_embed_lookup_q8_0_cuda(dev.weights.token_embd, d_tok.ptr, d_x.ptr, n, E, None))
+                for layer in range(cfg.n_layers):
+                    lk, lv = d_k.ptr + layer * layer_bytes, d_v.ptr + layer * layer_bytes
+                    if kind == "blocks":
+                        capi.check(lib.bpd_llama_block_cuda(d_x.ptr, C.byref(dev.layers[layer]), C.byref(cfg), d_pos.ptr, n, kv_pos,
+                                                            lk, lv, ptrs[0], ptrs[1], ptrs[2], dev.weights.rope_freqs, None))
+                    else:
+                        _block_by_twins(lib, dev, layer, d_x.ptr, d_pos.ptr, n, kv_pos, lk, lv, ptrs)
+                capi.check(lib.bpd_rmsnorm_llama_cuda(d_x.ptr, dev.weights.output_norm_w, ptrs[0], n, E, cfg.rms_eps, None))
+                capi.check(lib.bpd_qmatmul_q8_0_cuda(dev.weights.output_w, ptrs[0], d_logits.ptr, n, cfg.vocab_size, E, None))
+            lib.bpdq_sync()
+            assert lib.bpdq_last_status() == 0
+            return d_logits.read(np.uint32), d_k.read(np.uint16), d_v.read(np.uint16)
+
+        want = run("twins")
+        for kind in ("blocks", "forward"):
+            got = run(kind)
+            for a, b, what in zip(got, want, ("logits", "k cache", "v cache")):
+                assert np.array_equal(a, b), (kind, what, int(np.count_nonzero(a != b)))
     finally:
         dev.close()
