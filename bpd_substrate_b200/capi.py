@@ -96,6 +96,12 @@ SIGNATURES = {
     "bpd_argmax_dim_cuda": (i32, [vp, vp, i32, i32, i32, vp]),
     "bpd_llama_block_cuda": (i32, [vp, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp]),
     "bpd_llama_forward_cuda": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp]),
+    "bpdq_ipc_export": (i32, [vp, vp]),
+    "bpdq_ipc_import": (vp, [vp]),
+    "bpdq_ipc_close": (i32, [vp]),
+    "bpdq_set_peer_outputs": (i32, [vp, sz, i32, vp]),
+    "bpdq_peer_signal": (i32, [vp, i32, C.c_uint, vp]),
+    "bpdq_peer_wait": (i32, [vp, i32, C.c_uint, vp]),
     "bpd_llama_forward_tiles_cuda": (i32, [vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "bpdq_gemv_stream_create": (vp, [i32, vp, vp, sz]),
     "bpdq_gemv_stream_run": (i32, [vp, vp]),

@@ -51,6 +51,18 @@ Tuning& tuning();
 int gemv_q8_0_fast(const uint8_t* W, const float* x, float* out, int N, int K, cudaStream_t s);
 int gemv_q8_0_fast_multi(int n, const uint8_t* const* Ws, float* const* outs, const int* Ns, const float* x, int K,
                          cudaStream_t s);
+// peer_exchange.cu: where a product's results are stored besides its own output (gathered buffers of all
+// ranks, byte shifts from the output address), and the flag slots of the per-step signal
+constexpr int kMaxPeerTargets = 8;
+struct PeerTargets {
+    int n;
+    long long shift[kMaxPeerTargets];
+};
+struct PeerFlagSlots {
+    int n;
+    unsigned* slot[kMaxPeerTargets];
+};
+bool peer_targets_for(const void* lo, const void* hi, PeerTargets& t);
 // gemm_q4k_mma.cu: tensor-core path for many tokens, out[tokens][N], C-ABI nibble order
 int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s);
 int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s);

@@ -263,9 +263,9 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
         const int row0 = (v - pb.tile_begin) * pb.rt;
         const uint8_t* tile_smem = ring + (size_t)s * p.slot_bytes;
         if (FMT == 0) {
-            if (pb.rt == 4) batch_tile<4, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-            else if (pb.rt == 2) batch_tile<2, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-            else batch_tile<1, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane);
+            if (pb.rt == 4) batch_tile<4, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, &p.peers);
+            else if (pb.rt == 2) batch_tile<2, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, &p.peers);
+            else batch_tile<1, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, &p.peers);
         } else {
             if (pb.rt == 4) batch_tile_q80<4>(tile_smem, xq + pb.xq_off, pb, row0, lane);
             else if (pb.rt == 2) batch_tile_q80<2>(tile_smem, xq + pb.xq_off, pb, row0, lane);
@@ -355,6 +355,25 @@ int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt)
     long want = (p.n_tiles + p.nw - 1) / p.nw;
     if (want < 1) want = 1;
     p.grid = (int)(want < sm_count() ? want : sm_count());
+    // outputs inside the range registered with bpdq_set_peer_outputs: results are stored to every target too
+    p.peers.n = 0;
+    if (fmt == 0) {
+        const char *lo = nullptr, *hi = nullptr;
+        bool plain = true;
+        for (int j = 0; j < n; j++) {
+            const char* a = (const char*)p.prob[j].out;
+            const char* b = a + (size_t)p.prob[j].M * sizeof(float);
+            if (!lo || a < lo) lo = a;
+            if (!hi || b > hi) hi = b;
+            if (p.prob[j].accumulate) plain = false;
+        }
+        PeerTargets t;
+        bool all_inside = plain;
+        for (int j = 0; j < n && all_inside; j++)
+            all_inside = peer_targets_for(p.prob[j].out, p.prob[j].out + p.prob[j].M, t);
+        if (all_inside && n > 0) p.peers = t;
+        (void)lo; (void)hi;
+    }
     return 0;
 }
 
@@ -364,6 +383,11 @@ static int launch_batch(const BatchPlan& p, cudaStream_t s)
     if (ACC == 0) {
         for (int j = 0; j < p.n_problems; j++)
             if (p.prob[j].accumulate) return launch_batch<FMT, LAYOUT, 1>(p, s);
+        // results also go to the ranks' gathered buffers: its own instantiation, so that the single-GPU
+        // kernel stays as it is (Q4_K in the C-ABI nibble order only)
+        if constexpr (FMT == 0 && LAYOUT == BPDQ_LAYOUT_BPD) {
+            if (p.peers.n > 0) return launch_batch<FMT, LAYOUT, 2>(p, s);
+        }
     }
     auto kern = k_gemv_batch_q4k_q8k<FMT, LAYOUT, kMidCtaThreads, ACC>;
     static bool attr_set[64] = {false};

@@ -189,6 +189,9 @@ struct BatchPlan {
     float pro_eps;
     BatchProblem prob[kMaxBatch];
     BatchVector vec[kMaxBatch];
+    // n > 0: every result is also stored at its output address + shift[t] (the gathered buffers of the ranks
+    // of a row-sharded model, peer memory included); used by the EPI = 2 instantiation
+    PeerTargets peers;
 };
 
 // Quantizes one 256-block held by a warp (lane l: elements 4l..4l+3 in v0, 128+4l.. in v1) and
@@ -297,7 +300,7 @@ __device__ __forceinline__ void batch_tile_q80(const uint8_t* tile_smem, const u
 
 template <int R, int LAYOUT, int ACC>
 __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8_t* xq, const BatchProblem& pb, int row0,
-                                           int lane)
+                                           int lane, const PeerTargets* peers = nullptr)
 {
     const int rows = min(R, pb.M - row0);
     const int n_hb = 2 * pb.nb;
@@ -335,8 +338,16 @@ __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8
     const int my_row = lane / kLanesPerRow;
     // ACC: launches with a residual epilogue are a separate instantiation (the conditional costs the
     // plain product 2 % of its bandwidth); the residual stream was written by an earlier launch: read it past L1
-    if ((lane % kLanesPerRow) == 0 && my_row < rows)
-        pb.out[row0 + my_row] = (ACC && pb.accumulate) ? __ldcg(pb.out + row0 + my_row) + total : total;
+    if ((lane % kLanesPerRow) == 0 && my_row < rows) {
+        float* o = pb.out + row0 + my_row;
+        *o = (ACC == 1 && pb.accumulate) ? __ldcg(o) + total : total;
+        if (ACC == 2) {
+            // the exchange step of row sharding, folded into the product: the same value to every rank's
+            // gathered buffer (R consecutive floats per tile and target; peer memory is written, never read)
+            for (int t = 0; t < peers->n; t++)
+                *reinterpret_cast<float*>(reinterpret_cast<char*>(o) + peers->shift[t]) = total;
+        }
+    }
 }
 
 // ---- Elementwise steps done by the consumer warps of a product kernel itself (every CTA repeats

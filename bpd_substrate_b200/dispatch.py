@@ -177,10 +177,13 @@ class LayerSet:
                     rc = lib.bpd_qmatmul_q4k_q8k_multi_cuda(n, wp, op, mp, x, K, s)
                 capi.check(rc, "GEMV launch")
 
-    def capture(self, schedule="grouped", layers=None):
+    def capture(self, schedule="grouped", layers=None, tag=None):
         """Records a step (or a range of its layers) into a CUDA graph (launch gaps disappear, PDL
-        edges are kept)."""
+        edges are kept).  tag: tells apart recordings of the same step made under different library
+        state (the peer-store targets registered with bpdq_set_peer_outputs are read at recording time)."""
         key = schedule if layers is None else (schedule, tuple(layers))
+        if tag is not None:
+            key = (key, "tag", tag)
         if key not in self.graph:
             lib = self.lib
             self.enqueue_step(schedule, layers=layers)     # warm-up outside capture (attributes, caches)
@@ -193,10 +196,10 @@ class LayerSet:
             self.graph[key] = g
         return self.graph[key]
 
-    def step(self, schedule="grouped", layers=None):
+    def step(self, schedule="grouped", layers=None, tag=None):
         """One step (or a range of its layers) with inputs already on the device (asynchronous on
         self.stream)."""
-        capi.check(self.lib.bpdq_graph_launch(self.capture(schedule, layers), self.stream), "graph launch")
+        capi.check(self.lib.bpdq_graph_launch(self.capture(schedule, layers, tag), self.stream), "graph launch")
 
     def layer_output_range(self, first, last):
         """(byte offset, bytes) of the outputs of layers [first, last) in the output arena."""

@@ -343,6 +343,29 @@ int bpd_llama_forward_tiles_cuda(const int32_t* token_ids, int n_tokens, const b
                                  int kv_pos, void* k_cache, void* v_cache, float* logits_out, long long* token_out,
                                  void* stream);
 
+/* ---- row-sharded products on several GPUs without a collective.
+ * The reference's decode loop runs on one GPU; with the rows of every matrix sharded over ranks (one
+ * process per GPU) each rank needs the other ranks' output slices.  Instead of an all-gather after the
+ * products, the batched product kernel stores each result, besides its own output, into every rank's
+ * gathered buffer (peer memory mapped through CUDA IPC), and a flag per rank and step replaces the
+ * collective's rendezvous.
+ *   bpdq_ipc_export / bpdq_ipc_import / bpdq_ipc_close: cudaIpcGetMemHandle / cudaIpcOpenMemHandle (with lazy
+ *     peer access) / cudaIpcCloseMemHandle on a bpdq_alloc allocation; the handle is 64 bytes.
+ *   bpdq_set_peer_outputs: for this device, every batched Q4_K product (bpd_qmatmul_q4k_q8k_batch*_cuda,
+ *     C-ABI nibble order, no accumulate) whose outputs all lie in [local_base, local_base + bytes) also
+ *     stores result i to targets[t] + (address of result i - local_base) for t < n_targets (<= 8; 16-byte
+ *     aligned; a rank's own gathered buffer is one of the targets).  n_targets = 0 clears.  Read when a launch
+ *     is planned, so set it before the launches are made or captured into a graph.
+ *   bpdq_peer_signal: after all earlier work of the stream, writes `value` to each of the n slots (this rank's
+ *     flag in each rank's flag array).  bpdq_peer_wait: returns when the n flags at local_flags have all
+ *     reached `value` (flags only grow); gives up after about a second and latches status -4. */
+int bpdq_ipc_export(const void* dev_ptr, void* handle64);
+void* bpdq_ipc_import(const void* handle64);
+int bpdq_ipc_close(void* imported);
+int bpdq_set_peer_outputs(const void* local_base, size_t bytes, int n_targets, void* const* targets);
+int bpdq_peer_signal(unsigned* const* slots, int n, unsigned value, void* stream);
+int bpdq_peer_wait(const unsigned* local_flags, int n, unsigned value, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
