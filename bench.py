@@ -257,6 +257,25 @@ def run_gpu(args):
         for c in chunks:
             ls.capture(schedule, c if len(chunks) > 1 else None)
 
+    # The exchange without a collective: the product kernels store their results into every rank's gathered
+    # buffer themselves (peer memory), and a flag per rank and step replaces the all-gather's rendezvous.
+    peer = None
+    if world > 1 and args.exchange == "peer" and schedule == "batched" and args.tokens == 1:
+        from bpd_substrate_b200.peer import PeerExchange
+        try:
+            peer = PeerExchange(lib, dist, rank, world, ls.o_bytes)
+            for parity in (0, 1):
+                peer.register(ls.d_out, parity)
+                ls.capture(schedule, tag=parity)
+            peer.unregister()
+        except Exception as exc:            # set-up fails on all ranks or on none (PeerExchange agrees on it)
+            sys.stderr.write(f"rank {rank}: {exc}; using the NCCL all-gather\n")
+            lib.bpdq_clear_status()
+            peer = None
+        if peer is not None:
+            chunks = [(0, args.layers)]
+    steps_done = [0]
+
     ev0, ev1 = lib.bpdq_event_create(), lib.bpdq_event_create()
 
     def barrier():
@@ -273,6 +292,12 @@ def run_gpu(args):
         """One step's GEMVs and the all-gather of their outputs."""
         if world == 1:
             ls.step(schedule)
+            return
+        if peer is not None:
+            ls.step(schedule, tag=steps_done[0] & 1)
+            peer.signal(ls.stream)
+            peer.wait(ls.stream)      # this rank's gathered buffer of the step's parity is complete
+            steps_done[0] += 1
             return
         g_off = 0
         for c in chunks:
@@ -360,7 +385,10 @@ def run_gpu(args):
                        "independent products, inputs resident before the step",
                        "l2": "inputs larger than L2: 3.9 GB of weights stream through once per step",
                        "parallelism": f"row-shard x{world}" if world > 1 else "single GPU",
-                       "exchange": (f"NCCL all-gather of output slices in {len(chunks)} chunks of layers per step, each under "
+                       "exchange": ("none: the product kernels store every result into all ranks' gathered buffers over NVLink "
+                                    "(peer memory, double-buffered by step parity); one flag per rank and step, bounded wait"
+                                    if peer is not None else
+                                    f"NCCL all-gather of output slices in {len(chunks)} chunks of layers per step, each under "
                                     "the next chunk's GEMVs" if len(chunks) > 1 else
                                     "NCCL all-gather of output slices once per step") if world > 1 else "none"},
             "pct_of_peak": 100.0 * value / (peak * world),
@@ -384,6 +412,8 @@ def run_gpu(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
+        if peer is not None:
+            peer.close()
         dist.destroy_process_group()
     ls.close()
     if status != 0:
@@ -409,6 +439,9 @@ def main():
     ap.add_argument("--copy-chunks", type=int, default=4,
                     help="end-to-end leg: ranges of layers whose host copies run on their own streams under the other "
                          "ranges' GEMVs (1: copy in, step, copy out in sequence)")
+    ap.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
+                    help="N > 1 GPUs: peer = the product kernels store their results into every rank's gathered buffer "
+                         "(no collective; schedule batched); nccl = one all-gather per step")
     ap.add_argument("--gather-chunks", type=int, default=1,
                     help="N > 1 GPUs: 1 = one all-gather after the step's GEMVs (default); more = the gather is cut into "
                          "chunks of layers, each on a second stream under the next chunk's GEMVs (measured slower at 2 GPUs: "

@@ -30,31 +30,46 @@ class PeerExchange:
         self.lib, self.rank, self.world, self.slot_bytes = lib, rank, world, slot_bytes
         self.gathered_bytes = world * slot_bytes
         total = 2 * self.gathered_bytes + self.FLAG_BYTES
-        self.base = lib.bpdq_alloc(total)
-        if not self.base:
-            raise MemoryError("gathered buffers")
-        capi.check(lib.bpdq_memset_async(self.base, 0, total, None))
-        capi.check(lib.bpdq_stream_sync(None))
-        handle = (C.c_char * 64)()
-        capi.check(lib.bpdq_ipc_export(self.base, handle), "bpdq_ipc_export")
+        self.base, self.bases, self._imported = None, [], []
+        # No rank leaves between the collective calls below: a failure is carried to the common verdict at the end,
+        # and then every rank raises.
+        problem, payload = None, None
+        try:
+            self.base = lib.bpdq_alloc(total)
+            if not self.base:
+                raise MemoryError("gathered buffers")
+            capi.check(lib.bpdq_memset_async(self.base, 0, total, None))
+            capi.check(lib.bpdq_stream_sync(None))
+            handle = (C.c_char * 64)()
+            capi.check(lib.bpdq_ipc_export(self.base, handle), "bpdq_ipc_export")
+            payload = bytes(handle.raw)
+        except Exception as exc:
+            problem = f"rank {rank}: {exc}"
         handles = [None] * world
-        dist.all_gather_object(handles, bytes(handle.raw))
-        self.bases, self._imported = [], []
-        for r in range(world):
-            if r == rank:
-                self.bases.append(self.base)
-                continue
-            buf = (C.c_char * 64).from_buffer_copy(handles[r])
-            p = lib.bpdq_ipc_import(buf)
-            if not p:
-                raise capi.BpdqError(f"rank {rank}: cannot map rank {r}'s gathered buffer (status {lib.bpdq_last_status()})")
-            self.bases.append(p)
-            self._imported.append(p)
+        dist.all_gather_object(handles, payload)
+        if problem is None and all(h is not None for h in handles):
+            for r in range(world):
+                if r == rank:
+                    self.bases.append(self.base)
+                    continue
+                p = lib.bpdq_ipc_import((C.c_char * 64).from_buffer_copy(handles[r]))
+                if not p:
+                    problem = f"rank {rank}: cannot map rank {r}'s gathered buffer (status {lib.bpdq_last_status()})"
+                    lib.bpdq_clear_status()
+                    break
+                self.bases.append(p)
+                self._imported.append(p)
+        elif problem is None:
+            problem = f"rank {rank}: another rank could not export its buffer"
+        verdicts = [None] * world
+        dist.all_gather_object(verdicts, problem)     # also: every rank has mapped every buffer before anyone stores into one
+        if any(v is not None for v in verdicts):
+            self.close()
+            raise capi.BpdqError("peer exchange set-up failed: " + "; ".join(v for v in verdicts if v))
         flags_off = 2 * self.gathered_bytes
         self.local_flags = self.base + flags_off
         self._slots = (C.c_void_p * world)(*[b + flags_off + 4 * rank for b in self.bases])
         self.step_no = 0
-        dist.barrier()       # every rank has mapped every buffer before anyone stores into one
 
     def gathered(self, parity):
         """This rank's gathered buffer of the given step parity: world slots of slot_bytes."""
@@ -80,7 +95,7 @@ class PeerExchange:
         capi.check(self.lib.bpdq_peer_wait(self.local_flags, self.world, self.step_no, stream), "bpdq_peer_wait")
 
     def close(self):
-        self.unregister()
+        self.lib.bpdq_set_peer_outputs(None, 0, 0, None)
         for p in self._imported:
             self.lib.bpdq_ipc_close(p)
         self._imported = []
