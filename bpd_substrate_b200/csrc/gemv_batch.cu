@@ -262,10 +262,11 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
         const BatchProblem& pb = p.prob[j];
         const int row0 = (v - pb.tile_begin) * pb.rt;
         const uint8_t* tile_smem = ring + (size_t)s * p.slot_bytes;
+        const PeerTargets* peers = ACC == 2 ? &p.peers : nullptr;
         if (FMT == 0) {
-            if (pb.rt == 4) batch_tile<4, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, &p.peers);
-            else if (pb.rt == 2) batch_tile<2, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, &p.peers);
-            else batch_tile<1, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, &p.peers);
+            if (pb.rt == 4) batch_tile<4, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, peers);
+            else if (pb.rt == 2) batch_tile<2, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, peers);
+            else batch_tile<1, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, peers);
         } else {
             if (pb.rt == 4) batch_tile_q80<4>(tile_smem, xq + pb.xq_off, pb, row0, lane);
             else if (pb.rt == 2) batch_tile_q80<2>(tile_smem, xq + pb.xq_off, pb, row0, lane);

@@ -338,15 +338,18 @@ __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8
     const int my_row = lane / kLanesPerRow;
     // ACC: launches with a residual epilogue are a separate instantiation (the conditional costs the
     // plain product 2 % of its bandwidth); the residual stream was written by an earlier launch: read it past L1
-    if ((lane % kLanesPerRow) == 0 && my_row < rows) {
-        float* o = pb.out + row0 + my_row;
-        *o = (ACC == 1 && pb.accumulate) ? __ldcg(o) + total : total;
-        if (ACC == 2) {
-            // the exchange step of row sharding, folded into the product: the same value to every rank's
-            // gathered buffer (R consecutive floats per tile and target; peer memory is written, never read)
+    if constexpr (ACC == 2) {
+        // the exchange step of row sharding, folded into the product: the same value to the rank's own output and to
+        // every rank's gathered buffer (R consecutive floats per tile and target; peer memory is written, never read)
+        if ((lane % kLanesPerRow) == 0 && my_row < rows) {
+            float* o = pb.out + row0 + my_row;
+            *o = total;
             for (int t = 0; t < peers->n; t++)
                 *reinterpret_cast<float*>(reinterpret_cast<char*>(o) + peers->shift[t]) = total;
         }
+    } else {
+        if ((lane % kLanesPerRow) == 0 && my_row < rows)
+            pb.out[row0 + my_row] = (ACC && pb.accumulate) ? __ldcg(pb.out + row0 + my_row) + total : total;
     }
 }
 
