@@ -295,8 +295,7 @@ def run_gpu(args):
             return
         if peer is not None:
             ls.step(schedule, tag=steps_done[0] & 1)
-            peer.signal(ls.stream)
-            peer.wait(ls.stream)      # this rank's gathered buffer of the step's parity is complete
+            peer.signal_and_wait(ls.stream)      # this rank's gathered buffer of the step's parity is complete
             steps_done[0] += 1
             return
         g_off = 0
@@ -379,7 +378,7 @@ def run_gpu(args):
             "config": {"workload": WORKLOAD if args.workload == "mistral7b" else
                        f"llama70b_layer_set_x{args.layers}_q4k_decode_batch{args.tokens}_rowshard{world}",
                        "layers": args.layers, "gemvs_per_step": 7 * args.layers, "tokens": args.tokens,
-                       "schedule": schedule, "launches_per_step": launches + (2 if peer is not None else 0),
+                       "schedule": schedule, "launches_per_step": launches + (1 if peer is not None else 0),
                        "weights_bytes_per_gpu": ls.weight_bytes,
                        "dependencies": "chain: every product reads the previous step's output" if chain else
                        "independent products, inputs resident before the step",
@@ -403,7 +402,7 @@ def run_gpu(args):
                          "avg_launch_us": ms_kernel * 1e3 / main_launches},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": ls.x_bytes * world,
                     "d2h_bytes_per_step": ls.o_bytes * world},
-            "gpu_launches": (launches + (2 if peer is not None else 0)) * args.steps,   # + the two flag kernels per step
+            "gpu_launches": (launches + (1 if peer is not None else 0)) * args.steps,   # + the flag kernel of a step
             "clocks": clocks,
             "status": status,
         }

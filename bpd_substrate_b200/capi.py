@@ -102,6 +102,7 @@ SIGNATURES = {
     "bpdq_set_peer_outputs": (i32, [vp, sz, i32, vp]),
     "bpdq_peer_signal": (i32, [vp, i32, C.c_uint, vp]),
     "bpdq_peer_wait": (i32, [vp, i32, C.c_uint, vp]),
+    "bpdq_peer_signal_wait": (i32, [vp, vp, i32, C.c_uint, vp]),
     "bpd_llama_forward_tiles_cuda": (i32, [vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "bpdq_gemv_stream_create": (vp, [i32, vp, vp, sz]),
     "bpdq_gemv_stream_run": (i32, [vp, vp]),

@@ -67,6 +67,22 @@ __global__ void k_peer_wait(const unsigned* flags, int n, unsigned value, int* e
     if (err) atomicCAS(err, 0, 51);
 }
 
+// Both in one launch: thread i raises this rank's flag at rank i, then waits for rank i's flag here.
+__global__ void k_peer_signal_wait(PeerFlagSlots slots, const unsigned* flags, unsigned value, int* err)
+{
+    __threadfence_system();
+    const int i = threadIdx.x;
+    if (i >= slots.n) return;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(slots.slot[i]), "r"(value) : "memory");
+    for (unsigned poll = 0; poll < (1u << 22); poll++) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + i) : "memory");
+        if ((int)(v - value) >= 0) return;
+        __nanosleep(200);
+    }
+    if (err) atomicCAS(err, 0, 51);
+}
+
 }  // namespace bpdq
 
 using namespace bpdq;
@@ -127,6 +143,20 @@ int bpdq_peer_signal(unsigned* const* slots, int n, unsigned value, void* stream
         s.slot[i] = slots[i];
     }
     k_peer_signal<<<1, 32, 0, (cudaStream_t)stream>>>(s, value);
+    return check_cuda(cudaGetLastError());
+}
+
+int bpdq_peer_signal_wait(unsigned* const* slots, const unsigned* local_flags, int n, unsigned value, void* stream)
+{
+    if (n < 0 || n > kMaxPeerTargets || (n > 0 && (!slots || !local_flags))) return latch(BPDQ_ERR_ARG);
+    if (n == 0) return 0;
+    PeerFlagSlots s;
+    s.n = n;
+    for (int i = 0; i < n; i++) {
+        if (!slots[i] || ((uintptr_t)slots[i] & 3)) return latch(BPDQ_ERR_ALIGN);
+        s.slot[i] = slots[i];
+    }
+    k_peer_signal_wait<<<1, 32, 0, (cudaStream_t)stream>>>(s, local_flags, value, device_error_flag());
     return check_cuda(cudaGetLastError());
 }
 

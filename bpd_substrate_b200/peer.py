@@ -9,7 +9,7 @@ s+1 while another still reads step s; it cannot reach step s+2 before every rank
     ex = PeerExchange(lib, dist, rank, world, slot_bytes)      # slot = one rank's outputs of a step
     ex.register(local_out_base, parity); <record or make the step's launches>; ex.unregister()
     ... per step: run the launches recorded for parity = step & 1, then
-    ex.signal(stream); ex.wait(stream)                          # gathered(parity) is complete on this rank
+    ex.signal_and_wait(stream)      # (or ex.signal + ex.wait)    gathered(parity) is complete on this rank
 
 python -m bpd_substrate_b200.peer   (under torchrun, 2 or more GPUs): checks the gathered buffers against an
 NCCL all-gather of the same outputs, bit for bit, over several steps.
@@ -94,6 +94,12 @@ class PeerExchange:
         bpdq_last_status() then reads -4)."""
         capi.check(self.lib.bpdq_peer_wait(self.local_flags, self.world, self.step_no, stream), "bpdq_peer_wait")
 
+    def signal_and_wait(self, stream):
+        """signal() and wait() in one launch."""
+        self.step_no += 1
+        capi.check(self.lib.bpdq_peer_signal_wait(self._slots, self.local_flags, self.world, self.step_no, stream),
+                   "bpdq_peer_signal_wait")
+
     def close(self):
         self.lib.bpdq_set_peer_outputs(None, 0, 0, None)
         for p in self._imported:
@@ -133,8 +139,11 @@ def _selftest():
         ls.upload_activations(x)
         parity = step & 1
         ls.step("batched", tag=parity)
-        ex.signal(ls.stream)
-        ex.wait(ls.stream)
+        if step % 3 == 2:
+            ex.signal(ls.stream)
+            ex.wait(ls.stream)
+        else:
+            ex.signal_and_wait(ls.stream)
         capi.check(lib.bpdq_stream_sync(ls.stream))
         lib.bpdq_d2d(out_t.data_ptr(), ls.d_out, ls.o_bytes)
         lib.bpdq_d2d(got.data_ptr(), ex.gathered(parity), world * ls.o_bytes)

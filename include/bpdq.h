@@ -365,6 +365,8 @@ int bpdq_ipc_close(void* imported);
 int bpdq_set_peer_outputs(const void* local_base, size_t bytes, int n_targets, void* const* targets);
 int bpdq_peer_signal(unsigned* const* slots, int n, unsigned value, void* stream);
 int bpdq_peer_wait(const unsigned* local_flags, int n, unsigned value, void* stream);
+/* both in one launch (slot i belongs to the rank whose flag is local_flags[i]) */
+int bpdq_peer_signal_wait(unsigned* const* slots, const unsigned* local_flags, int n, unsigned value, void* stream);
 
 #ifdef __cplusplus
 }

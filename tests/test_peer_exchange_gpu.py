@@ -56,6 +56,11 @@ def test_flags_signal_wait_and_bounded_wait(lib):
     lib.bpdq_sync()
     assert lib.bpdq_last_status() == 0
     assert list(flags.read(np.uint32)) == [0, 7, 0, 7, 0, 0, 0, 0]
+    # both in one launch: slot i and flag i belong to the same rank
+    one = (C.c_void_p * 1)(flags.ptr + 20)
+    assert lib.bpdq_peer_signal_wait(one, flags.ptr + 20, 1, 3, None) == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == 0 and flags.read(np.uint32)[5] == 3
     # flags only grow: an older value is satisfied at once
     assert lib.bpdq_peer_wait(flags.ptr + 4, 1, 5, None) == 0
     lib.bpdq_sync()

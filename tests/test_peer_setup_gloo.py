@@ -63,6 +63,11 @@ class FakeLib:
         self.signals.append(([slots[i] for i in range(n)], value))
         return 0
 
+    def bpdq_peer_signal_wait(self, slots, flags, n, value, stream):
+        self.signals.append(([slots[i] for i in range(n)], value))
+        self.waits.append((flags, n, value))
+        return 0
+
     def bpdq_peer_wait(self, flags, n, value, stream):
         self.waits.append((flags, n, value))
         return 0
@@ -92,8 +97,7 @@ def _worker(rank, world, port, failing_rank, q):
         ex.unregister()
         assert lib.registered is None
         ex.signal(None)
-        ex.signal(None)
-        ex.wait(None)
+        ex.signal_and_wait(None)
         flags_off = 2 * world * slot
         assert lib.signals == [([b + flags_off + 4 * rank for b in bases], 1), ([b + flags_off + 4 * rank for b in bases], 2)]
         assert lib.waits == [(own + flags_off, world, 2)]
