@@ -35,7 +35,8 @@ N_LAYERS = 32
 KERNEL_OF = {"persistent": "k_gemv_stream_q4k_q8k", "batched": "k_gemv_batch_q4k_q8k", "grouped": "k_gemv_q4k_q8k", "separate": "k_gemv_q4k_q8k",
              "chain": "k_gemv_batch_q4k_q8k", "chain4": "k_gemv_batch_q4k_q8k", "chain-separate": "k_gemv_batch_q4k_q8k",
              "chain-persistent": "k_decode_chain"}
-# DRAM traffic / algorithmic bytes measured with ncu (profiles/*.md): nothing is re-read
+# DRAM traffic / algorithmic bytes of each schedule's dominant kernel, from profiler captures of a 4-layer
+# case (dram__bytes_read.sum + dram__bytes_write.sum per launch): nothing is re-read
 TRAFFIC_PER_ALGORITHMIC = {"persistent": 1.03, "batched": 1.03, "grouped": 1.00, "separate": 1.00, "chain": 1.03, "chain4": 1.03,
                            "chain-separate": 1.03, "chain-persistent": 1.03}
 
@@ -63,7 +64,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -128,18 +129,21 @@ def cpu_reference_run(steps, warmup, layers_per_step, threads):
         def gemv(w, x, out, rows, cols):
             orc.lib.orc_qmatmul_q4k(w, x, out, rows, cols, 0)
     rng = np.random.default_rng(2000)
-    mats = []
+    base = []
     nbytes = 0
     for name, rows, cols in synth.MISTRAL_LAYER:
-        w = synth.q4k_matrix(rows, cols, rng)
-        x = synth.activations(cols, rng)
-        out = np.zeros(rows, np.float32)
-        mats.append((w, x, out, rows, cols))
+        base.append((synth.q4k_matrix(rows, cols, rng), synth.activations(cols, rng), np.zeros(rows, np.float32), rows, cols))
         nbytes += synth.gemv_bytes_q4k(rows, cols)
     nbytes *= layers_per_step
+    # every layer of the step has its own weight bytes, as on the GPU (layer l = the base matrices rotated by
+    # l + 1 super-blocks): 3.9 GB for 32 layers, streamed from host memory once per step
+    layers = []
+    for layer in range(layers_per_step):
+        layers.append([(np.roll(w, synth.Q4K_BYTES * (layer + 1)) if layers_per_step > 1 else w, x, out, rows, cols)
+                       for w, x, out, rows, cols in base])
     pool = ThreadPoolExecutor(threads)
 
-    def one_layer():
+    def one_layer(mats):
         jobs = []
         for w, x, out, rows, cols in mats:
             rb = synth.q4k_row_bytes(cols)
@@ -153,11 +157,12 @@ def cpu_reference_run(steps, warmup, layers_per_step, threads):
             j.result()
 
     for _ in range(warmup):
-        one_layer()
+        for mats in layers:
+            one_layer(mats)
     t0 = time.perf_counter()
     for _ in range(steps):
-        for _ in range(layers_per_step):
-            one_layer()
+        for mats in layers:
+            one_layer(mats)
     dt = (time.perf_counter() - t0) / steps
     pool.shutdown()
     return nbytes / dt / 1e9, kind, dt
@@ -168,15 +173,17 @@ def run_reference(args):
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    steps, warmup = args.steps, max(args.warmup, 1)
-    value, kind, dt = cpu_reference_run(steps, warmup, 1, threads)
-    sample = ("1 of 32 layers per step (7 GEMVs, 218,103,808 weights), W4A32 bpd_qmatmul_q4k, "
-              "rows split over host threads")
+    # a step is the whole workload (32 layers, 224 GEMVs), about 0.6 s on 16 threads; the number of timed steps is
+    # bounded so that the run ends within a few minutes whatever --steps says
+    steps, warmup = max(1, min(args.steps, 100)), max(1, min(args.warmup, 3))
+    value, kind, dt = cpu_reference_run(steps, warmup, N_LAYERS, threads)
+    sample = (f"the whole step (32 layers, 224 GEMVs, 6,979,321,856 weights) {steps} times, W4A32 bpd_qmatmul_q4k of the "
+              f"reference (the only Q4_K GEMV it has), rows split over {threads} host threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
+        "config": {"workload": WORKLOAD, "layers": N_LAYERS, "gemvs_per_step": 7 * N_LAYERS, "tokens": 1, "sample": sample},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -184,6 +191,25 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------- GPU arm
+
+def check_layer(ls, x_all, layer, schedule):
+    """Runs the step once more and compares every product of one layer with the CPU checker (Q8_K
+    quantization and the Q4_K x Q8_K dot in binary64): norm-wise max|d| / max|ref| per product."""
+    from oracle.binding import Oracle
+    orc = Oracle()
+    ls.upload_activations(x_all)
+    ls.step(schedule)
+    out_all = ls.download_outputs()
+    worst = 0.0
+    for m, (_, rows, cols) in enumerate(ls.local):
+        T = ls.tokens
+        x = ls.activation_slice(x_all, layer, m).reshape(T, cols)
+        got = ls.output_slice(out_all, layer, m).reshape(T, rows)
+        _, ref64 = orc.qmm_q4k_q8k(ls.host_weight(layer, m), x, T, rows, cols)
+        worst = max(worst, float(np.max(np.abs(got - ref64)) / np.max(np.abs(ref64))))
+    return {"layer": layer, "products": len(ls.local), "max_norm_err": worst, "tolerance": 1e-5, "ok": bool(worst <= 1e-5),
+            "against": "CPU checker: Q8_K quantizer + Q4_K x Q8_K dot, binary64 sum"}
+
 
 def run_gpu(args):
     rank = int(os.environ.get("RANK", "0"))
@@ -231,7 +257,7 @@ def run_gpu(args):
     launches = ls.launches_per_step(schedule)
     # launches of the dominant kernel (the batched schedule adds one small quantizer per layer,
     # which overlaps the previous GEMV kernel and is counted in the step time)
-    main_launches = 1 if schedule == "persistent" else args.layers if schedule == "batched" else (
+    main_launches = launches // 2 if schedule == "persistent" else args.layers if schedule == "batched" else (
         1 if schedule == "chain-persistent" else
         (7 if schedule == "chain-separate" else 4) * args.layers if chain else launches)
     x_host = lib.bpdq_host_alloc(ls.x_bytes)
@@ -248,7 +274,7 @@ def run_gpu(args):
         # into chunks of layers; the gather of a chunk runs on a second stream under the GEMVs of the
         # next chunk, and the compute stream joins it before the step ends, so that one pair of CUDA
         # events on the compute stream spans GEMVs and exchange.
-        n_chunks = max(1, min(args.gather_chunks, args.layers)) if not chain and schedule != "persistent" else 1
+        n_chunks = max(1, min(args.gather_chunks, args.layers)) if not chain else 1
         bounds = [args.layers * c // n_chunks for c in range(n_chunks + 1)]
         chunks = [(bounds[c], bounds[c + 1]) for c in range(n_chunks)]
         gathered = torch.empty(world * (ls.o_bytes // 4), dtype=torch.float32, device="cuda")
@@ -260,13 +286,15 @@ def run_gpu(args):
     # The exchange without a collective: the product kernels store their results into every rank's gathered
     # buffer themselves (peer memory), and a flag per rank and step replaces the all-gather's rendezvous.
     peer = None
-    if world > 1 and args.exchange == "peer" and schedule == "batched" and args.tokens == 1:
+    if world > 1 and args.exchange == "peer" and schedule in ("batched", "persistent") and args.tokens == 1:
         from bpd_substrate_b200.peer import PeerExchange
         try:
             peer = PeerExchange(lib, dist, rank, world, ls.o_bytes)
             for parity in (0, 1):
                 peer.register(ls.d_out, parity)
                 ls.capture(schedule, tag=parity)
+                for r in ls.host_ranges(args.copy_chunks):      # the end-to-end leg replays ranges of layers
+                    ls.capture(schedule, r, tag=parity)
             peer.unregister()
         except Exception as exc:            # set-up fails on all ranks or on none (PeerExchange agrees on it)
             sys.stderr.write(f"rank {rank}: {exc}; using the NCCL all-gather\n")
@@ -319,34 +347,57 @@ def run_gpu(args):
     for _ in range(args.warmup):
         step_with_exchange()
     barrier()
-    if rank == 0:
-        sampler.rows.clear()
-    t_wall0 = time.perf_counter()
     lib.bpdq_event_record(ev0, ls.stream)
     for _ in range(args.steps):
         step_with_exchange()
     lib.bpdq_event_record(ev1, ls.stream)
     ms_total = lib.bpdq_event_elapsed_ms(ev0, ev1)
     barrier()
-    t_wall = time.perf_counter() - t_wall0
-    del t_wall
     # GEMV-only device time (no exchange), for the roofline of the kernel itself
     lib.bpdq_event_record(ev0, ls.stream)
     for _ in range(args.steps):
         ls.step(schedule)
     lib.bpdq_event_record(ev1, ls.stream)
     ms_kernel_total = lib.bpdq_event_elapsed_ms(ev0, ev1)
-    clocks = sampler.stop() if rank == 0 else None
+    # The timed region can be shorter than one period of the clock sampler: keep the same steps running for
+    # half a second more (untimed) so that the record holds samples taken under this very load.
+    clocks = None
+    if rank == 0:
+        t_soak = time.perf_counter()
+        while time.perf_counter() - t_soak < 0.5:
+            for _ in range(20):
+                ls.step(schedule)
+            lib.bpdq_stream_sync(ls.stream)
+        clocks = sampler.stop()
+        clocks["window"] = "warm-up, the timed steps and 0.5 s of the same steps after them, sampled every 20 ms"
+
+    # ---- one layer of the step against the CPU checker (rank 0; the checker is never the thing measured)
+    check = None
+    if rank == 0 and not chain and not args.no_check:
+        check = check_layer(ls, x_np, args.layers // 2, schedule)
 
     # ---- end to end through the public call with HOST buffers
-    host_kw = {} if chain else {"chunks": args.copy_chunks}
+    def host_step():
+        """Copies in, products, exchange of the output slices, copies out; returns when everything has finished."""
+        if chain:
+            ls.step_host(x_host, o_host, schedule)
+        elif peer is not None:
+            def flags():
+                peer.signal_and_wait(ls.stream)
+            ls.step_host(x_host, o_host, schedule, chunks=args.copy_chunks, tag=steps_done[0] & 1, after=flags)
+            steps_done[0] += 1
+        else:
+            ls.step_host(x_host, o_host, schedule, chunks=args.copy_chunks)
+            exchange_all()
+            if world > 1:
+                ext_stream.synchronize()
+
     for _ in range(min(args.warmup, 3)):
-        ls.step_host(x_host, o_host, schedule, **host_kw)
+        host_step()
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        ls.step_host(x_host, o_host, schedule, **host_kw)
-        exchange_all()
+        host_step()
     t_e2e = time.perf_counter() - t0
 
     ms_step = ms_total / args.steps
@@ -360,6 +411,13 @@ def run_gpu(args):
     if rank == 0:
         peak, peak_kind = measured_peak()
         total_bytes = step_bytes * world
+        if args.tokens > 1:
+            # several activation rows per product: the batched multi-token kernel where the schedule is batched
+            kernel_name = ls.multi_token_kernel(schedule)
+            traffic = None
+        else:
+            kernel_name = KERNEL_OF[schedule]
+            traffic = TRAFFIC_PER_ALGORITHMIC[schedule] * step_bytes / main_launches
         value = total_bytes / (ms_step * 1e-3) / 1e9
         achieved = step_bytes / (ms_kernel * 1e-3) / 1e9      # per GPU, kernel only
         e2e_value = total_bytes / (t_e2e / args.steps) / 1e9
@@ -394,8 +452,7 @@ def run_gpu(args):
             "elements_per_s": (ls.weight_bytes / synth.Q4K_BYTES * 256) * world / (ms_step * 1e-3),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)",
-                         "kernel": KERNEL_OF[schedule], "traffic": TRAFFIC_PER_ALGORITHMIC[schedule] * step_bytes
-                         / main_launches,
+                         "kernel": kernel_name, "traffic": traffic,
                          "traffic_source": "ncu dram__bytes_read+write per launch / algorithmic bytes, 4-layer capture "
                                            "(profiles/), scaled by bytes",
                          "algorithmic_bytes_per_launch": step_bytes / main_launches,
@@ -406,15 +463,17 @@ def run_gpu(args):
             "clocks": clocks,
             "status": status,
         }
+        if check:
+            line["check"] = check
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
+    ls.close()                     # (destroys the graphs that store to the peers' buffers)
     if world > 1:
-        dist.barrier()
         if peer is not None:
-            peer.close()
+            peer.close(dist)
+        dist.barrier()
         dist.destroy_process_group()
-    ls.close()
     if status != 0:
         sys.exit(1)
 
@@ -435,6 +494,7 @@ def main():
                          "chain-separate: the reference's 13-call sequence per layer; chain-persistent: the whole token as "
                          "one cooperative launch with grid-wide barriers between dependent phases")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the comparison of one layer with the CPU checker")
     ap.add_argument("--copy-chunks", type=int, default=4,
                     help="end-to-end leg: ranges of layers whose host copies run on their own streams under the other "
                          "ranges' GEMVs (1: copy in, step, copy out in sequence)")

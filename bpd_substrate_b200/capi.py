@@ -27,8 +27,6 @@ SIGNATURES = {
     "bpdq_set_tuning": (None, [i32, i32, i32, i32, i32]),
     "bpdq_sm_count": (i32, []),
     "bpdq_set_dequant_tuning": (None, [i32, i32]),
-    "bpdq_debug_trace": (None, [vp, sz, i32]),
-    "bpdq_debug_trace_tc5": (None, [vp]),
     # memory (size_t)
     "bpdq_alloc": (vp, [sz]),
     "bpdq_free": (None, [vp]),
@@ -55,6 +53,7 @@ SIGNATURES = {
     "bpdq_graph_launch": (i32, [vp, vp]),
     "bpdq_graph_destroy": (None, [vp]),
     "bpdq_set_device": (i32, [i32]),
+    "bpdq_mem_info": (i32, [vp, vp]),
     "bpdq_l2_bytes": (i32, []),
     # reference memory helpers
     **{f"{p}_alloc": (vp, [i32]) for p in ("qgpu", "sgpu", "gpu")},
@@ -106,6 +105,8 @@ SIGNATURES = {
     "bpd_llama_forward_tiles_cuda": (i32, [vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp]),
     "bpdq_gemv_stream_create": (vp, [i32, vp, vp, sz]),
     "bpdq_gemv_stream_run": (i32, [vp, vp]),
+    "bpdq_gemv_stream_run_ready": (i32, [vp, vp]),
+    "bpdq_gemv_stream_launches": (i32, [vp]),
     "bpdq_gemv_stream_destroy": (None, [vp]),
     "bpdq_chain_create": (vp, [i32, vp]),
     "bpdq_chain_run": (i32, [vp, vp]),
@@ -115,6 +116,10 @@ SIGNATURES = {
     "bpd_qmatmul_q4k_q8k_batch_static_cuda": (i32, [i32, vp, vp]),
     "bpdq_batch_static_capacity": (sz, []),
     "bpd_qmm_q4k_q8k_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
+    "bpdq_qmm_q4k_q8k_workspace_bytes": (sz, [i32, i32, i32]),
+    "bpd_qmm_q4k_q8k_ws_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, sz, vp]),
+    "bpd_qmm_q4k_q8k_mma_ints_cuda": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "bpd_qmm_q4k_q8k_tc5_ints_cuda": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "bpd_qmm_q4k_q8k_mma_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "bpd_qmm_q4k_q8k_tc5_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),
@@ -136,6 +141,14 @@ SIGNATURES = {
     "bpd_q8_0_block_dots_cuda": (i32, [vp, vp, vp, sz, vp]),
     "bpd_qmatmul_q8_0_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "bpd_embed_lookup_q8_0_cuda": (i32, [vp, vp, vp, i32, i32, vp]),
+    "bpd_embed_lookup_q8_0_vocab_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "bpd_qmatmul_q8_0_llamafile_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "bpd_qmatmul_q8_0_dispatch_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    **{f"bpd_gemm_q8_0_{rm}_{rn}_cuda": (i32, [vp, vp, i32, i32, i32, vp, i32, vp]) for rm in (1, 2, 4) for rn in (1, 2, 4)},
+    "bpdq_qmatmul_q8_0_tiles_workspace_bytes": (sz, [i32, i32, i32]),
+    "bpd_qmatmul_q8_0_tiles_ws_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp, sz, vp]),
+    "bpdq_llama_forward_workspace_bytes": (sz, [vp, i32]),
+    "bpd_llama_forward_ws_cuda": (i32, [vp, i32, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, sz, vp]),
     "bpd_q8_0_tiles_bytes": (sz, [i32, i32]),
     "bpd_repack_q8_0_tiles_cuda": (i32, [vp, vp, i32, i32, vp]),
     "bpd_unrepack_q8_0_tiles_cuda": (i32, [vp, vp, i32, i32, vp]),

@@ -23,7 +23,8 @@ enum {
     BPDQ_ERR_ARG = -1,        // null pointer, negative size, K not a block multiple
     BPDQ_ERR_ALIGN = -2,      // a pointer that must be 16-byte aligned is not
     BPDQ_ERR_RANGE = -3,      // shape beyond what the kernel supports
-    BPDQ_ERR_DEVICE = -4,     // a kernel gave up on a bounded wait
+    BPDQ_ERR_DEVICE = -4,     // a kernel gave up on a bounded wait, or skipped an out-of-range index
+    BPDQ_ERR_CAPTURE = -5,    // library-owned scratch would have to grow while the stream is being captured
     BPDQ_ERR_CUDA = -1000     // BPDQ_ERR_CUDA - cudaError_t
 };
 
@@ -47,6 +48,21 @@ struct Tuning {
 };
 Tuning& tuning();
 
+// Scratch memory of the compute entry points (runtime.cu).  A caller-owned workspace is a plain byte
+// range that the entry carves up; without one, the library keeps a block per (device, stream, purpose).
+// Such a block only grows, and a block that has been handed out is never freed before the process
+// ends (a larger replacement is a new allocation; launches in flight and captured graphs that hold
+// the old address stay valid).  Growing is refused while the stream is being captured.
+enum ScratchKind { kScratchGemmActs = 0, kScratchTc5Acts, kScratchTc5Reduce, kScratchTilesActs, kScratchForward,
+                   kScratchQ4ktActs, kScratchQ4ktReduce, kScratchQ80Acts, kScratchKinds };
+struct Workspace {
+    uint8_t* base;
+    size_t bytes, used;
+};
+// `bytes` of scratch for `kind`: from *ws when ws is given (BPDQ_ERR_RANGE if it does not fit), else the
+// library's block for (current device, s, kind).  Returns null and sets *status on failure.
+uint8_t* scratch_take(Workspace* ws, int kind, size_t bytes, cudaStream_t s, int* status);
+
 // gemv_batch.cu: bulk-copy GEMV for Q8_0 weights (BPDQ_ERR_RANGE when the shape needs the generic kernel)
 int gemv_q8_0_fast(const uint8_t* W, const float* x, float* out, int N, int K, cudaStream_t s);
 int gemv_q8_0_fast_multi(int n, const uint8_t* const* Ws, float* const* outs, const int* Ns, const float* x, int K,
@@ -63,11 +79,18 @@ struct PeerFlagSlots {
     unsigned* slot[kMaxPeerTargets];
 };
 bool peer_targets_for(const void* lo, const void* hi, PeerTargets& t);
-// gemm_q4k_mma.cu: tensor-core path for many tokens, out[tokens][N], C-ABI nibble order
-int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s);
-int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s);
+// gemm_q4k_mma.cu: tensor-core path for many tokens, out[tokens][N], C-ABI nibble order.  ws: caller-owned scratch or
+// null (library-owned); sb_ints: optional int32 [tokens][N][K/256][2], the exact (isum, msum) of every super-block
+int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s,
+                     Workspace* ws = nullptr, int32_t* sb_ints = nullptr);
+size_t gemm_q4k_q8k_mma_workspace(int tokens, int K);
+int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s,
+                     Workspace* ws = nullptr, int32_t* sb_ints = nullptr);
+size_t gemm_q4k_q8k_tc5_workspace(int tokens, int N, int K);
 // gemm_q8_0_tiles.cu: tcgen05 product on re-tiled Q8_0 weights, out[m*N + n], the scalar reference's fp32 order
-int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, cudaStream_t s);
+int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, cudaStream_t s,
+                    Workspace* ws = nullptr);
+size_t gemm_q8_0_tiles_workspace(int M, int N, int K);
 
 #ifdef __CUDACC__
 

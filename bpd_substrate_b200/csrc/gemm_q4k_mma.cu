@@ -38,6 +38,7 @@ struct GemmPlan {
     int stage_bytes, act_bytes;      // bytes per ring slot, of which activations
     int row_pitch, box_rows;         // TMA box: bytes per row piece (144 or 288), rows (<= N)
     size_t smem;
+    int32_t* ints;                   // optional [tokens][N][nb][2]: the exact (isum, msum) of every super-block, or null
 };
 
 // D = A x B (no accumulator input: the C operand is the zero register)
@@ -245,10 +246,21 @@ k_gemm_q4k_q8k_mma(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                             v = dp2a_lo(bs.z, mhi, v);
                             return dp2a_hi(bs.w, mhi, v);
                         };
-                        const float v0 = d0 * (float)isum[n][0] - m0 * (float)msum(bs0, mna[0], mna[1]);
-                        const float v1 = d0 * (float)isum[n][1] - m0 * (float)msum(bs1, mna[0], mna[1]);
-                        const float v2 = d1 * (float)isum[n][2] - m1 * (float)msum(bs0, mnb[0], mnb[1]);
-                        const float v3 = d1 * (float)isum[n][3] - m1 * (float)msum(bs1, mnb[0], mnb[1]);
+                        const int ms[4] = {msum(bs0, mna[0], mna[1]), msum(bs1, mna[0], mna[1]), msum(bs0, mnb[0], mnb[1]),
+                                           msum(bs1, mnb[0], mnb[1])};
+                        if (p.ints) {
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const int row = row0 + g + (i >> 1) * 8, tok = tok0 + 8 * n + 2 * t + (i & 1);
+                                if (row < p.N && tok < p.tokens)
+                                    *reinterpret_cast<int2*>(p.ints + (((size_t)tok * p.N + row) * p.nb + (st * kSbPerStage + sb)) * 2) =
+                                        make_int2(isum[n][i], ms[i]);
+                            }
+                        }
+                        const float v0 = d0 * (float)isum[n][0] - m0 * (float)ms[0];
+                        const float v1 = d0 * (float)isum[n][1] - m0 * (float)ms[1];
+                        const float v2 = d1 * (float)isum[n][2] - m1 * (float)ms[2];
+                        const float v3 = d1 * (float)isum[n][3] - m1 * (float)ms[3];
                         facc[n][0] = fmaf(dA0, v0, facc[n][0]);
                         facc[n][1] = fmaf(dA1, v1, facc[n][1]);
                         facc[n][2] = fmaf(dA0, v2, facc[n][2]);
@@ -291,29 +303,6 @@ static int make_weight_map(CUtensorMap* map, const uint8_t* W, int N, int nb, in
     return r == CUDA_SUCCESS ? 0 : latch(BPDQ_ERR_CUDA - 900 - (int)r);
 }
 
-// Scratch for the quantized activations of the GEMM path: grown on demand, kept per device.
-static uint8_t* gemm_scratch(size_t bytes)
-{
-    static uint8_t* buf[64] = {nullptr};
-    static size_t cap[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (cap[dev] < bytes) {
-        if (buf[dev]) {
-            cudaDeviceSynchronize();
-            cudaFree(buf[dev]);
-            buf[dev] = nullptr;
-            cap[dev] = 0;
-        }
-        size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
-        void* p = nullptr;
-        if (check_cuda(cudaMalloc(&p, want)) != 0) return nullptr;
-        buf[dev] = (uint8_t*)p;
-        cap[dev] = want;
-    }
-    return buf[dev];
-}
-
 template <int NT>
 static int launch_gemm(const uint8_t* W, const uint8_t* acts, float* out, const GemmPlan& p, cudaStream_t s)
 {
@@ -343,7 +332,8 @@ static int launch_gemm(const uint8_t* W, const uint8_t* acts, float* out, const 
 }
 
 // out[tokens][N] for up to 64 tokens per pass.  C-ABI nibble order only.
-int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s)
+int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s, Workspace* ws,
+                     int32_t* sb_ints)
 {
     if (tokens < 0 || N < 0 || K <= 0 || (K % 256) != 0) return latch(BPDQ_ERR_ARG);
     if (tokens == 0 || N == 0) return 0;
@@ -382,9 +372,13 @@ int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, i
         if (p.stages > 6) p.stages = 6;
         if (p.stages < 2) return latch(BPDQ_ERR_RANGE);
         p.smem = 128 + (size_t)p.stages * p.stage_bytes;
+        p.ints = sb_ints ? sb_ints + (size_t)t0 * N * p.nb * 2 : nullptr;
         const size_t scratch_bytes = (size_t)p.nb * p.tok_pad * kActPitch;
-        uint8_t* acts = gemm_scratch(scratch_bytes);
-        if (!acts) return latch(BPDQ_ERR_CUDA);
+        // every pass of 64 tokens uses the same scratch: the quantizer waits for the pass before it
+        Workspace pass_ws = ws ? *ws : Workspace{nullptr, 0, 0};
+        int src = 0;
+        uint8_t* acts = scratch_take(ws ? &pass_ws : nullptr, kScratchGemmActs, scratch_bytes, s, &src);
+        if (!acts) return src;
         const long units = (long)p.nb * p.tok_pad;
         long want = (units + 7) / 8, cap = (long)sm_count() * 8;
         int rc;
@@ -406,6 +400,14 @@ int gemm_q4k_q8k_mma(const uint8_t* W, const float* X, float* out, int tokens, i
         if (rc) return latch(rc);
     }
     return 0;
+}
+
+// scratch bytes of gemm_q4k_q8k_mma for these sizes (an upper bound over its token passes)
+size_t gemm_q4k_q8k_mma_workspace(int tokens, int K)
+{
+    const int T = tokens < 64 ? tokens : 64;
+    const int nt = T <= 8 ? 1 : (T <= 32 ? 2 : 4), ts = T <= 16 ? 1 : 2;
+    return (size_t)(K / 256) * (8 * nt * ts) * kActPitch + 256;
 }
 
 }  // namespace bpdq

@@ -53,7 +53,8 @@ struct Tc5Plan {
     int raw_bytes;                // ring slot: rows + activations
     int off_raw, off_side, off_bar;
     size_t smem;
-    unsigned long long* trace;    // tuning aid: global-timer stamps of CTA 0, [role 0..4][super-block 0..31], or null
+    unsigned long long* trace;    // tuning aid (BPDQ_TC5_TRACE builds): stamps of CTA 0, [role 0..4][super-block 0..31], or null
+    int32_t* ints;                // optional [tokens][N][nb][2]: the exact (isum, msum) of every super-block, or null
 };
 
 __device__ __forceinline__ unsigned long long tc5_timer()
@@ -424,6 +425,9 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
 #pragma unroll
             for (int t = 0; t < kEpiCols; t++) facc[t] = 0.0f;
             bool gave_up = false;
+            const int unit = blockIdx.x + ul * gridDim.x;
+            const int tile = unit / p.splits, split = unit - tile * p.splits;
+            const int rowg = tile * kRows + r;
             for (int b = 0; b < p.sb_per_unit; b++, i++) {
                 const int a = kPasses == 2 ? pass : (i & 1);
                 const int use = kPasses == 2 ? i : (i >> 1);
@@ -449,6 +453,13 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                         const float v = d * (float)(8 * hi[t] + lo[t]) - dmin * (float)(64 * mh[t] + ml[t]);
                         facc[8 * c + t] = fmaf(dA[t], v, facc[8 * c + t]);
                     }
+                    if (p.ints && rowg < p.N) {
+#pragma unroll
+                        for (int t = 0; t < 8; t++)
+                            if (c0 + 8 * c + t < p.tokens)
+                                *reinterpret_cast<int2*>(p.ints + (((size_t)(c0 + 8 * c + t) * p.N + rowg) * p.nb + (split * p.sb_per_unit + b)) * 2) =
+                                    make_int2(8 * hi[t] + lo[t], 64 * mh[t] + ml[t]);
+                    }
                 }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -456,9 +467,6 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
                 if (tid == 32 * kTransformWarps) TC5_TRACE(4, i);
             }
             if (gave_up) break;
-            const int unit = blockIdx.x + ul * gridDim.x;
-            const int tile = unit / p.splits, split = unit - tile * p.splits;
-            const int rowg = tile * kRows + r;
             if (p.splits == 1) {
                 if (rowg < p.N) {
 #pragma unroll
@@ -519,32 +527,9 @@ k_gemm_q4k_q8k_tc5(const __grid_constant__ CUtensorMap wmap, const uint8_t* __re
     }
 }
 
+#ifdef BPDQ_TC5_TRACE
 static unsigned long long* g_tc5_trace = nullptr;
-
-// Per-device grow-only buffers: slot 0 = quantized activations, slot 1 = split-K partial sums and arrival counters.
-static uint8_t* tc5_scratch(int slot, size_t bytes)
-{
-    static uint8_t* bufs[2][64] = {{nullptr}};
-    static size_t caps[2][64] = {{0}};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    uint8_t** buf = bufs[slot];
-    size_t* cap = caps[slot];
-    if (cap[dev] < bytes) {
-        if (buf[dev]) {
-            cudaDeviceSynchronize();
-            cudaFree(buf[dev]);
-            buf[dev] = nullptr;
-            cap[dev] = 0;
-        }
-        void* ptr = nullptr;
-        const size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
-        if (check_cuda(cudaMalloc(&ptr, want)) != 0) return nullptr;
-        buf[dev] = (uint8_t*)ptr;
-        cap[dev] = want;
-    }
-    return buf[dev];
-}
+#endif
 
 static int tc5_weight_map(CUtensorMap* map, const uint8_t* W, int N, int nb)
 {
@@ -592,7 +577,8 @@ static int launch_tc5(const CUtensorMap& wmap, const uint8_t* acts, float* out, 
 }
 
 // out[tokens][N], X fp32 [tokens][K], C-ABI nibble order; N >= 128 rows (the TMA box), up to 64 tokens per pass.
-int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s)
+int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, int N, int K, cudaStream_t s, Workspace* ws,
+                     int32_t* sb_ints)
 {
     if (tokens < 0 || N < 0 || K <= 0 || (K % 256) != 0) return latch(BPDQ_ERR_ARG);
     if (tokens == 0 || N == 0) return 0;
@@ -608,7 +594,12 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
         p.N = N;
         p.nb = K / 256;
         p.tokens = T;
+#ifdef BPDQ_TC5_TRACE
         p.trace = g_tc5_trace;
+#else
+        p.trace = nullptr;
+#endif
+        p.ints = sb_ints ? sb_ints + (size_t)t0 * N * p.nb * 2 : nullptr;
         p.npad = T <= 16 ? 16 : (T <= 32 ? 32 : 64);
         p.n_tiles = (N + kRows - 1) / kRows;
         // Split K so that every SM has work and the per-CTA chain of super-blocks is short: pick the
@@ -641,11 +632,15 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
         p.off_bar = take(256);
         p.smem = off;
         if (p.smem > 227 * 1024) return latch(BPDQ_ERR_RANGE);
-        uint8_t* acts = tc5_scratch(0, (size_t)p.nb * p.act_bytes);
-        if (!acts) return latch(BPDQ_ERR_CUDA);
+        // every pass of 64 tokens uses the same scratch: the quantizer waits for the pass before it
+        Workspace pass_ws = ws ? *ws : Workspace{nullptr, 0, 0};
+        int src = 0;
+        uint8_t* acts = scratch_take(ws ? &pass_ws : nullptr, kScratchTc5Acts, (size_t)p.nb * p.act_bytes, s, &src);
+        if (!acts) return src;
         const size_t arrivals_bytes = ((size_t)p.n_tiles * 2 * sizeof(unsigned) + 255) / 256 * 256;
-        uint8_t* red = tc5_scratch(1, arrivals_bytes + (p.splits > 1 ? (size_t)p.splits * T * N * sizeof(float) : 0));
-        if (!red) return latch(BPDQ_ERR_CUDA);
+        uint8_t* red = scratch_take(ws ? &pass_ws : nullptr, kScratchTc5Reduce,
+                                    arrivals_bytes + (p.splits > 1 ? (size_t)p.splits * T * N * sizeof(float) : 0), s, &src);
+        if (!red) return src;
         p.arrivals = reinterpret_cast<unsigned*>(red);
         p.partials = reinterpret_cast<float*>(red + arrivals_bytes);
         const long units = (long)p.nb * p.npad;
@@ -671,16 +666,41 @@ int gemm_q4k_q8k_tc5(const uint8_t* W, const float* X, float* out, int tokens, i
     return 0;
 }
 
+// scratch bytes of gemm_q4k_q8k_tc5 (an upper bound: widest token padding, eight K ranges)
+size_t gemm_q4k_q8k_tc5_workspace(int tokens, int N, int K)
+{
+    const int T = tokens < 64 ? tokens : 64;
+    const int n_tiles = (N + kRows - 1) / kRows;
+    return (size_t)(K / 256) * 324 * 64 + 256 + ((size_t)n_tiles * 2 * sizeof(unsigned) + 255) / 256 * 256 +
+           (size_t)8 * T * N * sizeof(float) + 512;
+}
+
 }  // namespace bpdq
 
 using namespace bpdq;
 
 extern "C" {
-// Tuning aid: CTA 0 of later tcgen05 launches writes 5 x 32 global-timer stamps (ns) to dev_buf; NULL stops.
+#ifdef BPDQ_TC5_TRACE
+// Tuning aid of trace builds: CTA 0 of later tcgen05 launches writes 5 x 32 clock stamps to dev_buf; NULL stops.
 void bpdq_debug_trace_tc5(void* dev_buf) { g_tc5_trace = (unsigned long long*)dev_buf; }
+#endif
 // The tcgen05 kernel directly (bpd_qmm_q4k_q8k_cuda's dispatcher decides when to use it).
 int bpd_qmm_q4k_q8k_tc5_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream)
 {
     return gemm_q4k_q8k_tc5(qweight, X, out, tokens, M, K, (cudaStream_t)stream);
+}
+// Checking forms of the two tensor-core kernels: besides out they store, for every (token, row, super-block), the
+// exact int32 pair (isum, msum) that the fp32 scales are applied to; sb_ints is [tokens][M][K/256][2].
+int bpd_qmm_q4k_q8k_tc5_ints_cuda(const uint8_t* qweight, const float* X, float* out, int32_t* sb_ints, int tokens, int M, int K,
+                                  void* stream)
+{
+    if (!sb_ints || ((uintptr_t)sb_ints & 7)) return latch(sb_ints ? BPDQ_ERR_ALIGN : BPDQ_ERR_ARG);
+    return gemm_q4k_q8k_tc5(qweight, X, out, tokens, M, K, (cudaStream_t)stream, nullptr, sb_ints);
+}
+int bpd_qmm_q4k_q8k_mma_ints_cuda(const uint8_t* qweight, const float* X, float* out, int32_t* sb_ints, int tokens, int M, int K,
+                                  void* stream)
+{
+    if (!sb_ints || ((uintptr_t)sb_ints & 7)) return latch(sb_ints ? BPDQ_ERR_ALIGN : BPDQ_ERR_ARG);
+    return gemm_q4k_q8k_mma(qweight, X, out, tokens, M, K, (cudaStream_t)stream, nullptr, sb_ints);
 }
 }

@@ -328,29 +328,6 @@ static size_t tiles_bytes(int N, int K)
     return (size_t)((N + kTileRows - 1) / kTileRows) * (size_t)(K / 32) * kTileUnit;
 }
 
-// Per-device grow-only buffer for the quantized activations.
-static uint8_t* tiles_scratch(size_t bytes)
-{
-    static uint8_t* buf[64] = {nullptr};
-    static size_t cap[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (cap[dev] < bytes) {
-        if (buf[dev]) {
-            cudaDeviceSynchronize();
-            cudaFree(buf[dev]);
-            buf[dev] = nullptr;
-            cap[dev] = 0;
-        }
-        void* ptr = nullptr;
-        const size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
-        if (check_cuda(cudaMalloc(&ptr, want)) != 0) return nullptr;
-        buf[dev] = (uint8_t*)ptr;
-        cap[dev] = want;
-    }
-    return buf[dev];
-}
-
 static int permute_tiles(bool forward, const uint8_t* src, uint8_t* dst, int N, int K, cudaStream_t s)
 {
     if (N < 0 || K <= 0 || (K % 32) != 0) return latch(BPDQ_ERR_ARG);
@@ -395,7 +372,7 @@ static int launch_q8t(const uint8_t* tiles, const uint8_t* acts, float* out, int
 }
 
 // out[m*N + n] = W row n . q8_0(X row m), W in the re-tiled layout.
-int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, cudaStream_t s)
+int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, cudaStream_t s, Workspace* ws)
 {
     if (M < 0 || N < 0 || K <= 0 || (K % 32) != 0) return latch(BPDQ_ERR_ARG);
     if (M == 0 || N == 0) return 0;
@@ -420,8 +397,9 @@ int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int
     }
     const long token_tiles = (M + T - 1) / T;
     if (token_tiles > 65535) return latch(BPDQ_ERR_RANGE);
-    uint8_t* acts = tiles_scratch((size_t)token_tiles * nb * 36 * T);
-    if (!acts) return latch(BPDQ_ERR_CUDA);
+    int src = 0;
+    uint8_t* acts = scratch_take(ws, kScratchTilesActs, (size_t)token_tiles * nb * 36 * T, s, &src);
+    if (!acts) return src;
     {
         const long n_items = token_tiles * nb * T * 8;
         const long want = (n_items + 255) / 256, cap = (long)sm_count() * 8;
@@ -440,6 +418,13 @@ int gemm_q8_0_tiles(const uint8_t* tiles, const float* X, float* out, int M, int
     int rc = T == 16 ? launch_q8t<16>(tiles, acts, out, M, N, nb, s)
                      : (T == 32 ? launch_q8t<32>(tiles, acts, out, M, N, nb, s) : launch_q8t<64>(tiles, acts, out, M, N, nb, s));
     return rc ? latch(rc) : 0;
+}
+
+// scratch bytes of gemm_q8_0_tiles: 36 bytes per 32 activations, tokens padded to the widest token tile
+size_t gemm_q8_0_tiles_workspace(int M, int N, int K)
+{
+    (void)N;
+    return (size_t)((M + 63) / 64) * (size_t)(K / 32) * 36 * 64 + 256;
 }
 
 }  // namespace bpdq
@@ -466,5 +451,17 @@ int bpd_unrepack_q8_0_tiles_cuda(const uint8_t* tiles, uint8_t* raw, int N, int 
 int bpd_qmatmul_q8_0_tiles_cuda(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, void* stream)
 {
     return gemm_q8_0_tiles(tiles, X, out, M, N, K, (cudaStream_t)stream);
+}
+// the same with caller-owned scratch (bpdq_qmatmul_q8_0_tiles_workspace_bytes; 16-byte aligned)
+size_t bpdq_qmatmul_q8_0_tiles_workspace_bytes(int M, int N, int K)
+{
+    return M > 0 && K > 0 ? gemm_q8_0_tiles_workspace(M, N, K) : 0;
+}
+int bpd_qmatmul_q8_0_tiles_ws_cuda(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, void* workspace,
+                                   size_t workspace_bytes, void* stream)
+{
+    if (!workspace || ((uintptr_t)workspace & 15)) return latch(workspace ? BPDQ_ERR_ALIGN : BPDQ_ERR_ARG);
+    Workspace ws = {(uint8_t*)workspace, workspace_bytes, 0};
+    return gemm_q8_0_tiles(tiles, X, out, M, N, K, (cudaStream_t)stream, &ws);
 }
 }

@@ -26,10 +26,12 @@ struct QuantVectors {
 };
 
 // Activation quantizer of the batched path: one warp per 256-block, records go to global
-// scratch memory in the layout the GEMV kernel keeps in shared memory.  The inputs are not
-// written by the kernel before it in the stream in any way this kernel could know, so it reads
-// them at once and only joins the stream order (pdl_wait) before it ends; the scratch it
-// writes must therefore not be in use by an earlier launch.
+// scratch memory in the layout the GEMV kernel keeps in shared memory.  wait_first = 1: ordered
+// like any launch (the vectors may be written, and the scratch read, by the launch ahead of it).
+// wait_first = 0: the caller promises that the vectors are complete and the scratch unused, so the
+// kernel reads at once and only joins the stream order (pdl_wait) before it ends.  The vectors are
+// read past L1 (ld.global.cg): with programmatic launch this kernel can be resident while the
+// launch that writes them is still running, which rules out the non-coherent path.
 template <int FMT>
 __global__ void __launch_bounds__(256) k_quant_records(const QuantVectors q, uint8_t* __restrict__ records,
                                                         int wait_first)
@@ -43,7 +45,7 @@ __global__ void __launch_bounds__(256) k_quant_records(const QuantVectors q, uin
         int blk = b, k = 0;
         while (k + 1 < q.n_vectors && blk >= q.vec[k].nb) { blk -= q.vec[k].nb; k++; }
         const float4* xb = reinterpret_cast<const float4*>(q.vec[k].x + (size_t)blk * 256);
-        const float4 v0 = __ldg(xb + lane), v1 = __ldg(xb + 32 + lane);
+        const float4 v0 = __ldcg(xb + lane), v1 = __ldcg(xb + 32 + lane);
         if (FMT == 0) write_records(v0, v1, records + q.vec[k].xq_off + (size_t)(2 * blk) * kXqStride, lane);
         else write_records_q80(v0, v1, records + q.vec[k].xq_off + (size_t)(4 * blk) * kQ80PairStride, lane);
     }
@@ -191,11 +193,12 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
     }
 
     if (p.records) {
-        // Records were written by the quantizer kernel launched just before this one: one thread
-        // waits for it (and so for everything earlier in the stream) and pulls them in with one
-        // bulk copy; everybody else waits for the bytes.
+        // Records were written by the quantizer kernel launched just before this one: every consumer
+        // thread waits for it (and so for everything earlier in the stream; unbounded by design, it is
+        // the stream order), one of them pulls the records in with one bulk copy, and the bounded wait
+        // that follows covers nothing but that copy.
+        pdl_wait();
         if (tid == 0) {
-            pdl_wait();
             mbar_expect_tx(xbar, (uint32_t)p.xq_bytes);
             bulk_g2s(xq, p.records, (uint32_t)p.xq_bytes, xbar);
         }
@@ -653,6 +656,10 @@ size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs)
 int bpd_qmatmul_q4k_q8k_batch_static_cuda(int n, const bpdq_gemv_desc* descs, void* stream)
 {
     if (n < 0 || (n > 0 && !descs)) return latch(BPDQ_ERR_ARG);
+    for (int j = 0; j < n; j++) {     // malformed descriptors are an argument error, whatever their size
+        if (descs[j].M < 0 || descs[j].K <= 0 || (descs[j].K % 256) != 0) return latch(BPDQ_ERR_ARG);
+        if (descs[j].M > 0 && (!descs[j].W || !descs[j].x || !descs[j].out)) return latch(BPDQ_ERR_ARG);
+    }
     // the records of all launches of this call sit side by side in the fixed array
     if (bpdq_batch_workspace_bytes(n, descs) > kStaticRecordBytes) return latch(BPDQ_ERR_RANGE);
     int rc = 0;

@@ -1,6 +1,6 @@
-// Whole programs of Q4_K x Q8_K products in ONE launch, built from the batched kernel's pieces
+// A whole program of dependent Q4_K x Q8_K products in ONE launch, built from the batched kernel's pieces
 // (gemv_q4k_device.cuh): k_decode_chain walks dependent phases with a grid-wide barrier between them
-// (cooperative launch), k_gemv_stream_q4k_q8k walks independent products without any.
+// (cooperative launch).  Streams of independent products are in gemv_stream.cu.
 #include "gemv_q4k_device.cuh"
 
 #include <cstring>
@@ -34,10 +34,14 @@ struct ChainPlan {
     size_t smem;
     unsigned long long* trace;  // tuning aid: SM-clock stamps of CTA 0, [phase < 64][4], or null
 };
+#ifdef BPDQ_TRACE_BUILD
 #define CHAIN_TRACE(ph, k)                                                                     \
     do {                                                                                       \
         if (p.trace && blockIdx.x == 0 && tid == 0 && (ph) < 64) p.trace[(ph) * 4 + (k)] = clock64(); \
     } while (0)
+#else
+#define CHAIN_TRACE(ph, k) do { } while (0)
+#endif
 
 template <int LAYOUT, int MAXTHREADS>
 __global__ void __launch_bounds__(MAXTHREADS, 1)
@@ -308,333 +312,11 @@ static void chain_destroy(ChainHandle* h)
     delete h;
 }
 
-// ---- Stream of independent products: ONE persistent launch for any number of them.
-// The batched kernel above covers up to kMaxBatch products; a step of the benchmark has 224, i.e. 32
-// launches, and each launch boundary drains the weight ring: the SM idles from its CTA's last tile
-// until the next launch's first tile has arrived.  Here the products are cut into phases (as many
-// consecutive products as the shared-memory record buffer holds), the producer warp streams the tiles
-// of all phases back to back, and the consumer warps only pause between phases to swap the
-// activation records (a CTA-local barrier and one pass over <= 48 KB from L2).  All activation vectors
-// are quantized beforehand by one launch of k_quant_records_table.  No CTA waits for another.
-struct StreamPhase {            // device program entry
-    int n_problems, n_tiles, rec_bytes, pad;
-    const uint8_t* records;     // this phase's activation records in global scratch (16-byte aligned)
-    long long pad2;
-    BatchProblem prob[kMaxBatch];
-};
-static_assert(sizeof(StreamPhase) % 16 == 0, "phase descriptors are copied in 16-byte pieces");
-struct StreamPlan {
-    const StreamPhase* phases;
-    int n_phases;
-    int nw, slots, slot_bytes;
-    int off_ring, off_xq, off_desc, off_bar;
-    size_t smem;
-};
-struct VecEntry {               // one distinct activation vector of a stream
-    const float* x;
-    int nb, block_begin;        // 256-blocks of this vector, index of its first block among all
-    size_t rec_off;             // byte offset of its records in the scratch
-};
-
-__global__ void __launch_bounds__(256) k_quant_records_table(const VecEntry* __restrict__ table, int n_vec, int total_blocks,
-                                                              uint8_t* __restrict__ records)
-{
-    pdl_launch_dependents();
-    pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int n_warps = (gridDim.x * blockDim.x) >> 5;
-    for (int b = warp; b < total_blocks; b += n_warps) {
-        int lo = 0, hi = n_vec - 1;          // last entry whose block_begin <= b
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (table[mid].block_begin <= b) lo = mid;
-            else hi = mid - 1;
-        }
-        const VecEntry e = table[lo];
-        const int blk = b - e.block_begin;
-        const float4* xb = reinterpret_cast<const float4*>(e.x + (size_t)blk * 256);
-        write_records(__ldcg(xb + lane), __ldcg(xb + 32 + lane), records + e.rec_off + (size_t)(2 * blk) * kXqStride, lane);
-    }
-}
-
-template <int LAYOUT, int MAXTHREADS>
-__global__ void __launch_bounds__(MAXTHREADS, 1)
-k_gemv_stream_q4k_q8k(const StreamPlan p, int* __restrict__ err)
-{
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* ring = smem + p.off_ring;                                 // [nw][slots][slot_bytes]
-    uint8_t* xq = smem + p.off_xq;                                     // activation records of the consumers' phase
-    StreamPhase* desc_p = reinterpret_cast<StreamPhase*>(smem + p.off_desc);   // the producer's phase
-    StreamPhase* desc_c = desc_p + 1;                                           // the consumers' phase
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bar);    // [nw*slots]
-    uint64_t* empty = full + p.nw * p.slots;
-    volatile int* dead = reinterpret_cast<volatile int*>(empty + p.nw * p.slots);   // a wait gave up: leave at the next barrier
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nw = p.nw, grid = (int)gridDim.x;
-    constexpr int kDescWords = sizeof(StreamPhase) / 16;
-    if (tid == 0) {
-        for (int s = 0; s < nw * p.slots; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
-        }
-        *dead = 0;
-        mbar_init_fence();
-    }
-    __syncthreads();
-    pdl_launch_dependents();
-
-    if (warp == nw) {
-        // ---- producer: lane g feeds consumer warp g; weights never depend on the launch before
-        int slot = 0;
-        uint32_t wait_parity = 0;
-        bool wrapped = false, ok = true;
-        for (int ph = 0; ph < p.n_phases; ph++) {
-            __syncwarp();
-            for (int w = lane; w < kDescWords; w += 32)
-                reinterpret_cast<uint4*>(desc_p)[w] = __ldg(reinterpret_cast<const uint4*>(p.phases + ph) + w);
-            __syncwarp();
-            if (lane < nw && ok) {
-                const int g = lane;
-                for (int v = g * grid + (int)blockIdx.x; v < desc_p->n_tiles; v += nw * grid) {
-                    const int s = g * p.slots + slot;
-                    if (wrapped && !mbar_wait_bounded(&empty[s], wait_parity, err, 1)) { ok = false; break; }
-                    int j = 0;
-#pragma unroll
-                    for (int q = 1; q < kMaxBatch; q++)
-                        if (q < desc_p->n_problems && v >= desc_p->prob[q].tile_begin) j = q;
-                    const BatchProblem& pb = desc_p->prob[j];
-                    const int row0 = (v - pb.tile_begin) * pb.rt;
-                    const uint32_t bytes = (uint32_t)min(pb.rt, pb.M - row0) * pb.row_bytes;
-                    mbar_expect_tx(&full[s], bytes);
-                    bulk_g2s(ring + (size_t)s * p.slot_bytes, pb.W + (size_t)row0 * pb.row_bytes, bytes, &full[s]);
-                    if (++slot == p.slots) {
-                        slot = 0;
-                        if (wrapped) wait_parity ^= 1u;
-                        wrapped = true;
-                    }
-                }
-            }
-        }
-        return;
-    }
-
-    // ---- consumers
-    pdl_wait();   // the records come from the quantizer launched just before
-    int slot = 0;
-    uint32_t parity = 0;
-    for (int ph = 0; ph < p.n_phases; ph++) {
-        // everybody has finished the previous phase: descriptor and records may be replaced
-        named_bar_sync(2, nw * 32);
-        if (*dead) break;
-        if (warp == 0)
-            for (int w = lane; w < kDescWords; w += 32)
-                reinterpret_cast<uint4*>(desc_c)[w] = __ldg(reinterpret_cast<const uint4*>(p.phases + ph) + w);
-        {
-            const StreamPhase* gp = p.phases + ph;
-            const int n16 = gp->rec_bytes >> 4;
-            const uint4* src = reinterpret_cast<const uint4*>(gp->records);
-            for (int w = tid; w < n16; w += nw * 32) reinterpret_cast<uint4*>(xq)[w] = __ldcg(src + w);
-        }
-        named_bar_sync(2, nw * 32);
-        const int n_tiles = desc_c->n_tiles, n_prob = desc_c->n_problems;
-        for (int v = warp * grid + (int)blockIdx.x; v < n_tiles; v += nw * grid) {
-            const int s = warp * p.slots + slot;
-            if (!mbar_wait_bounded(&full[s], parity, err, 2)) {
-                *dead = 1;      // keep meeting the others at the barriers; everybody leaves at the next one
-                break;
-            }
-            if (++slot == p.slots) {
-                slot = 0;
-                parity ^= 1u;
-            }
-            int j = 0;
-#pragma unroll
-            for (int q = 1; q < kMaxBatch; q++)
-                if (q < n_prob && v >= desc_c->prob[q].tile_begin) j = q;
-            const BatchProblem& pb = desc_c->prob[j];
-            const int row0 = (v - pb.tile_begin) * pb.rt;
-            const uint8_t* tile_smem = ring + (size_t)s * p.slot_bytes;
-            if (pb.rt == 4) batch_tile<4, LAYOUT, 0>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-            else if (pb.rt == 2) batch_tile<2, LAYOUT, 0>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-            else batch_tile<1, LAYOUT, 0>(tile_smem, xq + pb.xq_off, pb, row0, lane);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-        }
-    }
-}
-
-struct StreamHandle {
-    StreamPlan plan;
-    StreamPhase* d_phases;
-    VecEntry* d_table;
-    uint8_t* records;
-    int n_vec, total_blocks, device;
-};
-
-// Plans `n` independent products as phases of consecutive products (at most kMaxBatch per phase and
-// at most kStreamXqBytes of activation records), lays their records out in `ws` and uploads the program.
-constexpr int kStreamXqBytes = 48 * 1024;
-static StreamHandle* stream_create(int n, const BatchDesc* d, uint8_t* ws, size_t ws_bytes)
-{
-    if (n < 1 || !d || !ws || ((uintptr_t)ws & 15)) { latch(BPDQ_ERR_ARG); return nullptr; }
-    const Tuning& tu = tuning();
-    std::vector<StreamPhase> prog;
-    std::vector<VecEntry> table;
-    int slot_bytes = 0, xq_max = 0, total_blocks = 0;
-    size_t ws_used = 0;
-    size_t stream_bytes = 0;
-    for (int j = 0; j < n; j++)
-        if (d[j].M > 0 && d[j].K > 0) stream_bytes += (size_t)d[j].M * (d[j].K / 256) * BPDQ_Q4K_BYTES;
-    const int tile_budget = (stream_bytes >= kBigLaunchBytes && tu.tile_bytes < kBigLaunchTileBytes) ? kBigLaunchTileBytes : tu.tile_bytes;
-    int i = 0;
-    while (i < n) {
-        StreamPhase P;
-        memset(&P, 0, sizeof(P));
-        const size_t vec_first = table.size();
-        int xq_bytes = 0;
-        while (i < n && P.n_problems < kMaxBatch) {
-            const BatchDesc& q = d[i];
-            if (q.M <= 0 || q.K <= 0 || (q.K % 256) != 0 || !q.W || !q.x || !q.out) { latch(BPDQ_ERR_ARG); return nullptr; }
-            if (((uintptr_t)q.W & 15) || ((uintptr_t)q.x & 15) || ((uintptr_t)q.out & 3)) { latch(BPDQ_ERR_ALIGN); return nullptr; }
-            const int nb = q.K / 256, row_bytes = nb * BPDQ_Q4K_BYTES;
-            if (row_bytes > 32 * 1024) { latch(BPDQ_ERR_RANGE); return nullptr; }
-            size_t k = vec_first;
-            for (; k < table.size(); k++)
-                if (table[k].x == q.x && table[k].nb == nb) break;
-            const int add = k == table.size() ? 2 * nb * kXqStride : 0;
-            if (P.n_problems > 0 && xq_bytes + add > kStreamXqBytes) break;
-            if (add > kStreamXqBytes) { latch(BPDQ_ERR_RANGE); return nullptr; }
-            if (k == table.size()) {
-                VecEntry e;
-                e.x = q.x;
-                e.nb = nb;
-                e.block_begin = total_blocks;
-                e.rec_off = ws_used + (size_t)xq_bytes;
-                table.push_back(e);
-                total_blocks += nb;
-            }
-            BatchProblem& pb = P.prob[P.n_problems];
-            pb.W = q.W;
-            pb.out = q.out;
-            pb.M = q.M;
-            pb.nb = nb;
-            pb.row_bytes = row_bytes;
-            pb.rt = 4 * row_bytes <= tile_budget ? 4 : (2 * row_bytes <= tile_budget ? 2 : 1);
-            pb.tile_begin = P.n_tiles;
-            pb.xq_off = (int)(table[k].rec_off - ws_used);
-            pb.accumulate = 0;
-            P.n_tiles += (pb.M + pb.rt - 1) / pb.rt;
-            if (pb.rt * row_bytes > slot_bytes) slot_bytes = pb.rt * row_bytes;
-            xq_bytes += add;
-            P.n_problems++;
-            i++;
-        }
-        for (int j = P.n_problems; j < kMaxBatch; j++) {
-            P.prob[j] = P.prob[0];
-            P.prob[j].tile_begin = 0x7FFFFFFF;
-        }
-        P.rec_bytes = xq_bytes;
-        P.records = ws + ws_used;
-        ws_used += ((size_t)xq_bytes + 127) / 128 * 128;
-        if (ws_used > ws_bytes) { latch(BPDQ_ERR_RANGE); return nullptr; }
-        if (xq_bytes > xq_max) xq_max = xq_bytes;
-        prog.push_back(P);
-    }
-    StreamHandle* h = new StreamHandle();
-    StreamPlan& p = h->plan;
-    p.n_phases = (int)prog.size();
-    p.slot_bytes = slot_bytes;
-    p.slots = tu.stages < 2 ? 2 : tu.stages;
-    p.nw = tu.warps < 1 ? 1 : (tu.warps > 16 ? 16 : tu.warps);
-    for (;;) {
-        size_t off = 0;
-        auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
-        p.off_ring = take((size_t)p.nw * p.slots * p.slot_bytes);
-        p.off_xq = take((size_t)xq_max);
-        p.off_desc = take(2 * sizeof(StreamPhase));
-        p.off_bar = take((size_t)2 * p.nw * p.slots * 8 + 16);
-        p.smem = off;
-        if (p.smem <= (size_t)kSmemLimit) break;
-        if (p.slots > 2) p.slots--;
-        else if (p.nw > 4) p.nw--;
-        else { delete h; latch(BPDQ_ERR_RANGE); return nullptr; }
-    }
-    cudaGetDevice(&h->device);
-    void *dp = nullptr, *dt = nullptr;
-    if (check_cuda(cudaMalloc(&dp, sizeof(StreamPhase) * prog.size())) || check_cuda(cudaMalloc(&dt, sizeof(VecEntry) * table.size())) ||
-        check_cuda(cudaMemcpy(dp, prog.data(), sizeof(StreamPhase) * prog.size(), cudaMemcpyHostToDevice)) ||
-        check_cuda(cudaMemcpy(dt, table.data(), sizeof(VecEntry) * table.size(), cudaMemcpyHostToDevice))) {
-        if (dp) cudaFree(dp);
-        if (dt) cudaFree(dt);
-        delete h;
-        latch(BPDQ_ERR_CUDA);
-        return nullptr;
-    }
-    h->d_phases = (StreamPhase*)dp;
-    h->d_table = (VecEntry*)dt;
-    h->records = ws;
-    h->n_vec = (int)table.size();
-    h->total_blocks = total_blocks;
-    p.phases = h->d_phases;
-    return h;
-}
-
-static int stream_run(StreamHandle* h, cudaStream_t s)
-{
-    if (!h) return latch(BPDQ_ERR_ARG);
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev != h->device) return latch(BPDQ_ERR_ARG);
-    auto kern = k_gemv_stream_q4k_q8k<BPDQ_LAYOUT_BPD, kMidCtaThreads>;
-    static bool attr_set[64] = {false};
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-        if (rc) return latch(rc);
-        attr_set[dev] = true;
-    }
-    // quantizer: stream-ordered (its inputs may be anything the stream produced before)
-    const int qgrid = glue_grid(h->total_blocks);
-    k_quant_records_table<<<qgrid, 256, 0, s>>>(h->d_table, h->n_vec, h->total_blocks, h->records);
-    int rc = check_cuda(cudaGetLastError());
-    if (rc) return latch(rc);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)sm_count());
-    cfg.blockDim = dim3((unsigned)(h->plan.nw + 1) * 32);
-    cfg.dynamicSmemBytes = h->plan.smem;
-    cfg.stream = s;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = tuning().pdl ? 1 : 0;
-    rc = check_cuda(cudaLaunchKernelEx(&cfg, kern, h->plan, device_error_flag()));
-    return rc ? latch(rc) : 0;
-}
-
-static void stream_destroy(StreamHandle* h)
-{
-    if (!h) return;
-    cudaFree(h->d_phases);
-    cudaFree(h->d_table);
-    delete h;
-}
-
 }  // namespace bpdq
 
 using namespace bpdq;
 
 extern "C" {
-
-void* bpdq_gemv_stream_create(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes)
-{
-    return stream_create(n, reinterpret_cast<const BatchDesc*>(descs), (uint8_t*)workspace, workspace_bytes);
-}
-
-int bpdq_gemv_stream_run(void* handle, void* stream) { return stream_run((StreamHandle*)handle, (cudaStream_t)stream); }
-
-void bpdq_gemv_stream_destroy(void* handle) { stream_destroy((StreamHandle*)handle); }
 
 void* bpdq_chain_create(int n_phases, const bpdq_chain_phase* phases)
 {

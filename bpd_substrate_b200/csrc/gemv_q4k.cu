@@ -372,7 +372,8 @@ k_gemv_q4k_q8k(const void* __restrict__ xin, int K, const GemvPlan p, int* __res
 
 // ---------------------------------------------------------------- host side
 
-// Timeline capture for tuning: when set, launch k writes its stamps at trace_base + k * trace_stride.
+// Timeline capture of the tuning builds: launch k writes its stamps at trace_base + k * trace_stride.
+#ifdef BPDQ_TRACE_BUILD
 static unsigned long long* g_trace_base = nullptr;
 static size_t g_trace_stride = 0;
 static int g_trace_left = 0;
@@ -385,6 +386,9 @@ unsigned long long* trace_take()
     g_trace_left--;
     return at;
 }
+#else
+unsigned long long* trace_take() { return nullptr; }
+#endif
 
 static int rows_per_tile(int row_bytes)
 {
@@ -576,7 +580,7 @@ int gemm_q4k_q8k_multi(int n, const uint8_t* const* Ws, float* const* outs, cons
 }
 
 int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M, int K, int layout, int xsrc,
-                 int32_t* dbg, cudaStream_t s)
+                 int32_t* dbg, cudaStream_t s, Workspace* ws)
 {
     if (M < 0) return latch(BPDQ_ERR_ARG);
     // many tokens: the weights would be streamed once per four tokens here; the tensor-core
@@ -588,8 +592,8 @@ int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M,
     // against 10.8 us for the mma.sync kernel; smaller matrices stay here (4096x4096: 9.0 against 10.2)
     if (tokens > (large ? 2 : 4) && layout == BPDQ_LAYOUT_BPD && xsrc == 0 && !dbg) {
         if (large && (tokens >= 33 || (tokens >= 24 && M >= 8192)))
-            return gemm_q4k_q8k_tc5(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s);
-        return gemm_q4k_q8k_mma(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s);
+            return gemm_q4k_q8k_tc5(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s, ws);
+        return gemm_q4k_q8k_mma(W, reinterpret_cast<const float*>(x), out, tokens, M, K, s, ws);
     }
     return gemm_q4k_q8k_multi(1, &W, &out, &M, x, tokens, K, layout, xsrc, dbg, s);
 }
@@ -601,7 +605,8 @@ using namespace bpdq;
 
 extern "C" {
 
-// Debug aid: the next `launches` GEMV launches each write 8 global-timer stamps per CTA
+#ifdef BPDQ_TRACE_BUILD
+// Tuning builds only: the next `launches` GEMV launches each write 8 global-timer stamps per CTA
 // (ns) into dev_buf, `stride_u64` 64-bit words apart.  Pass NULL to stop.
 void bpdq_debug_trace(void* dev_buf, size_t stride_u64, int launches)
 {
@@ -609,6 +614,7 @@ void bpdq_debug_trace(void* dev_buf, size_t stride_u64, int launches)
     g_trace_stride = stride_u64;
     g_trace_left = dev_buf ? launches : 0;
 }
+#endif
 
 int bpd_quant_q8_K_cuda(const float* x, uint8_t* y, size_t n_elements, void* stream)
 {
@@ -641,6 +647,23 @@ int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int 
 {
     if ((layout != 0 && layout != 1) || (xsrc != 0 && xsrc != 1)) return latch(BPDQ_ERR_ARG);
     return gemm_q4k_q8k(qweight, x, out, tokens, M, K, layout, xsrc, subdots, (cudaStream_t)stream);
+}
+
+// The same with caller-owned scratch: nothing is allocated and no state is shared with other calls, so
+// calls on different streams may overlap as long as their workspaces differ.
+size_t bpdq_qmm_q4k_q8k_workspace_bytes(int tokens, int M, int K)
+{
+    if (tokens <= 0 || M <= 0 || K <= 0 || (K % 256) != 0) return 0;
+    const size_t a = gemm_q4k_q8k_mma_workspace(tokens, K), b = M >= 128 ? gemm_q4k_q8k_tc5_workspace(tokens, M, K) : 0;
+    return a > b ? a : b;
+}
+int bpd_qmm_q4k_q8k_ws_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,
+                            int xsrc, int32_t* subdots, void* workspace, size_t workspace_bytes, void* stream)
+{
+    if ((layout != 0 && layout != 1) || (xsrc != 0 && xsrc != 1) || !workspace) return latch(BPDQ_ERR_ARG);
+    if ((uintptr_t)workspace & 15) return latch(BPDQ_ERR_ALIGN);
+    Workspace ws = {(uint8_t*)workspace, workspace_bytes, 0};
+    return gemm_q4k_q8k(qweight, x, out, tokens, M, K, layout, xsrc, subdots, (cudaStream_t)stream, &ws);
 }
 
 // The tensor-core kernel at any token count (the dispatcher above picks it for more than 8).

@@ -24,11 +24,16 @@ __device__ __forceinline__ unsigned long long global_timer_ns()
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// Timeline stamps of the tuning builds (-DBPDQ_TRACE_BUILD); nothing in the default build.
+#ifdef BPDQ_TRACE_BUILD
 #define BPDQ_TRACE(slot)                                                              \
     do {                                                                              \
         if (p.trace && lane == 0 && (warp == 0 || (slot) == 7))                       \
             p.trace[(size_t)blockIdx.x * 8 + (slot)] = global_timer_ns();             \
     } while (0)
+#else
+#define BPDQ_TRACE(slot) do { } while (0)
+#endif
 
 
 // Quantize one 256-float block with a warp (rule of bench/bpd_cpu.c:4106-4136, fp32 scale).
@@ -339,13 +344,24 @@ __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8
     // ACC: launches with a residual epilogue are a separate instantiation (the conditional costs the
     // plain product 2 % of its bandwidth); the residual stream was written by an earlier launch: read it past L1
     if constexpr (ACC == 2) {
-        // the exchange step of row sharding, folded into the product: the same value to the rank's own output and to
-        // every rank's gathered buffer (R consecutive floats per tile and target; peer memory is written, never read)
-        if ((lane % kLanesPerRow) == 0 && my_row < rows) {
-            float* o = pb.out + row0 + my_row;
-            *o = total;
-            for (int t = 0; t < peers->n; t++)
-                *reinterpret_cast<float*>(reinterpret_cast<char*>(o) + peers->shift[t]) = total;
+        // The exchange step of row sharding, folded into the product: the tile's R results go to the rank's own output
+        // and to every rank's gathered buffer (peer memory is written, never read).  The row totals are gathered into
+        // every lane, then lane 0 stores to the own output and lane t to target t - 1, each with ONE store of R floats:
+        // one store instruction per tile for all targets together.
+        float vals[R];
+#pragma unroll
+        for (int rr = 0; rr < R; rr++) vals[rr] = __shfl_sync(0xFFFFFFFFu, total, rr * kLanesPerRow);
+        if (lane <= peers->n) {
+            char* dst = reinterpret_cast<char*>(pb.out + row0) + (lane == 0 ? 0ll : peers->shift[lane > 0 ? lane - 1 : 0]);
+            if (rows == R && (reinterpret_cast<uintptr_t>(dst) & (4 * R - 1)) == 0) {
+                if constexpr (R == 4) *reinterpret_cast<float4*>(dst) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+                else if constexpr (R == 2) *reinterpret_cast<float2*>(dst) = make_float2(vals[0], vals[1]);
+                else *reinterpret_cast<float*>(dst) = vals[0];
+            } else {
+#pragma unroll
+                for (int rr = 0; rr < R; rr++)
+                    if (rr < rows) reinterpret_cast<float*>(dst)[rr] = vals[rr];
+            }
         }
     } else {
         if ((lane % kLanesPerRow) == 0 && my_row < rows)
@@ -423,11 +439,11 @@ struct BatchDesc {
 };
 
 // ---- host side shared by the three files
-// gemv_q4k.cu: next timeline buffer of the tuning aid bpdq_debug_trace, or null
+// gemv_q4k.cu: next timeline buffer of a tuning build, else null
 unsigned long long* trace_take();
 // gemv_q4k.cu: one matrix (or tokens > 1), any shape
 int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M, int K, int layout, int xsrc,
-                 int32_t* dbg, cudaStream_t s);
+                 int32_t* dbg, cudaStream_t s, Workspace* ws = nullptr);
 // gemv_batch.cu: plan and launch of the batched kernel (fmt 0: Q4_K weights, 1: Q8_0)
 int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt = 0);
 int launch_batch_plan(const BatchPlan& p, int fmt, int layout, cudaStream_t s);

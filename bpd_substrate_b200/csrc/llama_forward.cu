@@ -150,7 +150,8 @@ __global__ void __launch_bounds__(256) k_rope_qk_store_kv(float* __restrict__ q,
                                                            const float* __restrict__ v, void* __restrict__ k_cache,
                                                            void* __restrict__ v_cache, const int32_t* __restrict__ pos_ids,
                                                            const float* __restrict__ freq_factors, int n_tokens, int n_heads,
-                                                           int n_kv_heads, int head_dim, int n_dims, float theta_scale)
+                                                           int n_kv_heads, int head_dim, int n_dims, float theta_scale,
+                                                           int max_seq_len, int* __restrict__ err)
 {
     const int half = n_dims / 2, pairs = head_dim / 2, heads = n_heads + 2 * n_kv_heads;
     const long total = (long)n_tokens * heads * pairs;
@@ -170,6 +171,10 @@ __global__ void __launch_bounds__(256) k_rope_qk_store_kv(float* __restrict__ q,
             const int hk = h - n_heads - (is_k ? 0 : n_kv_heads);
             const float* p = (is_k ? k : v) + ((size_t)t * n_kv_heads + hk) * head_dim + 2 * pair;
             float y0 = p[0], y1 = p[1];
+            if (pos < 0 || pos >= max_seq_len) {      // no cache row of that index: nothing is stored, code 20 is recorded
+                if (pair == 0 && hk == 0 && err) atomicCAS(err, 0, 20);
+                continue;
+            }
             if (is_k) rope_pair(p[0], p[1], pair, half, pos, freq_factors, theta_scale, y0, y1);
             const size_t at = ((size_t)pos * n_kv_heads + hk) * head_dim + 2 * pair;
             void* cache = is_k ? k_cache : v_cache;
@@ -184,15 +189,22 @@ __global__ void __launch_bounds__(256) k_rope_qk_store_kv(float* __restrict__ q,
     }
 }
 
-// cache[pos[t]][:] = f16(src[t][:]) (round to nearest even) or the fp32 copy
+// cache[pos[t]][:] = f16(src[t][:]) (round to nearest even) or the fp32 copy.  A position outside
+// [0, max_seq_len) has no cache row: nothing is stored for that token and code 20 is recorded.
 template <int F16>
 __global__ void __launch_bounds__(256) k_kv_write(void* __restrict__ cache, const float* __restrict__ src,
-                                                   const int32_t* __restrict__ pos_ids, int n_tokens, int row)
+                                                   const int32_t* __restrict__ pos_ids, int n_tokens, int row, int max_seq_len,
+                                                   int* __restrict__ err)
 {
     const long total = (long)n_tokens * row;
     for (long u = (long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long)gridDim.x * blockDim.x) {
         const int t = (int)(u / row), i = (int)(u - (long)t * row);
-        const size_t at = (size_t)pos_ids[t] * row + i;
+        const int pos = pos_ids[t];
+        if (pos < 0 || pos >= max_seq_len) {
+            if (i == 0 && err) atomicCAS(err, 0, 20);
+            continue;
+        }
+        const size_t at = (size_t)pos * row + i;
         if (F16) reinterpret_cast<__half*>(cache)[at] = __float2half_rn(src[u]);
         else reinterpret_cast<float*>(cache)[at] = src[u];
     }
@@ -335,28 +347,6 @@ static int grid_1d(long n)
     return (int)(want < 1 ? 1 : (want < cap ? want : cap));
 }
 
-// grow-only per-device scratch of the forward pass (x and the three scratch vectors of the reference)
-static float* forward_scratch(size_t floats)
-{
-    static float* buf[64] = {nullptr};
-    static size_t cap[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (cap[dev] < floats) {
-        if (buf[dev]) {
-            cudaDeviceSynchronize();
-            cudaFree(buf[dev]);
-            buf[dev] = nullptr;
-            cap[dev] = 0;
-        }
-        void* p = nullptr;
-        if (check_cuda(cudaMalloc(&p, floats * sizeof(float))) != 0) return nullptr;
-        buf[dev] = (float*)p;
-        cap[dev] = floats;
-    }
-    return buf[dev];
-}
-
 static int launch_attn(const float* q, const void* kc, const void* vc, float* dst, int n_q, int n_kv, int H, int HKV, int D,
                        float scale, int kv_offset, int f16, cudaStream_t s)
 {
@@ -386,10 +376,11 @@ static int launch_rope(const float* in, float* out, const int32_t* pos_ids, cons
     return check_cuda(cudaGetLastError());
 }
 
-static int launch_kv_write(void* cache, const float* src, const int32_t* pos_ids, int n_tokens, int row, int f16, cudaStream_t s)
+static int launch_kv_write(void* cache, const float* src, const int32_t* pos_ids, int n_tokens, int row, int f16, int max_seq_len,
+                           cudaStream_t s)
 {
-    if (f16) k_kv_write<1><<<grid_1d((long)n_tokens * row), 256, 0, s>>>(cache, src, pos_ids, n_tokens, row);
-    else k_kv_write<0><<<grid_1d((long)n_tokens * row), 256, 0, s>>>(cache, src, pos_ids, n_tokens, row);
+    if (f16) k_kv_write<1><<<grid_1d((long)n_tokens * row), 256, 0, s>>>(cache, src, pos_ids, n_tokens, row, max_seq_len, device_error_flag());
+    else k_kv_write<0><<<grid_1d((long)n_tokens * row), 256, 0, s>>>(cache, src, pos_ids, n_tokens, row, max_seq_len, device_error_flag());
     return check_cuda(cudaGetLastError());
 }
 
@@ -397,20 +388,24 @@ static int launch_kv_write(void* cache, const float* src, const int32_t* pos_ids
 // when there is one and enough tokens to pay for it, else on the rows (one pass per token).
 constexpr int kTilesMinTokens = 3;
 static int product(const uint8_t* rows, const uint8_t* tiles, const float* x, float* out, int n_tokens, int N, int K,
-                   cudaStream_t s)
+                   cudaStream_t s, Workspace* ws)
 {
-    if (tiles && n_tokens >= kTilesMinTokens) return gemm_q8_0_tiles(tiles, x, out, n_tokens, N, K, s);
+    if (tiles && n_tokens >= kTilesMinTokens) {
+        // consecutive products share one piece of scratch: they are ordered on the stream
+        Workspace one = ws ? *ws : Workspace{nullptr, 0, 0};
+        return gemm_q8_0_tiles(tiles, x, out, n_tokens, N, K, s, ws ? &one : nullptr);
+    }
     return bpd_qmatmul_q8_0_cuda(rows, x, out, n_tokens, N, K, s);
 }
 
 // Products that read the same vector: one launch where the fast Q8_0 kernel applies (one token, K a
 // multiple of 256, aligned pointers), else one call each.  Same arithmetic either way.
 static int products_shared_input(int n, const uint8_t* const* Ws, const uint8_t* const* Ts, float* const* outs, const int* Ns,
-                                 const float* x, int n_tokens, int K, cudaStream_t s)
+                                 const float* x, int n_tokens, int K, cudaStream_t s, Workspace* ws)
 {
     if (n_tokens == 1 && gemv_q8_0_fast_multi(n, Ws, outs, Ns, x, K, s) == 0) return 0;
     for (int j = 0; j < n; j++) {
-        int rc = product(Ws[j], Ts[j], x, outs[j], n_tokens, Ns[j], K, s);
+        int rc = product(Ws[j], Ts[j], x, outs[j], n_tokens, Ns[j], K, s, ws);
         if (rc) return rc;
     }
     return 0;
@@ -430,12 +425,14 @@ static int check_cfg(const bpd_llama_config* c, int n_tokens, int kv_pos)
 
 static int launch_rope_qk_store_kv(float* q, const float* k, const float* v, void* k_cache, void* v_cache, const int32_t* pos_ids,
                                    const float* ff, int n_tokens, int H, int HKV, int D, int n_dims, float freq_base, int f16,
-                                   cudaStream_t s)
+                                   int max_seq_len, cudaStream_t s)
 {
     const float theta_scale = powf(freq_base, -2.0f / (float)n_dims);
     const int grid = grid_1d((long)n_tokens * (H + 2 * HKV) * (D / 2));
-    if (f16) k_rope_qk_store_kv<1><<<grid, 256, 0, s>>>(q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale);
-    else k_rope_qk_store_kv<0><<<grid, 256, 0, s>>>(q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale);
+    if (f16) k_rope_qk_store_kv<1><<<grid, 256, 0, s>>>(q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale,
+                                                        max_seq_len, device_error_flag());
+    else k_rope_qk_store_kv<0><<<grid, 256, 0, s>>>(q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale,
+                                                    max_seq_len, device_error_flag());
     return check_cuda(cudaGetLastError());
 }
 
@@ -445,7 +442,8 @@ static int launch_rope_qk_store_kv(float* q, const float* k, const float* v, voi
 static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_llama_layer_weights* lt,
                          const bpd_llama_config* cfg, const int32_t* pos_ids,
                          int n_tokens, int kv_pos, void* k_cache, void* v_cache, float* s1, float* s2, float* s3,
-                         const float* rope_freqs, bool x_normed, bool fuse_next, const float* next_norm_w, cudaStream_t s)
+                         const float* rope_freqs, bool x_normed, bool fuse_next, const float* next_norm_w, cudaStream_t s,
+                         Workspace* ws)
 {
     const int E = cfg->embed_dim, H = cfg->n_heads, HKV = cfg->n_kv_heads, D = cfg->head_dim, F = cfg->ffn_dim;
     const int n_kv_full = cfg->max_seq_len;
@@ -461,33 +459,33 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
         const uint8_t* Ts[3] = {lt ? lt->w_q : nullptr, lt ? lt->w_k : nullptr, lt ? lt->w_v : nullptr};
         float* outs[3] = {s2, s3, vbuf};
         const int Ns[3] = {H * D, row, row};
-        if ((rc = products_shared_input(kv_together ? 3 : 2, Ws, Ts, outs, Ns, s1, n_tokens, E, s))) return rc;
+        if ((rc = products_shared_input(kv_together ? 3 : 2, Ws, Ts, outs, Ns, s1, n_tokens, E, s, ws))) return rc;
     }
     if (kv_together) {
         if ((rc = launch_rope_qk_store_kv(s2, s3, vbuf, k_cache, v_cache, pos_ids, rope_freqs, n_tokens, H, HKV, D, cfg->rope_dim,
-                                          cfg->rope_base, cfg->kv_cache_f16, s)))
+                                          cfg->rope_base, cfg->kv_cache_f16, cfg->max_seq_len, s)))
             return rc;
     } else {
         if ((rc = launch_rope(s2, s2, pos_ids, rope_freqs, n_tokens, H, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
         if ((rc = launch_rope(s3, s3, pos_ids, rope_freqs, n_tokens, HKV, D, cfg->rope_dim, cfg->rope_base, s))) return rc;
-        if ((rc = launch_kv_write(k_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
-        if ((rc = product(lw->w_v, lt ? lt->w_v : nullptr, s1, vbuf, n_tokens, row, E, s))) return rc;
-        if ((rc = launch_kv_write(v_cache, vbuf, pos_ids, n_tokens, row, cfg->kv_cache_f16, s))) return rc;
+        if ((rc = launch_kv_write(k_cache, s3, pos_ids, n_tokens, row, cfg->kv_cache_f16, cfg->max_seq_len, s))) return rc;
+        if ((rc = product(lw->w_v, lt ? lt->w_v : nullptr, s1, vbuf, n_tokens, row, E, s, ws))) return rc;
+        if ((rc = launch_kv_write(v_cache, vbuf, pos_ids, n_tokens, row, cfg->kv_cache_f16, cfg->max_seq_len, s))) return rc;
     }
     if ((rc = launch_attn(s2, k_cache, v_cache, s1, n_tokens, n_kv_full, H, HKV, D, 1.0f / sqrtf((float)D), kv_pos,
                           cfg->kv_cache_f16, s)))
         return rc;
-    if ((rc = product(lw->w_o, lt ? lt->w_o : nullptr, s1, s2, n_tokens, E, H * D, s))) return rc;
+    if ((rc = product(lw->w_o, lt ? lt->w_o : nullptr, s1, s2, n_tokens, E, H * D, s, ws))) return rc;
     k_add_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, s2, lw->ffn_norm_w, s1, E, cfg->rms_eps);
     {
         const uint8_t* Ws[2] = {lw->w_gate, lw->w_up};
         const uint8_t* Ts[2] = {lt ? lt->w_gate : nullptr, lt ? lt->w_up : nullptr};
         float* outs[2] = {s2, s3};
         const int Ns[2] = {F, F};
-        if ((rc = products_shared_input(2, Ws, Ts, outs, Ns, s1, n_tokens, E, s))) return rc;
+        if ((rc = products_shared_input(2, Ws, Ts, outs, Ns, s1, n_tokens, E, s, ws))) return rc;
     }
     k_swiglu_f32<<<grid_1d((long)n_tokens * F), 256, 0, s>>>(s2, s3, s2, (long)n_tokens * F);
-    if ((rc = product(lw->w_down, lt ? lt->w_down : nullptr, s2, s1, n_tokens, E, F, s))) return rc;
+    if ((rc = product(lw->w_down, lt ? lt->w_down : nullptr, s2, s1, n_tokens, E, F, s, ws))) return rc;
     if (fuse_next) k_add_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, s1, next_norm_w, s1, E, cfg->rms_eps);
     else k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s1, x, (long)n_tokens * E);
     return check_cuda(cudaGetLastError());
@@ -522,19 +520,19 @@ int bpd_rope_norm_freqs_cuda(const float* input, float* output, const int32_t* p
 int bpd_kv_cache_write_f16_cuda(uint16_t* cache, const float* src, const int32_t* pos_ids, int n_tokens, int n_kv_heads,
                                 int head_dim, int max_seq_len, void* stream)
 {
-    (void)max_seq_len;
-    if (n_tokens < 0 || n_kv_heads < 1 || head_dim < 1 || (n_tokens > 0 && (!cache || !src || !pos_ids))) return latch(BPDQ_ERR_ARG);
+    if (n_tokens < 0 || n_kv_heads < 1 || head_dim < 1 || max_seq_len < 1 || (n_tokens > 0 && (!cache || !src || !pos_ids)))
+        return latch(BPDQ_ERR_ARG);
     if (n_tokens == 0) return 0;
-    int rc = launch_kv_write(cache, src, pos_ids, n_tokens, n_kv_heads * head_dim, 1, (cudaStream_t)stream);
+    int rc = launch_kv_write(cache, src, pos_ids, n_tokens, n_kv_heads * head_dim, 1, max_seq_len, (cudaStream_t)stream);
     return rc ? latch(rc) : 0;
 }
 int bpd_kv_cache_write_cuda(float* cache, const float* src, const int32_t* pos_ids, int n_tokens, int n_kv_heads, int head_dim,
                             int max_seq_len, void* stream)
 {
-    (void)max_seq_len;
-    if (n_tokens < 0 || n_kv_heads < 1 || head_dim < 1 || (n_tokens > 0 && (!cache || !src || !pos_ids))) return latch(BPDQ_ERR_ARG);
+    if (n_tokens < 0 || n_kv_heads < 1 || head_dim < 1 || max_seq_len < 1 || (n_tokens > 0 && (!cache || !src || !pos_ids)))
+        return latch(BPDQ_ERR_ARG);
     if (n_tokens == 0) return 0;
-    int rc = launch_kv_write(cache, src, pos_ids, n_tokens, n_kv_heads * head_dim, 0, (cudaStream_t)stream);
+    int rc = launch_kv_write(cache, src, pos_ids, n_tokens, n_kv_heads * head_dim, 0, max_seq_len, (cudaStream_t)stream);
     return rc ? latch(rc) : 0;
 }
 int bpd_gqa_attn_cuda(const float* q, const void* k, const void* v, float* dst, int n_q_tokens, int n_kv, int n_q_heads,
@@ -573,7 +571,51 @@ int bpd_llama_block_cuda(float* x, const bpd_llama_layer_weights* lw, const bpd_
     if (rc) return latch(rc);
     if (!x || !lw || !pos_ids || !k_cache || !v_cache || !scratch1 || !scratch2 || !scratch3) return latch(BPDQ_ERR_ARG);
     rc = block_forward(x, lw, nullptr, cfg, pos_ids, n_tokens, kv_pos, k_cache, v_cache, scratch1, scratch2, scratch3, rope_freqs,
-                       false, false, nullptr, (cudaStream_t)stream);
+                       false, false, nullptr, (cudaStream_t)stream, nullptr);
+    return rc ? latch(rc) : 0;
+}
+
+// floats of the forward's own vectors (x and the reference's three scratch vectors)
+static void forward_floats(const bpd_llama_config* cfg, int n_tokens, size_t& nx, size_t& n1, size_t& n2)
+{
+    const int E = cfg->embed_dim, F = cfg->ffn_dim, H = cfg->n_heads, D = cfg->head_dim;
+    const size_t max_dim = (size_t)(E > F ? E : F), max_proj = (size_t)(H * D > F ? H * D : F);
+    nx = ((size_t)n_tokens * E + 63) / 64 * 64;
+    n1 = ((size_t)n_tokens * max_dim + 63) / 64 * 64;
+    n2 = ((size_t)n_tokens * max_proj + 63) / 64 * 64;
+}
+
+static int llama_forward(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights, const bpd_llama_weights* tiles,
+                         const bpd_llama_config* cfg, const int32_t* pos_ids, int kv_pos, void* k_cache, void* v_cache,
+                         float* logits_out, long long* token_out, Workspace* ws, cudaStream_t s)
+{
+    int rc = check_cfg(cfg, n_tokens, kv_pos);
+    if (rc) return latch(rc);
+    if (!token_ids || !weights || !pos_ids || !k_cache || !v_cache || !logits_out || !weights->token_embd ||
+        !weights->output_w || (cfg->n_layers > 0 && !weights->layers))
+        return latch(BPDQ_ERR_ARG);
+    const int E = cfg->embed_dim, D = cfg->head_dim, HKV = cfg->n_kv_heads;
+    size_t nx, n1, n2;
+    forward_floats(cfg, n_tokens, nx, n1, n2);
+    float* base = reinterpret_cast<float*>(scratch_take(ws, kScratchForward, (nx + n1 + 2 * n2) * sizeof(float), s, &rc));
+    if (!base) return rc;
+    float *x = base, *s1 = x + nx, *s2 = s1 + n1, *s3 = s2 + n2;
+    if ((rc = bpd_embed_lookup_q8_0_vocab_cuda(weights->token_embd, token_ids, x, n_tokens, E, cfg->vocab_size, s))) return rc;
+    const size_t kv_layer = (size_t)cfg->max_seq_len * HKV * D * (cfg->kv_cache_f16 ? 2 : 4);
+    // every block's last residual add also computes the norm that follows it: the next block's, or the output norm
+    for (int layer = 0; layer < cfg->n_layers; layer++) {
+        const bool last = layer + 1 == cfg->n_layers;
+        rc = block_forward(x, &weights->layers[layer], tiles && tiles->layers ? &tiles->layers[layer] : nullptr, cfg, pos_ids,
+                           n_tokens, kv_pos, (uint8_t*)k_cache + layer * kv_layer, (uint8_t*)v_cache + layer * kv_layer, s1, s2, s3,
+                           weights->rope_freqs, layer > 0, true,
+                           last ? weights->output_norm_w : weights->layers[layer + 1].attn_norm_w, s, ws);
+        if (rc) return latch(rc);
+    }
+    if (cfg->n_layers == 0) k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, weights->output_norm_w, s1, E, cfg->rms_eps);
+    if ((rc = product(weights->output_w, tiles ? tiles->output_w : nullptr, s1, logits_out, n_tokens, cfg->vocab_size, E, s, ws)))
+        return rc;
+    if (token_out) k_argmax_rows<<<n_tokens, 256, 0, s>>>(logits_out, token_out, cfg->vocab_size);
+    rc = check_cuda(cudaGetLastError());
     return rc ? latch(rc) : 0;
 }
 
@@ -582,36 +624,29 @@ int bpd_llama_forward_tiles_cuda(const int32_t* token_ids, int n_tokens, const b
                                  int kv_pos, void* k_cache, void* v_cache, float* logits_out, long long* token_out,
                                  void* stream)
 {
-    int rc = check_cfg(cfg, n_tokens, kv_pos);
-    if (rc) return latch(rc);
-    if (!token_ids || !weights || !pos_ids || !k_cache || !v_cache || !logits_out || !weights->token_embd ||
-        !weights->output_w || (cfg->n_layers > 0 && !weights->layers))
-        return latch(BPDQ_ERR_ARG);
-    cudaStream_t s = (cudaStream_t)stream;
-    const int E = cfg->embed_dim, F = cfg->ffn_dim, H = cfg->n_heads, D = cfg->head_dim, HKV = cfg->n_kv_heads;
-    const size_t max_dim = (size_t)(E > F ? E : F), max_proj = (size_t)(H * D > F ? H * D : F);
-    const size_t nx = ((size_t)n_tokens * E + 63) / 64 * 64, n1 = ((size_t)n_tokens * max_dim + 63) / 64 * 64,
-                 n2 = ((size_t)n_tokens * max_proj + 63) / 64 * 64;
-    float* base = forward_scratch(nx + n1 + 2 * n2);
-    if (!base) return latch(BPDQ_ERR_CUDA);
-    float *x = base, *s1 = x + nx, *s2 = s1 + n1, *s3 = s2 + n2;
-    if ((rc = bpd_embed_lookup_q8_0_cuda(weights->token_embd, token_ids, x, n_tokens, E, s))) return rc;
-    const size_t kv_layer = (size_t)cfg->max_seq_len * HKV * D * (cfg->kv_cache_f16 ? 2 : 4);
-    // every block's last residual add also computes the norm that follows it: the next block's, or the output norm
-    for (int layer = 0; layer < cfg->n_layers; layer++) {
-        const bool last = layer + 1 == cfg->n_layers;
-        rc = block_forward(x, &weights->layers[layer], tiles && tiles->layers ? &tiles->layers[layer] : nullptr, cfg, pos_ids,
-                           n_tokens, kv_pos, (uint8_t*)k_cache + layer * kv_layer, (uint8_t*)v_cache + layer * kv_layer, s1, s2, s3,
-                           weights->rope_freqs, layer > 0, true,
-                           last ? weights->output_norm_w : weights->layers[layer + 1].attn_norm_w, s);
-        if (rc) return latch(rc);
-    }
-    if (cfg->n_layers == 0) k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, weights->output_norm_w, s1, E, cfg->rms_eps);
-    if ((rc = product(weights->output_w, tiles ? tiles->output_w : nullptr, s1, logits_out, n_tokens, cfg->vocab_size, E, s)))
-        return rc;
-    if (token_out) k_argmax_rows<<<n_tokens, 256, 0, s>>>(logits_out, token_out, cfg->vocab_size);
-    rc = check_cuda(cudaGetLastError());
-    return rc ? latch(rc) : 0;
+    return llama_forward(token_ids, n_tokens, weights, tiles, cfg, pos_ids, kv_pos, k_cache, v_cache, logits_out, token_out,
+                         nullptr, (cudaStream_t)stream);
+}
+
+// The same with caller-owned scratch (bpdq_llama_forward_workspace_bytes; 16-byte aligned): no allocation, no
+// state shared with other calls.
+size_t bpdq_llama_forward_workspace_bytes(const bpd_llama_config* cfg, int n_tokens)
+{
+    if (!cfg || n_tokens < 1 || check_cfg(cfg, n_tokens, 0) == BPDQ_ERR_ARG) return 0;
+    size_t nx, n1, n2;
+    forward_floats(cfg, n_tokens, nx, n1, n2);
+    const int kmax = cfg->embed_dim > cfg->ffn_dim ? cfg->embed_dim : cfg->ffn_dim;
+    return (nx + n1 + 2 * n2) * sizeof(float) + 512 + gemm_q8_0_tiles_workspace(n_tokens, 0, kmax) + 256;
+}
+int bpd_llama_forward_ws_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
+                              const bpd_llama_weights* tiles, const bpd_llama_config* cfg, const int32_t* pos_ids, int kv_pos,
+                              void* k_cache, void* v_cache, float* logits_out, long long* token_out, void* workspace,
+                              size_t workspace_bytes, void* stream)
+{
+    if (!workspace || ((uintptr_t)workspace & 15)) return latch(workspace ? BPDQ_ERR_ALIGN : BPDQ_ERR_ARG);
+    Workspace ws = {(uint8_t*)workspace, workspace_bytes, 0};
+    return llama_forward(token_ids, n_tokens, weights, tiles, cfg, pos_ids, kv_pos, k_cache, v_cache, logits_out, token_out, &ws,
+                         (cudaStream_t)stream);
 }
 
 int bpd_llama_forward_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,

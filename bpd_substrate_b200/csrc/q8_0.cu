@@ -31,10 +31,11 @@ __global__ void __launch_bounds__(256) k_dequant_q8_0(const uint8_t* __restrict_
     }
 }
 
-// Rows gathered by token id, then dequantized: out[t][embed_dim].
+// Rows gathered by token id, then dequantized: out[t][embed_dim].  An id outside [0, vocab) reads nothing and
+// writes nothing (the row of `out` keeps its contents); the kernel records code 21 in the error word instead.
 __global__ void __launch_bounds__(256) k_embed_lookup_q8_0(const uint8_t* __restrict__ table,
                                                            const int32_t* __restrict__ ids, float* __restrict__ out,
-                                                           int n_tokens, int blocks_per_row)
+                                                           int n_tokens, int blocks_per_row, int vocab, int* __restrict__ err)
 {
     const long per_tok = (long)blocks_per_row * 8;
     const long n_items = per_tok * n_tokens;
@@ -42,8 +43,13 @@ __global__ void __launch_bounds__(256) k_embed_lookup_q8_0(const uint8_t* __rest
         const long t = it / per_tok, r = it - t * per_tok;
         const long b = r >> 3;
         const int q = (int)(r & 7);
+        const int id = __ldg(ids + t);
+        if (id < 0 || id >= vocab) {
+            if (r == 0 && err) atomicCAS(err, 0, 21);
+            continue;
+        }
         const unsigned short* blk = reinterpret_cast<const unsigned short*>(
-            table + ((size_t)__ldg(ids + t) * blocks_per_row + b) * BPDQ_Q80_BYTES);
+            table + ((size_t)id * blocks_per_row + b) * BPDQ_Q80_BYTES);
         const float s = f16_bits_to_f32(__ldg(blk));
         const unsigned short lo = __ldg(blk + 1 + 2 * q), hi = __ldg(blk + 2 + 2 * q);
         float4 o;
@@ -127,6 +133,57 @@ __global__ void __launch_bounds__(256) k_gemv_q8_0_generic(const uint8_t* __rest
     if (lane == 0) out[row] = acc;
 }
 
+// Q8_0 weights times activations that are ALREADY Q8_0 blocks (the dispatcher and tile kernels of
+// bench/bpd_gemm_q8_0_cpu.c:32-207 take them so): out[j * ldc + i] for weight row i (rows w_stride bytes
+// apart) and activation row j (a_stride bytes apart).  The reference keeps, per output cell, eight fp32 lanes:
+// lane q adds, block after block, (wd * ad) * (float)(sum of the four products of elements 4q..4q+3), multiply
+// and add rounded separately; the lanes are then summed as (c_q + c_{q+4}), (s_0 + s_2, s_1 + s_3), t_0 + t_1
+// (bench/bpd_gemm_q8_0_cpu.c:44-85).  Eight threads per cell play those lanes, in that order: the reference's
+// AVX result bit for bit.  Rows are 2-byte aligned only.
+__global__ void __launch_bounds__(256) k_qmatmul_q8_0_q8_0(const uint8_t* __restrict__ W, const uint8_t* __restrict__ Xq,
+                                                           float* __restrict__ out, int m_weight, int m_tokens, int nbk,
+                                                           long w_stride, long a_stride, int ldc)
+{
+    const long n_cells = (long)m_weight * m_tokens;
+    const long n_items = (n_cells * 8 + 31) / 32 * 32;      // whole warps, so that the shuffles see all lanes
+    for (long it = (long)blockIdx.x * blockDim.x + threadIdx.x; it < n_items; it += (long)gridDim.x * blockDim.x) {
+        const long cell = it >> 3;
+        const int q = (int)(it & 7);
+        const bool live = cell < n_cells;
+        const int j = live ? (int)(cell / m_weight) : 0, i = live ? (int)(cell - (long)j * m_weight) : 0;
+        const uint8_t* wr = W + (size_t)i * w_stride;
+        const uint8_t* ar = Xq + (size_t)j * a_stride;
+        float c = 0.0f;
+        if (live) {
+            for (int b = 0; b < nbk; b++) {
+                const unsigned short* wb = reinterpret_cast<const unsigned short*>(wr + (size_t)b * BPDQ_Q80_BYTES);
+                const unsigned short* ab = reinterpret_cast<const unsigned short*>(ar + (size_t)b * BPDQ_Q80_BYTES);
+                const uint32_t ww = __ldg(wb + 1 + 2 * q) | ((uint32_t)__ldg(wb + 2 + 2 * q) << 16);
+                const uint32_t aa = __ldg(ab + 1 + 2 * q) | ((uint32_t)__ldg(ab + 2 + 2 * q) << 16);
+                const float scale = __fmul_rn(f16_bits_to_f32(__ldg(wb)), f16_bits_to_f32(__ldg(ab)));
+                c = __fadd_rn(__fmul_rn(scale, (float)dp4a_ss(ww, aa, 0)), c);
+            }
+        }
+        c = __fadd_rn(c, __shfl_xor_sync(0xFFFFFFFFu, c, 4));
+        c = __fadd_rn(c, __shfl_xor_sync(0xFFFFFFFFu, c, 2));
+        c = __fadd_rn(c, __shfl_xor_sync(0xFFFFFFFFu, c, 1));
+        if (live && q == 0) out[(size_t)j * ldc + i] = c;
+    }
+}
+
+static int qmatmul_q8_0_q8_0(const uint8_t* W, const uint8_t* Xq, float* out, int m_weight, int m_tokens, int nbk, long w_stride,
+                             long a_stride, int ldc, cudaStream_t s)
+{
+    if (m_weight < 0 || m_tokens < 0 || nbk <= 0 || ldc < m_weight || w_stride < 0 || a_stride < 0) return latch(BPDQ_ERR_ARG);
+    if (m_weight == 0 || m_tokens == 0) return 0;
+    if (!W || !Xq || !out) return latch(BPDQ_ERR_ARG);
+    if (((uintptr_t)W & 1) || ((uintptr_t)Xq & 1) || (w_stride & 1) || (a_stride & 1) || ((uintptr_t)out & 3)) return latch(BPDQ_ERR_ALIGN);
+    const long want = ((long)m_weight * m_tokens * 8 + 255) / 256, cap = (long)sm_count() * 16;
+    k_qmatmul_q8_0_q8_0<<<(unsigned)(want < cap ? want : cap), 256, 0, s>>>(W, Xq, out, m_weight, m_tokens, nbk, w_stride, a_stride, ldc);
+    int rc = check_cuda(cudaGetLastError());
+    return rc ? latch(rc) : 0;
+}
+
 static int grid_for(long items, int threads = 256)
 {
     long want = (items + threads - 1) / threads, cap = (long)sm_count() * 8;
@@ -138,6 +195,8 @@ static int grid_for(long items, int threads = 256)
 using namespace bpdq;
 
 extern "C" {
+
+int bpd_qmatmul_q8_0_dispatch_cuda(const uint8_t* Wq, const uint8_t* Xq, float* out, int m_weight, int m_tokens, int K, void* stream);
 
 int bpd_dequant_q8_0_cuda(const uint8_t* raw, float* out, size_t n_blocks, void* stream)
 {
@@ -188,17 +247,60 @@ int bpd_qmatmul_q8_0_cuda(const uint8_t* W, const float* X, float* out, int M, i
     return 0;
 }
 
-int bpd_embed_lookup_q8_0_cuda(const uint8_t* table, const int32_t* ids, float* out, int n_tokens, int embed_dim,
-                               void* stream)
+int bpd_embed_lookup_q8_0_vocab_cuda(const uint8_t* table, const int32_t* ids, float* out, int n_tokens, int embed_dim,
+                                     int vocab_size, void* stream)
 {
-    if (n_tokens < 0 || embed_dim <= 0 || (embed_dim % 32) != 0) return latch(BPDQ_ERR_ARG);
+    if (n_tokens < 0 || embed_dim <= 0 || (embed_dim % 32) != 0 || vocab_size < 1) return latch(BPDQ_ERR_ARG);
     if (n_tokens == 0) return 0;
     if (!table || !ids || !out) return latch(BPDQ_ERR_ARG);
     if (((uintptr_t)table & 1) || ((uintptr_t)out & 15)) return latch(BPDQ_ERR_ALIGN);
     const long items = (long)n_tokens * (embed_dim / 4);
-    k_embed_lookup_q8_0<<<grid_for(items), 256, 0, (cudaStream_t)stream>>>(table, ids, out, n_tokens, embed_dim / 32);
+    k_embed_lookup_q8_0<<<grid_for(items), 256, 0, (cudaStream_t)stream>>>(table, ids, out, n_tokens, embed_dim / 32, vocab_size,
+                                                                            device_error_flag());
     return check_cuda(cudaGetLastError());
 }
+// The reference's signature has no table size (bench/bpd_cpu.c:4002): only negative ids can be refused.
+int bpd_embed_lookup_q8_0_cuda(const uint8_t* table, const int32_t* ids, float* out, int n_tokens, int embed_dim,
+                               void* stream)
+{
+    return bpd_embed_lookup_q8_0_vocab_cuda(table, ids, out, n_tokens, embed_dim, 0x7FFFFFFF, stream);
+}
+
+// bench/bpd_cpu.c:4428-4459  bpd_qmatmul_q8_0_llamafile_cpu(W, X, out, m_weight, m_tokens, K): fp32 activations,
+// out[token * m_weight + weight_row]
+int bpd_qmatmul_q8_0_llamafile_cuda(const uint8_t* W, const float* X, float* out, int m_weight, int m_tokens, int K, void* stream)
+{
+    if (m_weight < 0 || m_tokens < 0 || K <= 0 || (K % 32) != 0) return latch(BPDQ_ERR_ARG);
+    if (m_weight == 0 || m_tokens == 0) return 0;
+    if (!W || !X || !out) return latch(BPDQ_ERR_ARG);
+    // as the reference does: quantize the activation rows to Q8_0 (library-owned scratch of this stream), then the dispatcher
+    const size_t row = (size_t)(K / 32) * BPDQ_Q80_BYTES;
+    int rc = 0;
+    uint8_t* xq = scratch_take(nullptr, kScratchQ80Acts, (size_t)m_tokens * row, (cudaStream_t)stream, &rc);
+    if (!xq) return rc;
+    if ((rc = bpd_quant_q8_0_cuda(X, xq, (size_t)m_tokens * K, stream))) return rc;
+    return bpd_qmatmul_q8_0_dispatch_cuda(W, xq, out, m_weight, m_tokens, K, stream);
+}
+// bench/bpd_gemm_q8_0_cpu.c:159-207  bpd_qmatmul_q8_0_dispatch_cpu(Wq, Xq, out, m_weight, m_tokens, K): activations
+// already quantized to Q8_0 rows [m_tokens][K/32][34]
+int bpd_qmatmul_q8_0_dispatch_cuda(const uint8_t* Wq, const uint8_t* Xq, float* out, int m_weight, int m_tokens, int K, void* stream)
+{
+    if (K <= 0 || (K % 32) != 0) return latch(BPDQ_ERR_ARG);
+    const long row = (long)(K / 32) * BPDQ_Q80_BYTES;
+    return qmatmul_q8_0_q8_0(Wq, Xq, out, m_weight, m_tokens, K / 32, row, row, m_weight, (cudaStream_t)stream);
+}
+// bench/bpd_gemm_q8_0_cpu.c:32-157  bpd_gemm_q8_0_{RM}_{RN}_cpu(W_tile, B_tile, k, w_stride, a_stride, out, ldc): one
+// tile of RM weight rows x RN activation rows over k blocks, out[j * ldc + i]
+#define BPDQ_Q8_0_TILE(RM, RN)                                                                                                  \
+    int bpd_gemm_q8_0_##RM##_##RN##_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride,       \
+                                         float* out, int ldc, void* stream)                                                     \
+    {                                                                                                                           \
+        return qmatmul_q8_0_q8_0(W_tile, B_tile, out, RM, RN, k, w_stride, a_stride, ldc, (cudaStream_t)stream);               \
+    }
+BPDQ_Q8_0_TILE(1, 1) BPDQ_Q8_0_TILE(1, 2) BPDQ_Q8_0_TILE(1, 4)
+BPDQ_Q8_0_TILE(2, 1) BPDQ_Q8_0_TILE(2, 2) BPDQ_Q8_0_TILE(2, 4)
+BPDQ_Q8_0_TILE(4, 1) BPDQ_Q8_0_TILE(4, 2) BPDQ_Q8_0_TILE(4, 4)
+#undef BPDQ_Q8_0_TILE
 
 // gpu_vecmat-shaped: (activations, weights, out, k, n)  -- lib/kernel_templates_llama.pl:147-158
 void gpu_vecmat_q8_0(const float* a, const uint8_t* wq, float* c, int k, int n)

@@ -7,6 +7,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 namespace bpdq {
 
@@ -60,6 +61,70 @@ int* device_error_flag()
 }
 
 Tuning& tuning() { return g_tuning; }
+
+// ---- library-owned scratch: one block per (device, stream, purpose), grown by replacement
+namespace {
+struct ScratchBlock {
+    int dev, kind;
+    cudaStream_t stream;
+    uint8_t* ptr;
+    size_t cap;
+};
+std::mutex g_scratch_mutex;
+std::vector<ScratchBlock> g_scratch;     // live blocks
+std::vector<void*> g_scratch_retired;    // replaced blocks: kept allocated, earlier launches and graphs may use them
+}  // namespace
+
+uint8_t* scratch_take(Workspace* ws, int kind, size_t bytes, cudaStream_t s, int* status)
+{
+    *status = 0;
+    if (bytes == 0) bytes = 16;
+    if (ws) {
+        const size_t at = (ws->used + 255) / 256 * 256;
+        const size_t pad = (256 - ((uintptr_t)ws->base & 255)) & 255;   // the carved pieces are 256-byte aligned
+        if (!ws->base || at + pad + bytes > ws->bytes) {
+            *status = latch(BPDQ_ERR_RANGE);
+            return nullptr;
+        }
+        ws->used = at + bytes;
+        return ws->base + pad + at;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        *status = check_cuda(e);
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    ScratchBlock* blk = nullptr;
+    for (auto& b : g_scratch)
+        if (b.dev == dev && b.kind == kind && b.stream == s) { blk = &b; break; }
+    if (blk && blk->cap >= bytes) return blk->ptr;
+    // a new or larger block is an allocation: not while the stream records a graph
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess) (void)cudaGetLastError();
+    if (cap != cudaStreamCaptureStatusNone) {
+        *status = latch(BPDQ_ERR_CAPTURE);
+        return nullptr;
+    }
+    size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+    if (blk && want < 2 * blk->cap) want = 2 * blk->cap;
+    void* p = nullptr;
+    e = cudaMalloc(&p, want);
+    if (e != cudaSuccess && want > bytes) e = cudaMalloc(&p, want = bytes);
+    if (e != cudaSuccess) {
+        *status = check_cuda(e);
+        return nullptr;
+    }
+    if (blk) {
+        g_scratch_retired.push_back(blk->ptr);
+        blk->ptr = (uint8_t*)p;
+        blk->cap = want;
+    } else {
+        g_scratch.push_back({dev, kind, s, (uint8_t*)p, want});
+    }
+    return (uint8_t*)p;
+}
 
 static void* dev_alloc(size_t bytes)
 {
@@ -204,6 +269,15 @@ int bpdq_graph_launch(void* exec, void* stream)
 }
 void bpdq_graph_destroy(void* exec) { if (exec) check_cuda(cudaGraphExecDestroy((cudaGraphExec_t)exec)); }
 int bpdq_set_device(int dev) { return check_cuda(cudaSetDevice(dev)); }
+// Free and total device memory of the current device as the driver reports them.
+int bpdq_mem_info(size_t* free_bytes, size_t* total_bytes)
+{
+    size_t f = 0, t = 0;
+    int rc = check_cuda(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
+    return rc;
+}
 int bpdq_l2_bytes(void)
 {
     int dev = 0, n = 0;

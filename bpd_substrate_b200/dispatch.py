@@ -35,8 +35,9 @@ class LayerSet:
       share a launch and the first member's activation vector;
     * ``"batched"``  -- the seven independent products of a layer go to the device as ONE
       launch (``bpd_qmatmul_q4k_q8k_batch_cuda``), each with its own activation vector;
-    * ``"persistent"`` -- all products of the step as ONE persistent launch whose weight ring never
-      drains between layers (``bpdq_gemv_stream_run``), after one launch that quantizes all vectors.
+    * ``"persistent"`` -- the products of the step (or of a range of its layers) as persistent launches of up
+      to 128 products each, whose weight ring never drains between layers (``bpdq_gemv_stream_run_ready``),
+      each after one launch that quantizes its vectors.
     """
 
     def __init__(self, shapes=synth.MISTRAL_LAYER, n_layers=32, seed=2000, row_shard=(0, 1), lib=None,
@@ -84,11 +85,15 @@ class LayerSet:
         self.graph = {}
         self._keep = []
         self.ws = None             # scratch for quantized activations (batched schedule)
-        self.stream_plan = self.stream_ws = None      # plan and scratch of the persistent schedule
+        self.stream_plans = {}     # (first, last) -> (plan, scratch) of the persistent schedule
         self.copy_streams = self.copy_events = None   # second and third stream of step_host
         capi.check(lib.bpdq_last_status(), "LayerSet setup")
 
     # ---- sizes
+    def multi_token_kernel(self, schedule):
+        """Name of the kernel that does the work when every product has several activation rows."""
+        return "k_gemm_q4k_q8k_mma / k_gemm_q4k_q8k_tc5 / k_gemv_q4k_q8k (one launch per matrix, by token count and size)"
+
     def algorithmic_bytes(self):
         """Quantized weights + fp32 activations in + fp32 outputs out, per step."""
         return self.n_layers * sum(synth.gemv_bytes_q4k(rows, cols, self.tokens) for _, rows, cols in self.local)
@@ -97,7 +102,8 @@ class LayerSet:
         if self.tokens > 1:
             return 2 * self.n_layers * len(self.local)   # activation quantizer + GEMM kernel per matrix
         if schedule == "persistent":
-            return 2                      # one quantizer launch + one persistent GEMV launch per step
+            # quantizer + persistent GEMV kernel per 128 products
+            return self.lib.bpdq_gemv_stream_launches(self._stream_plan(0, self.n_layers)[0])
         if schedule == "batched":
             return 2 * self.n_layers      # activation quantizer + GEMV kernel per layer
         return self.n_layers * len(GROUPS_DECODE if schedule == "grouped" else GROUPS_NONE)
@@ -115,7 +121,7 @@ class LayerSet:
         self._keep.append((wp, op, mp))
         return n, wp, op, mp, self.d_x + self.x_off[idx[0]], self.local[members[0]][2]
 
-    def enqueue_step(self, schedule="grouped", stream=None, layers=None):
+    def enqueue_step(self, schedule="grouped", stream=None, layers=None, tag=None):
         """Queues one decode step's GEMVs on ``stream`` (default: this object's stream); ``layers`` =
         (first, last+1) restricts it to a range of layers."""
         lib, s = self.lib, (stream if stream is not None else self.stream)
@@ -131,22 +137,9 @@ class LayerSet:
                                                         None, s), "GEMM launch")
             return
         if schedule == "persistent":
-            if layers is not None:
-                raise ValueError("the persistent schedule covers the whole step")
-            if self.stream_plan is None:
-                nm = len(self.local)
-                descs = (capi.GemvDesc * (nm * self.n_layers))()
-                for layer in range(self.n_layers):
-                    for m, (_, rows, cols) in enumerate(self.local):
-                        i = layer * nm + m
-                        descs[i] = capi.GemvDesc(self.weights[layer][m], self.d_x + self.x_off[i],
-                                                 self.d_out + self.o_off[i], rows, cols)
-                self.stream_ws_bytes = lib.bpdq_batch_workspace_bytes(len(descs), descs)
-                self.stream_ws = lib.bpdq_alloc(self.stream_ws_bytes)
-                self.stream_plan = lib.bpdq_gemv_stream_create(len(descs), descs, self.stream_ws, self.stream_ws_bytes)
-                if not self.stream_plan:
-                    raise capi.BpdqError(f"stream plan rejected (status {lib.bpdq_last_status()})")
-            capi.check(lib.bpdq_gemv_stream_run(self.stream_plan, s), "persistent GEMV launch")
+            # the step's activations are all on the device before its first launch (independent products): the
+            # quantizer may read them ahead of stream order
+            capi.check(lib.bpdq_gemv_stream_run_ready(self._stream_plan(first, last, tag)[0], s), "persistent GEMV launch")
             return
         if schedule == "batched":
             nm = len(self.local)
@@ -177,6 +170,36 @@ class LayerSet:
                     rc = lib.bpd_qmatmul_q4k_q8k_multi_cuda(n, wp, op, mp, x, K, s)
                 capi.check(rc, "GEMV launch")
 
+    def _stream_plan(self, first, last, tag=None):
+        """Plan (and record scratch) of the persistent schedule for layers [first, last); made on first use.  Peer
+        targets registered at that moment are part of the plan, so plans made under different registrations carry
+        different tags."""
+        key = (first, last, tag)
+        if key not in self.stream_plans:
+            lib, nm = self.lib, len(self.local)
+            descs = (capi.GemvDesc * (nm * (last - first)))()
+            for layer in range(first, last):
+                for m, (_, rows, cols) in enumerate(self.local):
+                    i = layer * nm + m
+                    descs[i - first * nm] = capi.GemvDesc(self.weights[layer][m], self.d_x + self.x_off[i],
+                                                          self.d_out + self.o_off[i], rows, cols)
+            ws_bytes = lib.bpdq_batch_workspace_bytes(len(descs), descs)
+            ws = lib.bpdq_alloc(ws_bytes)
+            plan = lib.bpdq_gemv_stream_create(len(descs), descs, ws, ws_bytes)
+            if not plan:
+                lib.bpdq_free(ws)
+                raise capi.BpdqError(f"stream plan rejected (status {lib.bpdq_last_status()})")
+            self.stream_plans[key] = (plan, ws)
+        return self.stream_plans[key]
+
+    def drop_stream_plans(self):
+        """Forgets the persistent schedule's plans (they are rebuilt on next use, e.g. after the peer targets changed)."""
+        self.lib.bpdq_stream_sync(self.stream)
+        for plan, ws in self.stream_plans.values():
+            self.lib.bpdq_gemv_stream_destroy(plan)
+            self.lib.bpdq_free(ws)
+        self.stream_plans = {}
+
     def capture(self, schedule="grouped", layers=None, tag=None):
         """Records a step (or a range of its layers) into a CUDA graph (launch gaps disappear, PDL
         edges are kept).  tag: tells apart recordings of the same step made under different library
@@ -186,10 +209,10 @@ class LayerSet:
             key = (key, "tag", tag)
         if key not in self.graph:
             lib = self.lib
-            self.enqueue_step(schedule, layers=layers)     # warm-up outside capture (attributes, caches)
+            self.enqueue_step(schedule, layers=layers, tag=tag)     # warm-up outside capture (attributes, caches)
             capi.check(lib.bpdq_stream_sync(self.stream))
             capi.check(lib.bpdq_graph_begin(self.stream), "graph capture")
-            self.enqueue_step(schedule, layers=layers)
+            self.enqueue_step(schedule, layers=layers, tag=tag)
             g = lib.bpdq_graph_end(self.stream)
             if not g:
                 raise capi.BpdqError(f"graph capture failed (status {lib.bpdq_last_status()})")
@@ -208,18 +231,22 @@ class LayerSet:
         end = self.o_off[last * nm] if last < self.n_layers else self.o_bytes
         return begin, end - begin
 
-    def step_host(self, x_host_ptr, out_host_ptr, schedule="grouped", chunks=4):
+    def step_host(self, x_host_ptr, out_host_ptr, schedule="grouped", chunks=4, tag=None, after=None):
         """One step from HOST buffers (pinned: bpdq_host_alloc): activations in, GEMVs, outputs back, wait.
 
         The step is cut into ``chunks`` ranges of layers; the activations of a range are copied in on a
         second stream and its outputs copied back on a third while other ranges compute, so that only
-        the first range's copy-in and the last range's copy-out are not hidden.  ``chunks=1`` (and the
-        persistent schedule, which is one launch) runs copy, step, copy in sequence on one stream."""
+        the first range's copy-in and the last range's copy-out are not hidden.  ``chunks=1`` runs copy,
+        step, copy in sequence on one stream.  ``tag``: which recording of the step to replay (see capture);
+        ``after``: called when all launches are queued on self.stream and before the wait, e.g. to queue the
+        flag exchange of a row-sharded step."""
         lib = self.lib
-        n = 1 if schedule == "persistent" else max(1, min(chunks, self.n_layers))
+        n = max(1, min(chunks, self.n_layers))
         if n == 1:
             capi.check(lib.bpdq_h2d_async(self.d_x, x_host_ptr, self.x_bytes, self.stream))
-            self.step(schedule)
+            self.step(schedule, tag=tag)
+            if after is not None:
+                after()
             capi.check(lib.bpdq_d2h_async(out_host_ptr, self.d_out, self.o_bytes, self.stream))
             capi.check(lib.bpdq_stream_sync(self.stream))
             return
@@ -235,13 +262,21 @@ class LayerSet:
             capi.check(lib.bpdq_event_record(self.copy_events[c][0], s_in))
         for c, (first, last) in enumerate(ranges):
             capi.check(lib.bpdq_stream_wait_event(self.stream, self.copy_events[c][0]))
-            self.step(schedule, (first, last))
+            self.step(schedule, (first, last), tag)
             capi.check(lib.bpdq_event_record(self.copy_events[c][1], self.stream))
             capi.check(lib.bpdq_stream_wait_event(s_out, self.copy_events[c][1]))
             begin, nbytes = self.layer_output_range(first, last)
             capi.check(lib.bpdq_d2h_async(out_host_ptr + begin, self.d_out + begin, nbytes, s_out))
+        if after is not None:
+            after()
         capi.check(lib.bpdq_stream_sync(s_out))
         capi.check(lib.bpdq_stream_sync(self.stream))
+
+    def host_ranges(self, chunks):
+        """The ranges of layers that step_host(chunks=...) runs as separate recordings."""
+        n = max(1, min(chunks, self.n_layers))
+        bounds = [self.n_layers * c // n for c in range(n + 1)]
+        return [None] if n == 1 else [(bounds[c], bounds[c + 1]) for c in range(n)]
 
     def layer_input_range(self, first, last):
         """(byte offset, bytes) of the activations of layers [first, last) in the input arena."""
@@ -264,11 +299,11 @@ class LayerSet:
 
     def activation_slice(self, x_all, layer, m):
         i = layer * len(self.local) + m
-        return x_all[self.x_off[i] // 4: self.x_off[i] // 4 + self.local[m][2]]
+        return x_all[self.x_off[i] // 4: self.x_off[i] // 4 + self.tokens * self.local[m][2]]
 
     def output_slice(self, out_all, layer, m):
         i = layer * len(self.local) + m
-        return out_all[self.o_off[i] // 4: self.o_off[i] // 4 + self.local[m][1]]
+        return out_all[self.o_off[i] // 4: self.o_off[i] // 4 + self.tokens * self.local[m][1]]
 
     def close(self):
         lib = self.lib
@@ -288,10 +323,7 @@ class LayerSet:
                 lib.bpdq_event_destroy(a)
                 lib.bpdq_event_destroy(b)
             self.copy_streams = None
-        if self.stream_plan:
-            lib.bpdq_gemv_stream_destroy(self.stream_plan)
-            lib.bpdq_free(self.stream_ws)
-            self.stream_plan = None
+        self.drop_stream_plans()
         if self.ws is not None:
             lib.bpdq_free(self.ws)
         if self._own_out:
@@ -366,6 +398,10 @@ class DecodeChain:
 
     def norm_ptr(self, layer, which):
         return self.d_norm + (layer * 2 + which) * self.hidden * 4
+
+    def multi_token_kernel(self, schedule):
+        """Name of the kernel that does the work when every product has several activation rows."""
+        return "k_gemm_q4k_q8k_mma / k_gemm_q4k_q8k_tc5 / k_gemv_q4k_q8k (one launch per matrix, by token count and size)"
 
     def algorithmic_bytes(self):
         """Quantized weights + fp32 vector in + fp32 vector out of every product, per token."""

@@ -100,14 +100,30 @@ class PeerExchange:
         capi.check(self.lib.bpdq_peer_signal_wait(self._slots, self.local_flags, self.world, self.step_no, stream),
                    "bpdq_peer_signal_wait")
 
-    def close(self):
-        self.lib.bpdq_set_peer_outputs(None, 0, 0, None)
+    def close(self, dist=None, stream=None):
+        """Collective when ``dist`` is given: every rank finishes its own work, then all ranks agree that nobody will
+        store into a peer's buffer any more, and only then are the mappings closed and the buffer freed.  Graphs
+        recorded while targets were registered keep storing to those addresses: destroy them before close().  If a rank
+        reports a failed wait (status -4: a peer may still be running and storing), nothing is unmapped or freed on any
+        rank -- the memory is left to the end of the process rather than pulled away under a peer's stores."""
+        lib = self.lib
+        lib.bpdq_set_peer_outputs(None, 0, 0, None)
+        safe = True
+        if dist is not None:
+            ok = lib.bpdq_stream_sync(stream) == 0 and lib.bpdq_last_status() == 0
+            verdicts = [None] * self.world
+            dist.all_gather_object(verdicts, bool(ok))      # also a barrier: every rank's launches have completed
+            safe = all(verdicts)
+        if not safe:
+            self._imported, self.base = [], None
+            return False
         for p in self._imported:
-            self.lib.bpdq_ipc_close(p)
+            lib.bpdq_ipc_close(p)
         self._imported = []
         if self.base:
-            self.lib.bpdq_free(self.base)
+            lib.bpdq_free(self.base)
             self.base = None
+        return True
 
 
 def _selftest():
@@ -156,8 +172,8 @@ def _selftest():
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
         print("peer exchange selftest:", "ok" if int(flag.item()) else "MISMATCH", f"({world} ranks, 6 steps)", flush=True)
-    ex.close()
-    ls.close()
+    ls.close()             # destroys the graphs recorded with peer targets
+    ex.close(dist)
     dist.destroy_process_group()
     return 0 if int(flag.item()) else 1
 

@@ -32,7 +32,8 @@ extern "C" {
 #define BPDQ_STATUS_ERR_ARG (-1)     /* null pointer, negative size, K not a block multiple */
 #define BPDQ_STATUS_ERR_ALIGN (-2)   /* pointer not aligned as the kernel needs (16 B for weights) */
 #define BPDQ_STATUS_ERR_RANGE (-3)   /* shape beyond what the kernel supports */
-#define BPDQ_STATUS_ERR_DEVICE (-4)  /* a kernel gave up on a bounded wait */
+#define BPDQ_STATUS_ERR_DEVICE (-4)  /* a kernel gave up on a bounded wait, or skipped an out-of-range index */
+#define BPDQ_STATUS_ERR_CAPTURE (-5) /* library-owned scratch would have to grow while the stream is being captured */
 #define BPDQ_STATUS_ERR_CUDA (-1000) /* minus the cudaError_t value */
 
 /* ---- library state (additive; the reference keeps none) ------------------------------ */
@@ -41,15 +42,29 @@ void* bpdq_get_stream(void);
 int bpdq_last_status(void);                /* first error since the last clear (synchronizes) */
 int bpdq_device_error_word(void);
 void bpdq_clear_status(void);
-/* GEMV launch tuning: max bytes per weight tile, ring slots per warp group, CTAs per SM,
- * consumer warps per CTA, programmatic dependent launch on/off.  <=0 (pdl: <0) keeps a field. */
+/* Launch tuning, process-wide (set it once, before the launches it should apply to; not per stream): max bytes
+ * per weight tile of the GEMV ring, ring slots per warp, CTAs per SM, consumer warps per CTA, programmatic
+ * dependent launch on/off.  <=0 (pdl: <0) keeps a field. */
 void bpdq_set_tuning(int tile_bytes, int slots, int ctas_per_sm, int warps, int pdl);
 /* dequant launch tuning: variant 0 = four outputs per thread, 1 = eight; CTAs per SM of the grid */
 void bpdq_set_dequant_tuning(int variant, int ctas_per_sm);
 int bpdq_sm_count(void);
-/* tuning aid: the next `launches` GEMV launches write 8 global-timer stamps (ns) per CTA */
-void bpdq_debug_trace(void* dev_buf, size_t stride_u64, int launches);
-void bpdq_debug_trace_tc5(void* dev_buf);   /* 5 x 32 stamps of CTA 0 of the tcgen05 kernel */
+
+/* ---- scratch memory of the compute entries -------------------------------------------------
+ * Three kinds of entry need device scratch beyond their inputs and outputs (quantized activations,
+ * split-K partial sums, the forward pass's vectors): the many-token products bpd_qmm_q4k_q8k_cuda /
+ * _mma_cuda / _tc5_cuda / gpu_matmul_q4k, bpd_qmatmul_q8_0_tiles_cuda and bpd_qmatmul_q8_0_llamafile_cuda,
+ * and bpd_llama_forward*_cuda.  Each has two forms:
+ *   *_ws_cuda(..., workspace, workspace_bytes, stream): the caller owns the scratch (16-byte aligned, at
+ *     least the matching *_workspace_bytes()).  Nothing is allocated and no state is shared between calls:
+ *     calls on different streams may overlap if their workspaces differ; BPDQ_STATUS_ERR_RANGE if too small.
+ *   the plain form: the library keeps one block per (device, stream, purpose).  Calls on one stream are ordered
+ *     by the stream; calls on different streams use different blocks.  A block grows by replacement the first
+ *     time a larger size is asked for on that stream (cudaMalloc, which synchronizes the device); a block that
+ *     was handed out is never freed before the process ends, so launches in flight and captured graphs that
+ *     hold its address stay valid.  While a stream is being captured a block cannot grow: the call returns
+ *     BPDQ_STATUS_ERR_CAPTURE and launches nothing -- make one call of that size on the stream before the
+ *     capture (a warm-up run), or use the *_ws_cuda form. */
 
 /* ---- device memory helpers (additive, size_t) ------------------------------------------ */
 void* bpdq_alloc(size_t bytes);
@@ -78,6 +93,7 @@ void* bpdq_graph_end(void* stream);        /* -> executable graph handle, NULL o
 int bpdq_graph_launch(void* graph, void* stream);
 void bpdq_graph_destroy(void* graph);
 int bpdq_set_device(int device);
+int bpdq_mem_info(size_t* free_bytes, size_t* total_bytes);   /* cudaMemGetInfo of the current device */
 int bpdq_l2_bytes(void);
 
 /* ---- reference memory helpers, name for name ------------------------------------------- */
@@ -176,14 +192,21 @@ size_t bpdq_batch_workspace_bytes(int n, const bpdq_gemv_desc* descs);
  *    must be serialized by the caller. */
 int bpd_qmatmul_q4k_q8k_batch_static_cuda(int n, const bpdq_gemv_desc* descs, void* stream);
 size_t bpdq_batch_static_capacity(void);
-/* Any number of independent products as ONE persistent launch (plus one launch that quantizes all
- * their activation vectors): the weights of all products stream through the shared-memory ring without
- * a launch boundary in between.  bpdq_gemv_stream_create plans the products (same descriptors as the batched
- * entries), lays the activation records out in `workspace` (bpdq_batch_workspace_bytes(n, descs) bytes,
- * 16-byte aligned, must stay allocated) and uploads the plan (it allocates device memory); bpdq_gemv_stream_run
- * launches it, stream-ordered like any launch; same bits as the batched entries. */
+/* Any number of independent products as ONE persistent launch per 128 products (plus one launch that quantizes
+ * their activation vectors): the weights of all products stream through the shared-memory ring without a launch
+ * boundary in between, every consumer warp refilling its own ring slots, and the activation records are swapped
+ * through two shared-memory buffers phase by phase without any CTA-wide barrier.  bpdq_gemv_stream_create plans
+ * the products (same descriptors as the batched entries), lays the activation records out in `workspace`
+ * (bpdq_batch_workspace_bytes(n, descs) bytes, 16-byte aligned, must stay allocated) and uploads the plan (it
+ * allocates device memory; peer targets registered with bpdq_set_peer_outputs are read here);
+ * bpdq_gemv_stream_run launches it, stream-ordered like any launch; bpdq_gemv_stream_run_ready is for callers who
+ * can promise that every activation vector is complete when the call is made (nothing in flight writes them): the
+ * quantizer then reads them under the tail of the launch ahead.  Same bits as the batched entries.
+ * bpdq_gemv_stream_launches: kernel launches one run makes. */
 void* bpdq_gemv_stream_create(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes);   /* NULL on error */
 int bpdq_gemv_stream_run(void* handle, void* stream);
+int bpdq_gemv_stream_run_ready(void* handle, void* stream);
+int bpdq_gemv_stream_launches(void* handle);
 void bpdq_gemv_stream_destroy(void* handle);
 
 /* ---- Decode glue.  Replaces, around the products of a decoder layer, the separate elementwise
@@ -231,11 +254,21 @@ void bpdq_chain_destroy(void* chain);
  * [tokens][K/256]; subdots (may be NULL): int32 [M][K/256][8], token 0's exact sub-block dots */
 int bpd_qmm_q4k_q8k_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,
                          int xsrc, int32_t* subdots, void* stream);
+/* the same with caller-owned scratch (see "scratch memory" above) */
+size_t bpdq_qmm_q4k_q8k_workspace_bytes(int tokens, int M, int K);
+int bpd_qmm_q4k_q8k_ws_cuda(const uint8_t* qweight, const void* x, float* out, int tokens, int M, int K, int layout,
+                            int xsrc, int32_t* subdots, void* workspace, size_t workspace_bytes, void* stream);
 /* the int8 tensor-core kernel behind bpd_qmm_q4k_q8k_cuda for more than 8 tokens, callable at any
  * token count: out[tokens][M], X float [tokens][K], nibble order of bench/bpd_quant.c:68-72 */
 int bpd_qmm_q4k_q8k_mma_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream);
 /* the same product on tcgen05 tensor cores with TMEM accumulators (M >= 128 weight rows) */
 int bpd_qmm_q4k_q8k_tc5_cuda(const uint8_t* qweight, const float* X, float* out, int tokens, int M, int K, void* stream);
+/* checking forms of the two tensor-core kernels: besides out they store, for every (token, row, super-block),
+ * the exact int32 pair (isum, msum) the fp32 scales are applied to; sb_ints is int32 [tokens][M][K/256][2] */
+int bpd_qmm_q4k_q8k_mma_ints_cuda(const uint8_t* qweight, const float* X, float* out, int32_t* sb_ints, int tokens, int M, int K,
+                                  void* stream);
+int bpd_qmm_q4k_q8k_tc5_ints_cuda(const uint8_t* qweight, const float* X, float* out, int32_t* sb_ints, int tokens, int M, int K,
+                                  void* stream);
 /* dispatch-shaped forms: argument order of gpu_vecmat (lib/kernel_templates_llama.pl:147-158)
  * and gpu_matmul (lib/kernel_templates_llama.pl:1104-1112) with the fp32 [K][N] weight
  * replaced by Q4_K rows [N][K/256][144] */
@@ -258,9 +291,29 @@ int bpd_quant_q8_0_cuda(const float* x, uint8_t* y, size_t n_elements, void* str
 int bpd_q8_0_block_dots_cuda(const uint8_t* w, const uint8_t* a, int32_t* dots, size_t n_blocks, void* stream);
 /* bench/bpd_cpu.c:4295-4315  bpd_qmatmul_q8_0_cpu: out[m*N+n] = W row n . q8_0(X row m) */
 int bpd_qmatmul_q8_0_cuda(const uint8_t* W, const float* X, float* out, int M, int N, int K, void* stream);
-/* bench/bpd_cpu.c:4002-4013  bpd_embed_lookup_q8_0_cpu */
+/* bench/bpd_cpu.c:4428-4459  bpd_qmatmul_q8_0_llamafile_cpu: fp32 activations X[m_tokens][K], out[token*m_weight + row];
+ * quantizes X to Q8_0 (library-owned scratch of the stream) and runs the dispatcher below */
+int bpd_qmatmul_q8_0_llamafile_cuda(const uint8_t* W, const float* X, float* out, int m_weight, int m_tokens, int K, void* stream);
+/* bench/bpd_gemm_q8_0_cpu.c:159-207  bpd_qmatmul_q8_0_dispatch_cpu: activations already Q8_0 rows [m_tokens][K/32][34].
+ * Eight fp32 partial sums per output, added in the order of the reference's AVX lanes: its result bit for bit. */
+int bpd_qmatmul_q8_0_dispatch_cuda(const uint8_t* Wq, const uint8_t* Xq, float* out, int m_weight, int m_tokens, int K, void* stream);
+/* bench/bpd_gemm_q8_0_cpu.c:32-97  bpd_gemm_q8_0_{RM}_{RN}_cpu: one tile of RM weight rows (w_stride bytes apart) x RN
+ * activation rows (a_stride bytes apart) over k blocks, out[j*ldc + i] */
+int bpd_gemm_q8_0_1_1_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+int bpd_gemm_q8_0_1_2_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+int bpd_gemm_q8_0_1_4_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+int bpd_gemm_q8_0_2_1_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+int bpd_gemm_q8_0_2_2_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+int bpd_gemm_q8_0_2_4_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+int bpd_gemm_q8_0_4_1_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+int bpd_gemm_q8_0_4_2_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+int bpd_gemm_q8_0_4_4_cuda(const uint8_t* W_tile, const uint8_t* B_tile, int k, int w_stride, int a_stride, float* out, int ldc, void* stream);
+/* bench/bpd_cpu.c:4002-4013  bpd_embed_lookup_q8_0_cpu.  An id below zero (and, in the _vocab form, at or above
+ * vocab_size) is not looked up: that row of `out` is left as it was and bpdq_last_status() reports -4. */
 int bpd_embed_lookup_q8_0_cuda(const uint8_t* table, const int32_t* ids, float* out, int n_tokens, int embed_dim,
                                void* stream);
+int bpd_embed_lookup_q8_0_vocab_cuda(const uint8_t* table, const int32_t* ids, float* out, int n_tokens, int embed_dim,
+                                     int vocab_size, void* stream);
 /* Q8_0 re-tiled for the tensor cores: the idea of inference/llamatov_c_inference.py:88-100 ("Q8 padded 64B
  * coalesced [nb,N,64]") as a pure permutation of the Q8_0 bytes.  Per tile of 128 rows and block of 32
  * elements a unit of 4352 bytes: the 128x32 int8 quants, element (r,k) at (k/16)*2048 + (r/8)*128 +
@@ -272,6 +325,9 @@ int bpd_unrepack_q8_0_tiles_cuda(const uint8_t* tiles, uint8_t* raw, int N, int 
 /* bench/bpd_cpu.c:4295-4315  bpd_qmatmul_q8_0_cpu on re-tiled weights, any number of tokens M, on the
  * tcgen05 tensor cores; the fp32 operations per block are the scalar reference's, in its order */
 int bpd_qmatmul_q8_0_tiles_cuda(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, void* stream);
+size_t bpdq_qmatmul_q8_0_tiles_workspace_bytes(int M, int N, int K);
+int bpd_qmatmul_q8_0_tiles_ws_cuda(const uint8_t* tiles, const float* X, float* out, int M, int N, int K, void* workspace,
+                                   size_t workspace_bytes, void* stream);
 /* gpu_vecmat's argument order (lib/kernel_templates_llama.pl:147-158) with Q8_0 rows [n][k/32][34] */
 void gpu_vecmat_q8_0(const float* a, const uint8_t* wq, float* c, int k, int n);
 
@@ -293,7 +349,11 @@ void gpu_matmul_opt(const float* A, const float* B, float* C, int M, int N, int 
  * for field), same argument order; every pointer inside them and every array argument is DEVICE
  * memory; the KV caches are [n_layers][max_seq_len][n_kv_heads*head_dim] f16 (kv_cache_f16 = 1) or f32
  * and must be zero where nothing has been written (all max_seq_len rows take part in the softmax,
- * masked, as in the reference).  token_out may be NULL.  Asynchronous on `stream`; 0 or a status. */
+ * masked, as in the reference).  token_out may be NULL.  Asynchronous on `stream`; 0 or a status.
+ * Indices that come from device memory are checked on the device: a token id outside [0, vocab_size) is not looked
+ * up and a position outside [0, max_seq_len) is not stored (the embedding row / cache row is left untouched), and
+ * bpdq_last_status() then reports -4.  Attention takes query t to sit at position kv_pos + t: pos_ids must be
+ * kv_pos, kv_pos + 1, ... (as the reference's callers pass them); the rotary embedding uses pos_ids itself. */
 typedef struct {
     int n_layers, n_heads, n_kv_heads, head_dim, embed_dim, ffn_dim, vocab_size, max_seq_len;
     float rms_eps, rope_base;
@@ -342,6 +402,13 @@ int bpd_llama_forward_tiles_cuda(const int32_t* token_ids, int n_tokens, const b
                                  const bpd_llama_weights* tiles, const bpd_llama_config* cfg, const int32_t* pos_ids,
                                  int kv_pos, void* k_cache, void* v_cache, float* logits_out, long long* token_out,
                                  void* stream);
+
+/* the forward with caller-owned scratch (see "scratch memory" above); tiles may be NULL */
+size_t bpdq_llama_forward_workspace_bytes(const bpd_llama_config* cfg, int n_tokens);
+int bpd_llama_forward_ws_cuda(const int32_t* token_ids, int n_tokens, const bpd_llama_weights* weights,
+                              const bpd_llama_weights* tiles, const bpd_llama_config* cfg, const int32_t* pos_ids, int kv_pos,
+                              void* k_cache, void* v_cache, float* logits_out, long long* token_out, void* workspace,
+                              size_t workspace_bytes, void* stream);
 
 /* ---- row-sharded products on several GPUs without a collective.
  * The reference's decode loop runs on one GPU; with the rows of every matrix sharded over ranks (one

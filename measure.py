@@ -1,16 +1,16 @@
 """Timings of the secondary configurations (the benchmark line itself comes from bench.py).
 
-    python -m bpd_substrate_b200.measure            # prints one JSON object per configuration
-    python -m bpd_substrate_b200.measure --llama-decode [LAYERS]
+    python measure.py            # prints one JSON object per configuration
+    python measure.py --llama-decode [LAYERS]
                                                     # Q8_0 Llama forward, 8B-shaped layers: ms per decoded token
-    python -m bpd_substrate_b200.measure --llama-prefill [LAYERS] [TOKENS]
+    python measure.py --llama-prefill [LAYERS] [TOKENS]
                                                     # the same layers, a prefill: rows against re-tiled weights
-    python -m bpd_substrate_b200.measure --q8-tiles [N K]
+    python measure.py --q8-tiles [N K]
                                                     # Q8_0 many-token product on re-tiled weights (tcgen05)
                                                     # beside the row-layout kernel, 1..512 tokens
-    python -m bpd_substrate_b200.measure --q8-tiles-once TOKENS [N K]
+    python measure.py --q8-tiles-once TOKENS [N K]
                                                     # five launches of the re-tiled product: a small case for a profiler
-    python -m bpd_substrate_b200.measure --gemm-once tc5 64 [N K]
+    python measure.py --gemm-once tc5 64 [N K]
                                                     # five launches of one many-token product (kernel
                                                     # tc5 | mma | dispatch): a small case for a profiler
 
@@ -19,18 +19,20 @@ copies that the working set is several times the L2 size, so no launch finds its
 cached.  Times are CUDA events on the launching stream around `iters` launches.
 """
 import json
+import os
 import sys
 
 import numpy as np
 
-from . import capi, synth
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from bpd_substrate_b200 import capi, synth  # noqa: E402
 
 PEAK_FALLBACK = 6650.0
 
 
 def _peak():
-    import os
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     try:
         return float(json.load(open(path))["hbm_gbs"])
     except Exception:
@@ -88,7 +90,7 @@ def llama_prefill(lib, n_layers=4, tokens=128):
     """Prefill of `tokens` tokens through `n_layers` 8B-shaped Q8_0 layers, on the rows (one pass over each
     matrix per token) and on the re-tiled copies (one pass on the tensor cores)."""
     import ctypes as C
-    from . import llama
+    from bpd_substrate_b200 import llama
     cfg = llama.make_config(n_layers=n_layers, n_heads=32, n_kv_heads=8, head_dim=128, ffn_dim=14336, vocab_size=32000,
                             max_seq_len=max(256, tokens))
     model = llama.SyntheticLlama(cfg, seed=3)
@@ -167,7 +169,7 @@ def llama_decode(lib, n_layers=4, steps=32):
     f16 KV cache of 256 positions.  Prints ms per token and the bytes that a token must read."""
     import ctypes as C
 
-    from . import llama
+    from bpd_substrate_b200 import llama
     cfg = llama.make_config(n_layers=n_layers, n_heads=32, n_kv_heads=8, head_dim=128, ffn_dim=14336, vocab_size=32000,
                             max_seq_len=256)
     model = llama.SyntheticLlama(cfg, seed=1)
@@ -263,7 +265,25 @@ def main():
     x, o = _dev(lib, synth.activations(K, 1002)), lib.bpdq_alloc(N * 4)
     us = tm.run(lambda i: lib.bpd_qmatmul_q8_0_cuda(ws[i % n], x, o, 1, N, K, s), 100)
     report("1: Q8_0 GEMV 4096x4096 (single launches back to back)", us, synth.gemv_bytes_q8_0(N, K))
-    for p in ws + [x, o]:
+    # the same product the way the benchmark's step is measured: 32 distinct matrices (567 MB, beyond L2), each
+    # with its own vector, recorded once into a CUDA graph (programmatic launch edges kept) and replayed
+    n32 = 32
+    ws32 = ws[:n32] if n >= n32 else ws + [_dev(lib, W) for _ in range(n32 - n)]
+    xs32 = [_dev(lib, synth.activations(K, 1100 + j)) for j in range(n32)]
+    os32 = [lib.bpdq_alloc(N * 4) for _ in range(n32)]
+
+    def step32(_):
+        for j in range(n32):
+            lib.bpd_qmatmul_q8_0_cuda(ws32[j], xs32[j], os32[j], 1, N, K, s)
+    step32(0)
+    lib.bpdq_stream_sync(s)
+    lib.bpdq_graph_begin(s)
+    step32(0)
+    g = lib.bpdq_graph_end(s)
+    us = tm.run(lambda i: lib.bpdq_graph_launch(g, s), 50) / n32
+    report("1: Q8_0 GEMV 4096x4096 (32 distinct matrices per graph replay, per product)", us, synth.gemv_bytes_q8_0(N, K))
+    lib.bpdq_graph_destroy(g)
+    for p in list(set(ws32) | set(ws)) + xs32 + os32 + [x, o]:
         lib.bpdq_free(p)
 
     # ---- config 3: Q4_K x Q8_K GEMM, N=14336, K=4096, M tokens

@@ -26,7 +26,8 @@ Q4K_BYTES, Q80_BYTES, Q8K_BYTES = 144, 34, 292
 def build(ref_root=None):
     """Compile the restatement; also the reference files when their tree exists."""
     subprocess.check_call(["make", "-s", "-C", HERE, "all"])
-    root = ref_root or os.environ.get("BPD_REFERENCE_ROOT", "/root/reference")
+    # the reference checkout: named by the environment, else a directory "reference" beside this repository
+    root = ref_root or os.environ.get("BPD_REFERENCE_ROOT") or os.path.join(os.path.dirname(HERE), os.pardir, "reference")
     if os.path.isdir(os.path.join(root, "bench")):
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", "REF=" + root])
 
@@ -80,6 +81,9 @@ class Oracle:
         lib.orc_qmatmul_q4k_q8k.argtypes = [vp, vp, vp, vp, i, i, i]
         lib.orc_qmm_q4k_q8k.argtypes = [vp, vp, vp, vp, i, i, i, i]
         lib.orc_qmm_q4k_q8k.restype = i
+        lib.orc_qmm_q4k_q8k_ints.argtypes = [vp, vp, vp, i, i, i, i]
+        lib.orc_qmm_q4k_q8k_ints.restype = i
+        lib.orc_qmatmul_q8_0_lanes.argtypes = [vp, vp, vp, i, i, i]
         lib.orc_vecmat_f32.argtypes = [vp, vp, vp, i, i]
         lib.orc_rms_norm_f64.argtypes = [vp, vp, vp, i, i, C.c_float]
         f = C.c_float
@@ -208,6 +212,21 @@ class Oracle:
         out, out64 = np.empty((T, M), np.float32), np.empty((T, M), np.float64)
         assert self.lib.orc_qmm_q4k_q8k(_p(qw), _p(X), _p(out), _p(out64), T, M, K, layout) == 0
         return out, out64
+
+    def qmm_q4k_q8k_ints(self, qw, X, T, M, K, layout=0):
+        """X [T][K] fp32 -> int32 [T][M][K/256][2]: the exact (isum, msum) of every super-block."""
+        qw, X = _u8(qw), _f32(X)
+        ints = np.empty((T, M, K // 256, 2), np.int32)
+        assert self.lib.orc_qmm_q4k_q8k_ints(_p(qw), _p(X), _p(ints), T, M, K, layout) == 0
+        return ints
+
+    def qmatmul_q8_0_lanes(self, Wq, Xq, m_weight, m_tokens, K):
+        """Q8_0 x Q8_0 with the eight-lane fp32 order of the reference's AVX tile kernels:
+        out [m_tokens][m_weight]."""
+        Wq, Xq = _u8(Wq), _u8(Xq)
+        out = np.empty((m_tokens, m_weight), np.float32)
+        self.lib.orc_qmatmul_q8_0_lanes(_p(Wq), _p(Xq), _p(out), m_weight, m_tokens, K)
+        return out
 
     # -- fp32 dispatch ops
     def vecmat_f32(self, a, b, k, n):

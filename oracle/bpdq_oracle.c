@@ -351,6 +351,43 @@ int orc_qmatmul_q8_0_f64(const uint8_t *W, const float *X, double *out,
     return 0;
 }
 
+/* The tile kernels and dispatcher of bench/bpd_gemm_q8_0_cpu.c:32-97, 159-207
+ * (AVX build) on activations that are already Q8_0 rows.  Per output cell the
+ * reference keeps eight fp32 lanes; lane q takes, block after block,
+ *     c_q = (wd * ad) * (float)(w[4q..4q+3] . a[4q..4q+3]) + c_q
+ * (a 32-bit lane of p32 is the sum of four adjacent byte products; multiply
+ * and add are separate roundings), and joins the lanes at the end as
+ *     s_q = c_{q+4} + c_q (q < 4);  t_0 = s_0 + s_2, t_1 = s_1 + s_3;  t_0 + t_1.
+ * The tiling (which cells share a call) does not change a cell's arithmetic,
+ * so this is written cell by cell.  out[j * m_weight + i]. */
+void orc_qmatmul_q8_0_lanes(const uint8_t *Wq, const uint8_t *Xq, float *out,
+                            int m_weight, int m_tokens, int K)
+{
+    int bpr = K / Q80_BLK_ELEMS;
+    size_t rb = (size_t)bpr * Q80_BLK_BYTES;
+    for (int j = 0; j < m_tokens; j++)
+        for (int i = 0; i < m_weight; i++) {
+            float c[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int l = 0; l < bpr; l++) {
+                const uint8_t *wb = Wq + (size_t)i * rb + (size_t)l * Q80_BLK_BYTES;
+                const uint8_t *ab = Xq + (size_t)j * rb + (size_t)l * Q80_BLK_BYTES;
+                float wd = orc_f16_to_f32((uint16_t)(wb[0] | (wb[1] << 8)));
+                float ad = orc_f16_to_f32((uint16_t)(ab[0] | (ab[1] << 8)));
+                float scale = wd * ad;
+                const int8_t *wq = (const int8_t *)(wb + 2), *aq = (const int8_t *)(ab + 2);
+                for (int q = 0; q < 8; q++) {
+                    int32_t p = 0;
+                    for (int e = 0; e < 4; e++) p += (int32_t)wq[4 * q + e] * (int32_t)aq[4 * q + e];
+                    float prod = scale * (float)p;
+                    c[q] = prod + c[q];
+                }
+            }
+            float s0 = c[4] + c[0], s1 = c[5] + c[1], s2 = c[6] + c[2], s3 = c[7] + c[3];
+            float t0 = s0 + s2, t1 = s1 + s3;
+            out[(size_t)j * m_weight + i] = t0 + t1;
+        }
+}
+
 /* ------------------------------------------- Q8_K (builder-defined format) */
 
 /* Q8_K block, 292 bytes for 256 activations (size fact:
@@ -490,6 +527,28 @@ int orc_qmm_q4k_q8k(const uint8_t *qw, const float *X, float *out, double *out64
         orc_quant_q8_K(X + (size_t)t * K, xq, K);
         orc_qmatmul_q4k_q8k(qw, xq, out + (size_t)t * M,
                             out64 ? out64 + (size_t)t * M : NULL, M, K, layout);
+    }
+    free(xq);
+    return 0;
+}
+
+/* The exact integer pair of every (token, row, super-block) of the batched
+ * form: ints[((t*M + r)*nb + b)*2 + {0,1}] = (isum, msum) as defined at
+ * q4k_q8k_sb_ints.  Builder-defined. */
+int orc_qmm_q4k_q8k_ints(const uint8_t *qw, const float *X, int32_t *ints,
+                         int T, int M, int K, int layout)
+{
+    int nb = K / Q4K_SB_ELEMS;
+    uint8_t *xq = (uint8_t *)malloc((size_t)nb * Q8K_BLK_BYTES + 1);
+    if (!xq) return -1;
+    for (int t = 0; t < T; t++) {
+        orc_quant_q8_K(X + (size_t)t * K, xq, K);
+        for (int r = 0; r < M; r++)
+            for (int b = 0; b < nb; b++) {
+                int32_t *o = ints + (((size_t)t * M + r) * nb + b) * 2;
+                q4k_q8k_sb_ints(qw + ((size_t)r * nb + b) * Q4K_SB_BYTES,
+                                xq + (size_t)b * Q8K_BLK_BYTES, layout, o, o + 1);
+            }
     }
     free(xq);
     return 0;

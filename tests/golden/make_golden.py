@@ -35,6 +35,30 @@ def sha(a):
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
 
+def avx_tiles_fixture(ra):
+    """The tile dispatcher and three single tiles of the AVX build on ragged shapes (every RM x RN
+    combination occurs in 37 weight rows x 7 activation rows)."""
+    rng = np.random.default_rng(4250)
+    mw, mt, K = 37, 7, 1024
+    W = synth.q8_0_matrix(mw, K, rng)
+    X = synth.activations(K, rng, rows=mt)
+    rb = K // 32 * 34
+    Xq = np.zeros(mt * rb, np.uint8)
+    ra.bpd_quant_q8_0_cpu(X.ctypes.data, Xq.ctypes.data, mt * K)
+    disp = np.empty((mt, mw), np.float32)
+    ra.bpd_qmatmul_q8_0_dispatch_cpu(W.ctypes.data, Xq.ctypes.data, disp.ctypes.data, mw, mt, K)
+    lf = np.empty((mt, mw), np.float32)
+    ra.bpd_qmatmul_q8_0_llamafile_cpu(W.ctypes.data, X.ctypes.data, lf.ctypes.data, mw, mt, K)
+    tiles = {}
+    for rm, rn in ((4, 4), (2, 1), (1, 2)):
+        o = np.zeros((rn, 8), np.float32)          # ldc = 8
+        getattr(ra, f"bpd_gemm_q8_0_{rm}_{rn}_cpu")(W.ctypes.data + 3 * rb, Xq.ctypes.data + rb, K // 32, rb, rb,
+                                                     o.ctypes.data, 8)
+        tiles[f"tile_{rm}_{rn}"] = o.view(np.uint32)
+    np.savez_compressed(os.path.join(HERE, "q8_0_avx_tiles.npz"), W=W, X=X, Xq=Xq, dispatch=disp.view(np.uint32),
+                        llamafile=lf.view(np.uint32), shape=np.array([mw, mt, K]), **tiles)
+
+
 def main():
     binding.build()
     rq = binding.load_ref("bpd_quant.so")
@@ -85,6 +109,8 @@ def main():
     np.savez_compressed(os.path.join(HERE, "q8_0_small.npz"), W=Wq, X=X, dequant=deq.view(np.uint32), Xq=Xq,
                         matmul_scalar=mm.view(np.uint32), matmul_avx_tiles=mm_avx.view(np.uint32),
                         shape=np.array([Mt, Nw, Kq]))
+
+    avx_tiles_fixture(ra)
 
     # ---- Q8_0 GEMV of the benchmark shape 4096 x 4096: hash + sample (scalar build)
     W = synth.q8_0_matrix(4096, 4096, 1001)

@@ -194,11 +194,11 @@ def test_stream_of_products_equals_batched_entries(lib):
         descs = (capi.GemvDesc * n)(*[capi.GemvDesc(Ws[j].ptr, xs[j].ptr, outs[j].ptr, m, k) for j, (m, k) in enumerate(shapes)])
         ws_bytes = lib.bpdq_batch_workspace_bytes(n, descs)
         ws = Dev(lib, nbytes=ws_bytes)
-        if entry == "stream":
+        if entry in ("stream", "stream-ready"):
             h = lib.bpdq_gemv_stream_create(n, descs, ws.ptr, ws_bytes)
-            assert h
+            assert h and lib.bpdq_gemv_stream_launches(h) == 2
             for _ in range(3):
-                assert lib.bpdq_gemv_stream_run(h, None) == 0
+                assert (lib.bpdq_gemv_stream_run if entry == "stream" else lib.bpdq_gemv_stream_run_ready)(h, None) == 0
             lib.bpdq_sync()
             lib.bpdq_gemv_stream_destroy(h)
         else:
@@ -207,9 +207,10 @@ def test_stream_of_products_equals_batched_entries(lib):
         assert lib.bpdq_last_status() == 0
         return [o.read(np.uint32) for o in outs]
 
-    a, b = run("batch"), run("stream")
+    a, b, c = run("batch"), run("stream"), run("stream-ready")
     for j in range(n):
         assert np.array_equal(a[j], b[j]), j
+        assert np.array_equal(a[j], c[j]), j
     assert not lib.bpdq_gemv_stream_create(0, None, None, 0)
     lib.bpdq_clear_status()
 
@@ -253,3 +254,86 @@ def test_layer_set_schedules_and_host_step_agree(lib, oracle):
         assert lib.bpdq_last_status() == 0
     finally:
         ls.close()
+
+
+def test_product_chained_behind_its_producer_with_programmatic_launch(lib, oracle):
+    """The activation vector of a batched product is the OUTPUT of the launch just ahead of it (itself a
+    product kernel, which lets its dependents start early).  The stream-ordered entries (_ws and the
+    allocation-free one) must read the finished vector: same bits with programmatic launch on and off,
+    and equal to the checker fed the first product's output."""
+    from bpd_substrate_b200 import capi
+    K0, K1, M = 2048, 4096, 300
+    rng = np.random.default_rng(55)
+    W0, W1 = synth.q4k_matrix(K1, K0, rng), synth.q4k_matrix(M, K1, rng)
+    x0 = synth.activations(K0, rng)
+    dW0, dW1, dx0 = Dev(lib, W0), Dev(lib, W1), Dev(lib, x0)
+    results = {}
+    for pdl in (1, 0):
+        lib.bpdq_set_tuning(0, 0, 0, 0, pdl)
+        for entry in ("ws", "static"):
+            mid = Dev(lib, nbytes=K1 * 4, fill=0xFF)      # poisoned: a stale read shows
+            out = Dev(lib, nbytes=M * 4, fill=0xFF)
+            d0 = (capi.GemvDesc * 1)(capi.GemvDesc(dW0.ptr, dx0.ptr, mid.ptr, K1, K0))
+            d1 = (capi.GemvDesc * 1)(capi.GemvDesc(dW1.ptr, mid.ptr, out.ptr, M, K1))
+            nbytes = lib.bpdq_batch_workspace_bytes(1, d0) + lib.bpdq_batch_workspace_bytes(1, d1)
+            ws = Dev(lib, nbytes=nbytes)
+            for rep in range(20):                           # back to back: the overlap window is open every time
+                assert lib.bpd_qmatmul_q4k_q8k_batch_ws_cuda(1, d0, ws.ptr, nbytes, None) == 0
+                if entry == "ws":
+                    assert lib.bpd_qmatmul_q4k_q8k_batch_ws_cuda(1, d1, ws.ptr, nbytes, None) == 0
+                else:
+                    assert lib.bpd_qmatmul_q4k_q8k_batch_static_cuda(1, d1, None) == 0
+            lib.bpdq_sync()
+            assert lib.bpdq_last_status() == 0
+            results[(pdl, entry)] = (mid.read(np.float32), out.read(np.float32))
+    lib.bpdq_set_tuning(0, 0, 0, 0, 1)
+    mid_ref, out_ref = results[(0, "ws")]
+    for key, (mid, out) in results.items():
+        assert np.array_equal(mid.view(np.uint32), mid_ref.view(np.uint32)), key
+        assert np.array_equal(out.view(np.uint32), out_ref.view(np.uint32)), key
+    _, want = oracle.qmatmul_q4k_q8k(W1, oracle.quant_q8_K(mid_ref), M, K1)
+    assert normwise(out_ref, want) <= TOL
+
+
+def test_long_stream_many_phases_and_two_launches(lib, oracle):
+    """150 products (two persistent launches of 75) whose activation records fill the two shared-memory record
+    buffers many times over: every consumer warp passes through every phase, with and without tiles of its own
+    (several products have fewer tiles than there are warps).  Checked against the CPU checker product by product."""
+    from bpd_substrate_b200 import capi
+    rng = np.random.default_rng(314)
+    kinds = [(700, 4096), (40, 4096), (3, 14336), (260, 1024), (1, 256), (90, 8192), (33, 28672)]
+    base = {kk: synth.q4k_matrix(m, k, rng) for kk, (m, k) in enumerate(kinds)}
+    shapes, Ws, xs = [], [], []
+    for j in range(150):
+        kk = j % len(kinds)
+        shapes.append(kinds[kk])
+        Ws.append(np.roll(base[kk], 144 * (j // len(kinds) + 1)))
+        xs.append(synth.activations(kinds[kk][1], rng))
+    dW, dX = [Dev(lib, w) for w in Ws], [Dev(lib, x) for x in xs]
+    outs = [Dev(lib, nbytes=m * 4, fill=0xFF) for m, _ in shapes]
+    n = len(shapes)
+    descs = (capi.GemvDesc * n)(*[capi.GemvDesc(dW[j].ptr, dX[j].ptr, outs[j].ptr, m, k) for j, (m, k) in enumerate(shapes)])
+    ws_bytes = lib.bpdq_batch_workspace_bytes(n, descs)
+    ws = Dev(lib, nbytes=ws_bytes, fill=0xCD)
+    h = lib.bpdq_gemv_stream_create(n, descs, ws.ptr, ws_bytes)
+    assert h and lib.bpdq_gemv_stream_launches(h) == 4
+    first = None
+    for rep in range(3):
+        assert lib.bpdq_gemv_stream_run_ready(h, None) == 0
+        lib.bpdq_sync()
+        assert lib.bpdq_last_status() == 0
+        got = [o.read(np.float32) for o in outs]
+        if first is None:
+            first = got
+            for j, (m, k) in enumerate(shapes):
+                _, ref64 = oracle.qmatmul_q4k_q8k(Ws[j], oracle.quant_q8_K(xs[j]), m, k)
+                assert normwise(got[j], ref64) <= TOL, (j, m, k)
+        else:
+            for j in range(n):
+                assert np.array_equal(got[j].view(np.uint32), first[j].view(np.uint32)), (rep, j)
+        for o in outs:
+            lib.bpdq_memset_async(o.ptr, 0xFF, o.nbytes, None)
+    lib.bpdq_gemv_stream_destroy(h)
+    # too small a workspace is refused
+    assert not lib.bpdq_gemv_stream_create(n, descs, ws.ptr, 1024)
+    lib.bpdq_clear_status()

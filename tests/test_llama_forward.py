@@ -343,3 +343,90 @@ def test_block_and_forward_equal_their_separate_steps_bit_for_bit(lib, n):
                 assert np.array_equal(a, b), (kind, what, int(np.count_nonzero(a != b)))
     finally:
         dev.close()
+
+
+@pytest.mark.gpu
+def test_indices_from_device_memory_are_checked(lib, tiny):
+    """A position outside [0, max_seq_len) is not stored, a token id outside [0, vocab_size) is not looked
+    up: the cache keeps its bytes, nothing outside it is touched, and the status says -4.  (The
+    reference's CPU code would index out of bounds.)"""
+    import ctypes as C
+    from tests.util import Dev
+    c = tiny.cfg
+    row = c.n_kv_heads * c.head_dim
+    rng = np.random.default_rng(3)
+    src = rng.standard_normal((3, row)).astype(np.float32)
+    pos = np.array([2, c.max_seq_len, -1], np.int32)             # one good row, two without a home
+    d_src, d_pos = Dev(lib, src), Dev(lib, pos)
+    # the cache sits inside a larger poisoned buffer, so that a stray write would show on either side
+    guard = 4096
+    for f16, fn in ((1, lib.bpd_kv_cache_write_f16_cuda), (0, lib.bpd_kv_cache_write_cuda)):
+        esz = 2 if f16 else 4
+        nbytes = c.max_seq_len * row * esz
+        buf = Dev(lib, nbytes=nbytes + 2 * guard, fill=0xA5)
+        lib.bpdq_clear_status()
+        assert fn(buf.ptr + guard, d_src.ptr, d_pos.ptr, 3, c.n_kv_heads, c.head_dim, c.max_seq_len, None) == 0
+        lib.bpdq_sync()
+        assert lib.bpdq_last_status() == -4 and lib.bpdq_device_error_word() == 20
+        lib.bpdq_clear_status()
+        raw = buf.read(np.uint8)
+        body = raw[guard:guard + nbytes].reshape(c.max_seq_len, row * esz)
+        assert (raw[:guard] == 0xA5).all() and (raw[guard + nbytes:] == 0xA5).all()
+        want = src[0].astype(np.float16).view(np.uint8) if f16 else src[0].view(np.uint8)
+        assert np.array_equal(body[2], want)
+        assert (np.delete(body, 2, axis=0) == 0xA5).all()
+    # the whole forward: a bad token id and a bad position
+    dev = llama.DeviceLlama(tiny, lib)
+    try:
+        n = 2
+        d = {k: Dev(lib, v) for k, v in dict(tok=np.array([5, c.vocab_size], np.int32), pos=np.array([0, 1], np.int32),
+                                             badpos=np.array([0, c.max_seq_len + 3], np.int32),
+                                             oktok=np.array([5, 6], np.int32)).items()}
+        logits, out = Dev(lib, nbytes=4 * n * c.vocab_size), Dev(lib, nbytes=8 * n)
+        for tok, pos_key in (("tok", "pos"), ("oktok", "badpos")):
+            lib.bpdq_clear_status()
+            assert lib.bpd_llama_forward_cuda(d[tok].ptr, n, C.byref(dev.weights), C.byref(dev.cfg), d[pos_key].ptr, 0,
+                                              dev.d_k, dev.d_v, logits.ptr, out.ptr, dev.stream) == 0
+            assert lib.bpdq_stream_sync(dev.stream) == 0
+            assert lib.bpdq_last_status() == -4
+        lib.bpdq_clear_status()
+    finally:
+        dev.close()
+
+
+@pytest.mark.gpu
+def test_forward_with_caller_owned_workspace(lib, tiny):
+    """bpd_llama_forward_ws_cuda: same bits as the plain entry, prefill on re-tiled weights included; a
+    workspace that is too small is refused before anything runs."""
+    import ctypes as C
+    from tests.util import Dev
+    c = tiny.cfg
+    toks = np.array([3, 17, 95, 0, 42], np.int32)
+    pos = np.arange(5, dtype=np.int32)
+    results = []
+    for use_ws in (False, True):
+        dev = llama.DeviceLlama(tiny, lib)
+        try:
+            dev.retile()
+            d_tok, d_pos = Dev(lib, toks), Dev(lib, pos)
+            logits, out = Dev(lib, nbytes=4 * 5 * c.vocab_size, fill=0xFF), Dev(lib, nbytes=8 * 5)
+            if use_ws:
+                nbytes = lib.bpdq_llama_forward_workspace_bytes(C.byref(dev.cfg), 5)
+                assert nbytes > 0
+                ws = Dev(lib, nbytes=nbytes, fill=0xEE)
+                assert lib.bpd_llama_forward_ws_cuda(d_tok.ptr, 5, C.byref(dev.weights), C.byref(dev.tiles), C.byref(dev.cfg),
+                                                     d_pos.ptr, 0, dev.d_k, dev.d_v, logits.ptr, out.ptr, ws.ptr, 1024,
+                                                     dev.stream) == -3
+                lib.bpdq_clear_status()
+                rc = lib.bpd_llama_forward_ws_cuda(d_tok.ptr, 5, C.byref(dev.weights), C.byref(dev.tiles), C.byref(dev.cfg),
+                                                   d_pos.ptr, 0, dev.d_k, dev.d_v, logits.ptr, out.ptr, ws.ptr, nbytes, dev.stream)
+            else:
+                rc = lib.bpd_llama_forward_tiles_cuda(d_tok.ptr, 5, C.byref(dev.weights), C.byref(dev.tiles), C.byref(dev.cfg),
+                                                      d_pos.ptr, 0, dev.d_k, dev.d_v, logits.ptr, out.ptr, dev.stream)
+            assert rc == 0
+            assert lib.bpdq_stream_sync(dev.stream) == 0
+            assert lib.bpdq_last_status() == 0
+            results.append((logits.read(np.uint32), out.read(np.int64)))
+        finally:
+            dev.close()
+    assert np.array_equal(results[0][0], results[1][0]) and np.array_equal(results[0][1], results[1][1])

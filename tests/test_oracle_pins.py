@@ -139,6 +139,26 @@ def test_golden_q8_0_small(oracle):
     assert np.max(np.abs(avx - got)) / np.max(np.abs(got)) <= 1e-5
 
 
+def test_golden_q8_0_avx_tiles(oracle):
+    """The eight-lane restatement of the AVX tile kernels (bench/bpd_gemm_q8_0_cpu.c:32-207) gives the
+    bits the compiled AVX build produced: dispatcher, bpd_qmatmul_q8_0_llamafile_cpu and three single
+    tiles, on 37 weight rows x 7 activation rows (all nine tile shapes occur)."""
+    g = np.load(os.path.join(GOLD, "q8_0_avx_tiles.npz"))
+    mw, mt, K = (int(v) for v in g["shape"])
+    assert np.array_equal(oracle.quant_q8_0(g["X"]), g["Xq"])
+    got = oracle.qmatmul_q8_0_lanes(g["W"], g["Xq"], mw, mt, K)
+    assert np.array_equal(u32(got), g["dispatch"])
+    assert np.array_equal(u32(got), g["llamafile"])
+    rb = K // 32 * 34
+    for rm, rn in ((4, 4), (2, 1), (1, 2)):
+        tile = oracle.qmatmul_q8_0_lanes(g["W"][3 * rb:(3 + rm) * rb], g["Xq"][rb:(1 + rn) * rb], rm, rn, K)
+        assert np.array_equal(u32(tile), g[f"tile_{rm}_{rn}"][:, :rm])
+    # the small fixture's dispatcher output too
+    s = np.load(os.path.join(GOLD, "q8_0_small.npz"))
+    Mt, Nw, Kq = (int(v) for v in s["shape"])
+    assert np.array_equal(u32(oracle.qmatmul_q8_0_lanes(s["W"], s["Xq"], Nw, Mt, Kq)), s["matmul_avx_tiles"].reshape(Mt, Nw))
+
+
 def test_golden_q8_0_gemv_4096(oracle):
     g = np.load(os.path.join(GOLD, "q8_0_gemv_4096x4096.npz"))
     W = synth.q8_0_matrix(4096, 4096, int(g["w_seed"][0]))
@@ -148,6 +168,18 @@ def test_golden_q8_0_gemv_4096(oracle):
 
 
 # ---- the compiled reference itself, where present
+
+@pytest.mark.skipif(not binding.ref_available("bpd_cpu_avx.so"), reason="compiled reference (AVX build) not present")
+def test_lane_order_restatement_equals_compiled_avx_dispatcher(oracle):
+    ra = binding.load_ref("bpd_cpu_avx.so")
+    rng = np.random.default_rng(5)
+    for mw, mt, K in ((7, 5, 256), (33, 3, 1024), (4, 4, 64), (1, 1, 32), (130, 9, 4096)):
+        W = synth.q8_0_matrix(mw, K, rng)
+        xq = oracle.quant_q8_0(synth.activations(K, rng, rows=mt))
+        out = np.empty((mt, mw), np.float32)
+        ra.bpd_qmatmul_q8_0_dispatch_cpu(W.ctypes.data, xq.ctypes.data, out.ctypes.data, mw, mt, K)
+        assert np.array_equal(u32(out), u32(oracle.qmatmul_q8_0_lanes(W, xq, mw, mt, K))), (mw, mt, K)
+
 
 @needs_ref
 def test_checker_equals_compiled_reference_q4k(oracle):

@@ -18,8 +18,8 @@ class FakeLib:
     """The entry points PeerExchange calls, on plain integers.  Rank r's allocation sits at (r + 1) << 40; a handle
     is the owner's rank; importing rank o's handle on rank r gives (o + 1) << 40 | r << 32 (a distinct mapping)."""
 
-    def __init__(self, rank, fail_import=False):
-        self.rank, self.fail_import = rank, fail_import
+    def __init__(self, rank, fail_import=False, status=0):
+        self.rank, self.fail_import, self.status = rank, fail_import, status
         self.registered, self.signals, self.waits, self.closed, self.freed = None, [], [], [], []
 
     def bpdq_alloc(self, n):
@@ -50,7 +50,7 @@ class FakeLib:
         self.freed.append(p)
 
     def bpdq_last_status(self):
-        return -1000
+        return self.status
 
     def bpdq_clear_status(self):
         pass
@@ -73,7 +73,7 @@ class FakeLib:
         return 0
 
 
-def _worker(rank, world, port, failing_rank, q):
+def _worker(rank, world, port, failing_rank, q, timed_out_rank=-1):
     import torch.distributed as dist
     from bpd_substrate_b200 import capi
     from bpd_substrate_b200.peer import PeerExchange
@@ -81,7 +81,7 @@ def _worker(rank, world, port, failing_rank, q):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        lib = FakeLib(rank, fail_import=(rank == failing_rank))
+        lib = FakeLib(rank, fail_import=(rank == failing_rank), status=-4 if rank == timed_out_rank else 0)
         slot = 4096
         try:
             ex = PeerExchange(lib, dist, rank, world, slot)
@@ -102,18 +102,18 @@ def _worker(rank, world, port, failing_rank, q):
         assert lib.signals == [([b + flags_off + 4 * rank for b in bases], 1), ([b + flags_off + 4 * rank for b in bases], 2)]
         assert lib.waits == [(own + flags_off, world, 2)]
         assert ex.gathered(0) == own and ex.gathered(1) == own + world * slot
-        ex.close()
-        q.put((rank, "ok", "", lib.freed, lib.closed))
+        released = ex.close(dist)
+        q.put((rank, "ok" if released else "kept", "", lib.freed, lib.closed))
     finally:
         dist.destroy_process_group()
 
 
-def _run(failing_rank):
+def _run(failing_rank, timed_out_rank=-1):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, failing_rank, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, failing_rank, q, timed_out_rank)) for r in range(2)]
     for p in procs:
         p.start()
     for p in procs:
@@ -135,3 +135,12 @@ def test_a_failed_mapping_on_one_rank_stops_all_ranks():
         state, message, freed, _ = res[rank]
         assert state == "raised" and "rank 1" in message and "cannot map" in message
         assert freed == [(rank + 1) << 40]          # nothing is left allocated
+
+
+def test_close_after_a_failed_wait_releases_nothing_on_any_rank():
+    """A rank whose bounded flag wait gave up (status -4) cannot know that its peers have stopped storing into its
+    buffer: the ranks agree on the host, and then no rank unmaps or frees anything."""
+    res = _run(failing_rank=-1, timed_out_rank=1)
+    for rank in (0, 1):
+        state, _, freed, closed = res[rank]
+        assert state == "kept" and freed == [] and closed == []

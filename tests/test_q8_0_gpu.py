@@ -115,3 +115,87 @@ def test_vecmat_shaped_entry(lib, oracle):
     lib.bpdq_sync()
     assert lib.bpdq_last_status() == 0
     assert normwise(dO.read(np.float32), oracle.qmatmul_q8_0_f64(W, x, 1, N, K)[0]) <= TOL
+
+
+def test_llamafile_and_dispatch_twins_give_the_avx_reference_bits(lib, oracle):
+    """bpd_qmatmul_q8_0_dispatch_cuda / _llamafile_cuda (bench/bpd_gemm_q8_0_cpu.c:159-207, bench/bpd_cpu.c:4428-4459):
+    the fixture written by the reference's AVX build, bit for bit; per-block integers are exact by construction
+    (test_block_dots) and the eight fp32 lanes are added in the reference's order."""
+    g = np.load(os.path.join(GOLD, "q8_0_avx_tiles.npz"))
+    mw, mt, K = (int(v) for v in g["shape"])
+    dW, dX, dXq = Dev(lib, g["W"]), Dev(lib, g["X"]), Dev(lib, g["Xq"])
+    dO = Dev(lib, nbytes=mt * mw * 4, fill=0xFF)
+    assert lib.bpd_qmatmul_q8_0_dispatch_cuda(dW.ptr, dXq.ptr, dO.ptr, mw, mt, K, None) == 0
+    lib.bpdq_sync()
+    assert np.array_equal(dO.read(np.uint32).reshape(mt, mw), g["dispatch"])
+    lib.bpdq_memset_async(dO.ptr, 0xFF, dO.nbytes, None)
+    assert lib.bpd_qmatmul_q8_0_llamafile_cuda(dW.ptr, dX.ptr, dO.ptr, mw, mt, K, None) == 0
+    lib.bpdq_sync()
+    assert np.array_equal(dO.read(np.uint32).reshape(mt, mw), g["llamafile"])
+    assert lib.bpdq_last_status() == 0
+    # within the stated bar of the sequential-order product as well
+    assert normwise(dO.read(np.float32).reshape(mt, mw), oracle.qmatmul_q8_0_f64(g["W"], g["X"], mt, mw, K)) <= TOL
+
+
+@pytest.mark.parametrize("rm", [1, 2, 4])
+@pytest.mark.parametrize("rn", [1, 2, 4])
+def test_tile_twins(lib, oracle, rm, rn):
+    """The nine bpd_gemm_q8_0_{RM}_{RN}_cuda entries: strided tile in, out[j*ldc + i], cells outside the
+    tile untouched; equal to the lane-order checker (three of them also to the reference-made fixture)."""
+    g = np.load(os.path.join(GOLD, "q8_0_avx_tiles.npz"))
+    mw, mt, K = (int(v) for v in g["shape"])
+    rb = K // 32 * 34
+    dW, dXq = Dev(lib, g["W"]), Dev(lib, g["Xq"])
+    ldc = 8
+    dO = Dev(lib, nbytes=rn * ldc * 4, fill=0xFF)
+    fn = getattr(lib, f"bpd_gemm_q8_0_{rm}_{rn}_cuda")
+    assert fn(dW.ptr + 3 * rb, dXq.ptr + rb, K // 32, rb, rb, dO.ptr, ldc, None) == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == 0
+    got = dO.read(np.uint32).reshape(rn, ldc)
+    want = oracle.qmatmul_q8_0_lanes(g["W"][3 * rb:(3 + rm) * rb], g["Xq"][rb:(1 + rn) * rb], rm, rn, K)
+    assert np.array_equal(got[:, :rm], want.view(np.uint32))
+    assert (got[:, rm:] == 0xFFFFFFFF).all()
+    if f"tile_{rm}_{rn}" in g.files:
+        assert np.array_equal(got[:, :rm], g[f"tile_{rm}_{rn}"][:, :rm])
+
+
+def test_dispatch_twin_large_ragged(lib, oracle):
+    mw, mt, K = 1001, 13, 4096
+    rng = np.random.default_rng(77)
+    W = synth.q8_0_matrix(mw, K, rng)
+    Xq = oracle.quant_q8_0(synth.activations(K, rng, rows=mt))
+    dW, dXq, dO = Dev(lib, W), Dev(lib, Xq), Dev(lib, nbytes=mt * mw * 4, fill=0xFF)
+    assert lib.bpd_qmatmul_q8_0_dispatch_cuda(dW.ptr, dXq.ptr, dO.ptr, mw, mt, K, None) == 0
+    lib.bpdq_sync()
+    assert np.array_equal(dO.read(np.uint32).reshape(mt, mw), oracle.qmatmul_q8_0_lanes(W, Xq, mw, mt, K).view(np.uint32))
+    assert lib.bpd_qmatmul_q8_0_dispatch_cuda(dW.ptr, dXq.ptr, dO.ptr, mw, mt, 100, None) == -1
+    assert lib.bpd_qmatmul_q8_0_dispatch_cuda(dW.ptr + 1, dXq.ptr, dO.ptr, mw, mt, K, None) == -2
+    lib.bpdq_clear_status()
+
+
+def test_embed_lookup_refuses_out_of_range_ids(lib, oracle):
+    """A token id outside the table is not looked up: its output row keeps its bytes, the other rows are
+    right, and the status reports -4 (no read outside the table happens)."""
+    table = synth.q8_0_matrix(40, 512, 8)
+    ids = np.array([3, 40, 0, -1, 17], np.int32)
+    dT, dI, dO = Dev(lib, table), Dev(lib, ids), Dev(lib, nbytes=5 * 512 * 4, fill=0xCD)
+    lib.bpdq_clear_status()
+    assert lib.bpd_embed_lookup_q8_0_vocab_cuda(dT.ptr, dI.ptr, dO.ptr, 5, 512, 40, None) == 0
+    lib.bpdq_sync()
+    got = dO.read(np.float32).reshape(5, 512)
+    assert lib.bpdq_last_status() == -4 and lib.bpdq_device_error_word() == 21
+    lib.bpdq_clear_status()
+    want = oracle.embed_lookup_q8_0(table, np.array([3, 0, 0, 0, 17], np.int32), 512)
+    for t in (0, 2, 4):
+        assert_bits_equal(got[t], want[t])
+    for t in (1, 3):
+        assert (got[t].view(np.uint32) == 0xCDCDCDCD).all()
+    # the reference-shaped entry has no table size: negative ids are still refused
+    lib.bpdq_memset_async(dO.ptr, 0xCD, dO.nbytes, None)
+    dI2 = Dev(lib, np.array([3, 39, 0, -5, 17], np.int32))
+    assert lib.bpd_embed_lookup_q8_0_cuda(dT.ptr, dI2.ptr, dO.ptr, 5, 512, None) == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == -4
+    lib.bpdq_clear_status()
+    assert (dO.read(np.uint32).reshape(5, 512)[3] == 0xCDCDCDCD).all()

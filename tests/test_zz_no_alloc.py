@@ -48,6 +48,34 @@ def test_static_scratch_matches_ordinary_entry_twice_in_a_row(lib, oracle):
             assert normwise(got[j], ref64) <= 1e-5, (call, j)
 
 
+def test_static_scratch_allocates_nothing_and_takes_many_descriptors(lib, oracle):
+    """Twelve products in one call (more than one launch holds: their records sit side by side in the
+    fixed array), with the driver's free-memory reading unchanged across the calls."""
+    import ctypes as C
+    shapes = [(24 + 3 * j, 4096 if j % 3 else 1024) for j in range(12)]
+    Ws, xs, dW, dX = _problem(lib, shapes, 503)
+    want = _run(lib, "bpd_qmatmul_q4k_q8k_batch_cuda", shapes, dW, dX)
+    outs = [Dev(lib, nbytes=m * 4, fill=0xFF) for m, _ in shapes]
+    descs = (capi.GemvDesc * len(shapes))(*[capi.GemvDesc(dW[j].ptr, dX[j].ptr, outs[j].ptr, m, k)
+                                            for j, (m, k) in enumerate(shapes)])
+    assert lib.bpd_qmatmul_q4k_q8k_batch_static_cuda(len(shapes), descs, None) == 0   # first call: set-up done
+    lib.bpdq_sync()
+    free0, free1 = C.c_size_t(0), C.c_size_t(0)
+    assert lib.bpdq_mem_info(C.byref(free0), None) == 0
+    for _ in range(3):
+        assert lib.bpd_qmatmul_q4k_q8k_batch_static_cuda(len(shapes), descs, None) == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_mem_info(C.byref(free1), None) == 0
+    assert free1.value == free0.value
+    assert lib.bpdq_last_status() == 0
+    for j in range(len(shapes)):
+        assert np.array_equal(outs[j].read(np.uint32), want[j].view(np.uint32)), j
+    # a malformed descriptor is an argument error whatever the size of the call
+    bad = (capi.GemvDesc * 1)(capi.GemvDesc(dW[0].ptr, dX[0].ptr, outs[0].ptr, 4, 100))
+    assert lib.bpd_qmatmul_q4k_q8k_batch_static_cuda(1, bad, None) == -1
+    lib.bpdq_clear_status()
+
+
 def test_static_scratch_rejects_oversized_calls(lib):
     cap = lib.bpdq_batch_static_capacity()
     assert cap == 256 * 1024
