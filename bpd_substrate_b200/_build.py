@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbpdq.so")
-SOURCES = ["runtime.cu", "dequant_q4k.cu", "gemv_q4k.cu", "gemv_batch.cu", "gemv_persistent.cu", "gemv_stream.cu", "q8_0.cu", "w4a32.cu", "decode_ops.cu", "gemm_q4k_mma.cu", "gemm_q4k_tc5.cu", "gemm_q8_0_tiles.cu", "llama_forward.cu", "peer_exchange.cu"]
+SOURCES = ["runtime.cu", "dequant_q4k.cu", "gemv_q4k.cu", "gemv_batch.cu", "gemv_persistent.cu", "gemv_stream.cu", "q8_0.cu", "w4a32.cu", "decode_ops.cu", "gemm_q4k_mma.cu", "gemm_q4k_tc5.cu", "gemm_q4k_rg16.cu", "gemm_q8_0_tiles.cu", "llama_forward.cu", "peer_exchange.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

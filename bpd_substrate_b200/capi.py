@@ -120,6 +120,18 @@ SIGNATURES = {
     "bpd_qmm_q4k_q8k_ws_cuda": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, sz, vp]),
     "bpd_qmm_q4k_q8k_mma_ints_cuda": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "bpd_qmm_q4k_q8k_tc5_ints_cuda": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "bpd_q4k_rg16_bytes": (sz, [i32, i32]),
+    "bpd_repack_q4k_rg16_cuda": (i32, [vp, vp, i32, i32, vp]),
+    "bpd_unrepack_q4k_rg16_cuda": (i32, [vp, vp, i32, i32, vp]),
+    "bpd_qmm_q4k_q8k_rg16_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "bpdq_qmm_q4k_q8k_rg16_workspace_bytes": (sz, [i32, i32]),
+    "bpd_qmm_q4k_q8k_rg16_ws_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp, sz, vp]),
+    "bpd_qmm_q4k_q8k_rg16_ints_cuda": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "bpdq_gemm_rg16_stream_workspace_bytes": (sz, [i32, vp, i32]),
+    "bpdq_gemm_rg16_stream_create": (vp, [i32, vp, i32, vp, sz]),
+    "bpdq_gemm_rg16_stream_run": (i32, [vp, vp]),
+    "bpdq_gemm_rg16_stream_launches": (i32, [vp]),
+    "bpdq_gemm_rg16_stream_destroy": (None, [vp]),
     "bpd_qmm_q4k_q8k_mma_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "bpd_qmm_q4k_q8k_tc5_cuda": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "gpu_vecmat_q4k": (None, [vp, vp, vp, i32, i32]),

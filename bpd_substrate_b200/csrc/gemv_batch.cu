@@ -136,6 +136,10 @@ __global__ void __launch_bounds__(256) k_vector_records(const float* __restrict_
     }
 }
 
+// Every consumer warp owns `slots` ring slots and fills them itself: after it has used a slot it issues the
+// bulk copy of the tile it will need `slots` turns later, so a freed slot is on its way to being full again at
+// once and nobody has to notice that it became free.  (A producer warp polling the slots' "empty" barriers
+// reacted too slowly for tiles of a few KB: the weight stream then ran at 85 % of what HBM delivers.)
 template <int FMT, int LAYOUT, int MAXTHREADS, int ACC>
 __global__ void __launch_bounds__(MAXTHREADS, 1)
 k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
@@ -144,17 +148,12 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
     uint8_t* ring = smem + p.off_ring;                                 // [nw][slots][slot_bytes]
     uint8_t* xq = smem + p.off_xq;                                     // activation records
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bar);    // [nw*slots]
-    uint64_t* empty = full + p.nw * p.slots;
-    uint64_t* xbar = empty + p.nw * p.slots;                           // activation records have landed
+    uint64_t* xbar = full + 2 * p.nw * p.slots;                        // activation records have landed
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool is_producer = (warp == p.nw);
     BPDQ_TRACE(0);
     if (tid == 0) {
-        for (int s = 0; s < p.nw * p.slots; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
-        }
+        for (int s = 0; s < p.nw * p.slots; s++) mbar_init(&full[s], 1);
         mbar_init(xbar, 1);
         mbar_init_fence();
     }
@@ -162,41 +161,34 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
     pdl_launch_dependents();
     BPDQ_TRACE(1);
 
-    if (is_producer) {
-        if (lane < p.nw) {
-            // lane g feeds consumer warp g; weights never depend on the previous kernel
-            const int g = lane;
-            int slot = 0;
-            uint32_t wait_parity = 0;
-            bool wrapped = false;
-            for (int v = g * (int)gridDim.x + (int)blockIdx.x; v < p.n_tiles; v += p.nw * (int)gridDim.x) {
-                const int s = g * p.slots + slot;
-                if (wrapped && !mbar_wait_bounded(&empty[s], wait_parity, err, 1)) break;
-                int j = 0;
+    // ---- the tiles of this warp, in order; `lv` runs `slots` tiles ahead of the tile being computed
+    const int stride = p.nw * (int)gridDim.x;
+    const int first = warp * (int)gridDim.x + (int)blockIdx.x;
+    uint8_t* my_ring = ring + (size_t)warp * p.slots * p.slot_bytes;
+    uint64_t* my_full = full + warp * p.slots;
+    int lv = first;
+    auto issue = [&](int slot) {
+        int j = 0;
 #pragma unroll
-                for (int q = 1; q < kMaxBatch; q++)
-                    if (q < p.n_problems && v >= p.prob[q].tile_begin) j = q;
-                const BatchProblem& pb = p.prob[j];
-                const int row0 = (v - pb.tile_begin) * pb.rt;
-                const uint32_t bytes = (uint32_t)min(pb.rt, pb.M - row0) * pb.row_bytes;
-                mbar_expect_tx(&full[s], bytes);
-                bulk_g2s(ring + (size_t)s * p.slot_bytes, pb.W + (size_t)row0 * pb.row_bytes, bytes, &full[s]);
-                if (++slot == p.slots) {
-                    slot = 0;
-                    if (wrapped) wait_parity ^= 1u;
-                    wrapped = true;
-                }
-            }
-            if (lane == 0) BPDQ_TRACE(7);
+        for (int q = 1; q < kMaxBatch; q++)
+            if (q < p.n_problems && lv >= p.prob[q].tile_begin) j = q;
+        const BatchProblem& pb = p.prob[j];
+        const int row0 = (lv - pb.tile_begin) * pb.rt;
+        const uint32_t bytes = (uint32_t)min(pb.rt, pb.M - row0) * pb.row_bytes;
+        if (lane == 0) {
+            mbar_expect_tx(&my_full[slot], bytes);
+            bulk_g2s(my_ring + (size_t)slot * p.slot_bytes, pb.W + (size_t)row0 * pb.row_bytes, bytes, &my_full[slot]);
         }
-        return;
-    }
+        lv += stride;
+    };
+    // weights never depend on the launch before this one: the first tiles are requested at once
+    for (int k = 0; k < p.slots && lv < p.n_tiles; k++) issue(k);
 
     if (p.records) {
-        // Records were written by the quantizer kernel launched just before this one: every consumer
-        // thread waits for it (and so for everything earlier in the stream; unbounded by design, it is
-        // the stream order), one of them pulls the records in with one bulk copy, and the bounded wait
-        // that follows covers nothing but that copy.
+        // Records were written by the quantizer kernel launched just before this one: every thread waits
+        // for it (and so for everything earlier in the stream; unbounded by design, it is the stream
+        // order), one of them pulls the records in with one bulk copy, and the bounded wait that follows
+        // covers nothing but that copy.
         pdl_wait();
         if (tid == 0) {
             mbar_expect_tx(xbar, (uint32_t)p.xq_bytes);
@@ -213,7 +205,7 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
         } else if (p.prologue == 2) {
             cta_swiglu_records(p.pro_a, p.pro_b, p.vec[0].nb, xq, warp, lane, p.nw);
         } else {
-        // ---- quantize every activation vector of the launch into shared memory (all consumer warps)
+        // ---- quantize every activation vector of the launch into shared memory (all warps)
         constexpr int UNR = 4;
         for (int blk0 = warp; blk0 < p.total_blocks; blk0 += p.nw * UNR) {
             float4 v0[UNR], v1[UNR];
@@ -249,22 +241,17 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
 
     int slot = 0;
     uint32_t parity = 0;
-    bool first = true;
-    for (int v = warp * (int)gridDim.x + (int)blockIdx.x; v < p.n_tiles; v += p.nw * (int)gridDim.x) {
-        const int s = warp * p.slots + slot;
-        if (!mbar_wait_bounded(&full[s], parity, err, 2)) return;
-        if (first) { BPDQ_TRACE(5); first = false; }
-        if (++slot == p.slots) {
-            slot = 0;
-            parity ^= 1u;
-        }
+    bool first_tile = true;
+    for (int v = first; v < p.n_tiles; v += stride) {
+        if (!mbar_wait_bounded(&my_full[slot], parity, err, 2)) return;
+        if (first_tile) { BPDQ_TRACE(5); first_tile = false; }
         int j = 0;
 #pragma unroll
         for (int q = 1; q < kMaxBatch; q++)
             if (q < p.n_problems && v >= p.prob[q].tile_begin) j = q;
         const BatchProblem& pb = p.prob[j];
         const int row0 = (v - pb.tile_begin) * pb.rt;
-        const uint8_t* tile_smem = ring + (size_t)s * p.slot_bytes;
+        const uint8_t* tile_smem = my_ring + (size_t)slot * p.slot_bytes;
         const PeerTargets* peers = ACC == 2 ? &p.peers : nullptr;
         if (FMT == 0) {
             if (pb.rt == 4) batch_tile<4, LAYOUT, ACC>(tile_smem, xq + pb.xq_off, pb, row0, lane, peers);
@@ -275,8 +262,14 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
             else if (pb.rt == 2) batch_tile_q80<2>(tile_smem, xq + pb.xq_off, pb, row0, lane);
             else batch_tile_q80<1>(tile_smem, xq + pb.xq_off, pb, row0, lane);
         }
+        // every lane has read the slot (its values went into the row sums, which were folded over the lanes
+        // and stored): refill it
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
+        if (lv < p.n_tiles) issue(slot);
+        if (++slot == p.slots) {
+            slot = 0;
+            parity ^= 1u;
+        }
     }
     BPDQ_TRACE(6);
 }
@@ -404,7 +397,7 @@ static int launch_batch(const BatchPlan& p, cudaStream_t s)
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.grid);
-    cfg.blockDim = dim3((p.nw + 1) * 32);
+    cfg.blockDim = dim3(p.nw * 32);
     cfg.dynamicSmemBytes = p.smem;
     cfg.stream = s;
     cudaLaunchAttribute at[1];

@@ -41,11 +41,14 @@ class LayerSet:
     """
 
     def __init__(self, shapes=synth.MISTRAL_LAYER, n_layers=32, seed=2000, row_shard=(0, 1), lib=None,
-                 d_out=None, tokens=1):
+                 d_out=None, tokens=1, retile=None):
         self.lib = lib or capi.load()
         self.shapes = tuple(shapes)
         self.n_layers = n_layers
-        self.tokens = tokens       # activation rows per product (1 = decode; more: schedule "separate" only)
+        self.tokens = tokens       # activation rows per product (1 = decode)
+        # several activation rows per product: the weights are held re-tiled in groups of 16 rows (one copy, the
+        # permutation of bpd_repack_q4k_rg16_cuda) and the step runs as persistent launches of the MMA kernel on them
+        self.retiled = (tokens > 1) if retile is None else bool(retile)
         rank, world = row_shard
         self.rank, self.world = rank, world
         lib = self.lib
@@ -77,6 +80,12 @@ class LayerSet:
                 w = np.roll(base[m], synth.Q4K_BYTES * (layer + 1))
                 p = lib.bpdq_alloc(w.nbytes)
                 lib.bpdq_h2d(p, w.ctypes.data, w.nbytes)
+                if self.retiled:
+                    t = lib.bpdq_alloc(lib.bpd_q4k_rg16_bytes(rows, cols))
+                    capi.check(lib.bpd_repack_q4k_rg16_cuda(p, t, rows, cols, None), "bpd_repack_q4k_rg16_cuda")
+                    lib.bpdq_sync()
+                    lib.bpdq_free(p)
+                    p = t
                 ptrs.append(p)
                 self.weight_bytes += w.nbytes
             self.weights.append(ptrs)
@@ -92,6 +101,8 @@ class LayerSet:
     # ---- sizes
     def multi_token_kernel(self, schedule):
         """Name of the kernel that does the work when every product has several activation rows."""
+        if self.retiled:
+            return "k_gemm_q4k_rg16"
         return "k_gemm_q4k_q8k_mma / k_gemm_q4k_q8k_tc5 / k_gemv_q4k_q8k (one launch per matrix, by token count and size)"
 
     def algorithmic_bytes(self):
@@ -99,6 +110,8 @@ class LayerSet:
         return self.n_layers * sum(synth.gemv_bytes_q4k(rows, cols, self.tokens) for _, rows, cols in self.local)
 
     def launches_per_step(self, schedule):
+        if self.retiled:
+            return self.lib.bpdq_gemm_rg16_stream_launches(self._stream_plan(0, self.n_layers)[0])
         if self.tokens > 1:
             return 2 * self.n_layers * len(self.local)   # activation quantizer + GEMM kernel per matrix
         if schedule == "persistent":
@@ -126,8 +139,11 @@ class LayerSet:
         (first, last+1) restricts it to a range of layers."""
         lib, s = self.lib, (stream if stream is not None else self.stream)
         first, last = layers if layers is not None else (0, self.n_layers)
+        if self.retiled:
+            capi.check(lib.bpdq_gemm_rg16_stream_run(self._stream_plan(first, last, tag)[0], s), "persistent GEMM launch")
+            return
         if self.tokens > 1:
-            # several tokens per product: one launch per matrix (tensor-core kernel above 4 tokens)
+            # several tokens per product on the original rows: one launch per matrix (tensor-core kernel above 4 tokens)
             nm = len(self.local)
             for layer in range(first, last):
                 for m, (_, rows, cols) in enumerate(self.local):
@@ -183,9 +199,14 @@ class LayerSet:
                     i = layer * nm + m
                     descs[i - first * nm] = capi.GemvDesc(self.weights[layer][m], self.d_x + self.x_off[i],
                                                           self.d_out + self.o_off[i], rows, cols)
-            ws_bytes = lib.bpdq_batch_workspace_bytes(len(descs), descs)
-            ws = lib.bpdq_alloc(ws_bytes)
-            plan = lib.bpdq_gemv_stream_create(len(descs), descs, ws, ws_bytes)
+            if self.retiled:
+                ws_bytes = lib.bpdq_gemm_rg16_stream_workspace_bytes(len(descs), descs, self.tokens)
+                ws = lib.bpdq_alloc(ws_bytes)
+                plan = lib.bpdq_gemm_rg16_stream_create(len(descs), descs, self.tokens, ws, ws_bytes)
+            else:
+                ws_bytes = lib.bpdq_batch_workspace_bytes(len(descs), descs)
+                ws = lib.bpdq_alloc(ws_bytes)
+                plan = lib.bpdq_gemv_stream_create(len(descs), descs, ws, ws_bytes)
             if not plan:
                 lib.bpdq_free(ws)
                 raise capi.BpdqError(f"stream plan rejected (status {lib.bpdq_last_status()})")
@@ -196,7 +217,7 @@ class LayerSet:
         """Forgets the persistent schedule's plans (they are rebuilt on next use, e.g. after the peer targets changed)."""
         self.lib.bpdq_stream_sync(self.stream)
         for plan, ws in self.stream_plans.values():
-            self.lib.bpdq_gemv_stream_destroy(plan)
+            (self.lib.bpdq_gemm_rg16_stream_destroy if self.retiled else self.lib.bpdq_gemv_stream_destroy)(plan)
             self.lib.bpdq_free(ws)
         self.stream_plans = {}
 
@@ -398,10 +419,6 @@ class DecodeChain:
 
     def norm_ptr(self, layer, which):
         return self.d_norm + (layer * 2 + which) * self.hidden * 4
-
-    def multi_token_kernel(self, schedule):
-        """Name of the kernel that does the work when every product has several activation rows."""
-        return "k_gemm_q4k_q8k_mma / k_gemm_q4k_q8k_tc5 / k_gemv_q4k_q8k (one launch per matrix, by token count and size)"
 
     def algorithmic_bytes(self):
         """Quantized weights + fp32 vector in + fp32 vector out of every product, per token."""

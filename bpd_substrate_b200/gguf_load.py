@@ -231,3 +231,38 @@ def repack_tiles_to_q8_0(tiles_raw, rows, cols):
     out[..., 2:] = quants.transpose(0, 3, 4, 1, 2, 5).reshape(tiles, 16, 8, nb, 32)
     out[..., :2] = units[:, :, 4096:].reshape(tiles, nb, 16, 8, 2).transpose(0, 2, 3, 1, 4)
     return out.reshape(tiles * Q8_TILE_ROWS, nb * 34)[:rows].reshape(-1)
+
+
+# ---- Q4_K re-tiled in groups of 16 rows for the int8 MMA (host twin of bpd_repack_q4k_rg16_cuda)
+
+Q4K_RG_ROWS, Q4K_RG_UNIT = 16, 16 * 144
+
+
+def repack_q4k_to_rg16(raw, rows, cols):
+    """Q4_K rows [rows][cols/256][144] -> units [row group][super-block][2304]: the 16 block headers (16 bytes
+    each), then for q = 0..3 and lane L = 0..31 (g = L / 4, t = L % 4) 16 bytes = word t of sub-block 2q of rows g
+    and g + 8, then of sub-block 2q + 1 (word t of sub-block j = bytes 16 + 16 j + 4 t .. + 3 of the block).  Rows
+    beyond ``rows`` are zero.  A pure permutation of the bytes."""
+    nb = cols // 256
+    groups = -(-rows // Q4K_RG_ROWS)
+    src = np.zeros((groups * Q4K_RG_ROWS, nb, 144), np.uint8)
+    src[:rows] = np.asarray(raw, np.uint8).reshape(rows, nb, 144)
+    src = src.reshape(groups, 2, 8, nb, 144)                                   # [G][row / 8][g][b][byte]
+    out = np.empty((groups, nb, Q4K_RG_UNIT), np.uint8)
+    out[:, :, :256] = src[..., :16].reshape(groups, 16, nb, 16).transpose(0, 2, 1, 3).reshape(groups, nb, 256)
+    words = src[..., 16:].reshape(groups, 2, 8, nb, 4, 2, 4, 4)                # [G][hi][g][b][q][j & 1][t][byte]
+    # target order inside a unit: [q][g][t][j & 1][hi][byte]
+    out[:, :, 256:] = words.transpose(0, 3, 4, 2, 6, 5, 1, 7).reshape(groups, nb, 2048)
+    return out.reshape(-1)
+
+
+def repack_rg16_to_q4k(tiles_raw, rows, cols):
+    """The inverse of :func:`repack_q4k_to_rg16`."""
+    nb = cols // 256
+    groups = -(-rows // Q4K_RG_ROWS)
+    units = np.asarray(tiles_raw, np.uint8).reshape(groups, nb, Q4K_RG_UNIT)
+    out = np.empty((groups, 2, 8, nb, 144), np.uint8)
+    out[..., :16] = units[:, :, :256].reshape(groups, nb, 2, 8, 16).transpose(0, 2, 3, 1, 4)
+    words = units[:, :, 256:].reshape(groups, nb, 4, 8, 4, 2, 2, 4)            # [G][b][q][g][t][j & 1][hi][byte]
+    out[..., 16:] = words.transpose(0, 6, 3, 1, 2, 5, 4, 7).reshape(groups, 2, 8, nb, 128)
+    return out.reshape(groups * Q4K_RG_ROWS, nb * 144)[:rows].reshape(-1)

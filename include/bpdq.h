@@ -269,6 +269,35 @@ int bpd_qmm_q4k_q8k_mma_ints_cuda(const uint8_t* qweight, const float* X, float*
                                   void* stream);
 int bpd_qmm_q4k_q8k_tc5_ints_cuda(const uint8_t* qweight, const float* X, float* out, int32_t* sb_ints, int tokens, int M, int K,
                                   void* stream);
+/* ---- Q4_K re-tiled in groups of 16 rows ("rg16"), for products with 2..64 activation rows and more.
+ * The idea of inference/llamatov_c_inference.py:88-100 (a weight layout made for the kernel that reads it) applied to
+ * Q4_K as a pure, exactly invertible permutation: per group of 16 rows and super-block a unit of 2304 bytes = the 16
+ * block headers (row r at 16 r), then the nibble words in the order the int8 MMA m16n8k32 takes its A fragments: for
+ * q = 0..3 and lane L = 0..31 (g = L / 4, t = L % 4) the 16 bytes at 256 + 512 q + 16 L hold word t of sub-block 2q of
+ * rows g and g + 8, then of sub-block 2q + 1 (word t of sub-block j = bytes 16 + 16 j + 4 t .. + 3 of the row's block);
+ * units ordered [row group][super-block]; rows beyond N are zero.  tiles: 16-byte aligned, bpd_q4k_rg16_bytes(N, K). */
+size_t bpd_q4k_rg16_bytes(int N, int K);
+int bpd_repack_q4k_rg16_cuda(const uint8_t* raw, uint8_t* tiles, int N, int K, void* stream);
+int bpd_unrepack_q4k_rg16_cuda(const uint8_t* tiles, uint8_t* raw, int N, int K, void* stream);
+/* out[tokens][M] = q8K(X[tokens][K]) . W^T on re-tiled weights, any number of tokens (64 per pass over the weights): a
+ * streaming kernel (every warp refills its own ring slots with 1-D bulk copies of its row group's units; quantized
+ * activations swapped through two shared-memory buffers) around mma.sync int8 MMAs; the arithmetic, order and bits of
+ * bpd_qmm_q4k_q8k_mma_cuda.  The plain form uses library-owned scratch of the stream (see "scratch memory"). */
+int bpd_qmm_q4k_q8k_rg16_cuda(const uint8_t* tiles, const float* X, float* out, int tokens, int M, int K, void* stream);
+size_t bpdq_qmm_q4k_q8k_rg16_workspace_bytes(int tokens, int K);
+int bpd_qmm_q4k_q8k_rg16_ws_cuda(const uint8_t* tiles, const float* X, float* out, int tokens, int M, int K, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+int bpd_qmm_q4k_q8k_rg16_ints_cuda(const uint8_t* tiles, const float* X, float* out, int32_t* sb_ints, int tokens, int M, int K,
+                                   void* stream);    /* + the exact (isum, msum) pairs, as the _ints forms above */
+/* Any number of independent products on re-tiled weights, each with its own X [tokens][K_j] (tokens 1..64), as one
+ * persistent launch per 128 products (plus one launch that quantizes the activations): descs[j].W = re-tiled weights,
+ * descs[j].x = X_j, out_j [tokens][M_j].  create plans and uploads the tables (it allocates device memory); workspace:
+ * bpdq_gemm_rg16_stream_workspace_bytes, 16-byte aligned, must stay allocated.  run is stream-ordered like any launch. */
+size_t bpdq_gemm_rg16_stream_workspace_bytes(int n, const bpdq_gemv_desc* descs, int tokens);
+void* bpdq_gemm_rg16_stream_create(int n, const bpdq_gemv_desc* descs, int tokens, void* workspace, size_t workspace_bytes);
+int bpdq_gemm_rg16_stream_run(void* handle, void* stream);
+int bpdq_gemm_rg16_stream_launches(void* handle);
+void bpdq_gemm_rg16_stream_destroy(void* handle);
 /* dispatch-shaped forms: argument order of gpu_vecmat (lib/kernel_templates_llama.pl:147-158)
  * and gpu_matmul (lib/kernel_templates_llama.pl:1104-1112) with the fp32 [K][N] weight
  * replaced by Q4_K rows [N][K/256][144] */

@@ -12,7 +12,7 @@
                                                     # five launches of the re-tiled product: a small case for a profiler
     python measure.py --gemm-once tc5 64 [N K]
                                                     # five launches of one many-token product (kernel
-                                                    # tc5 | mma | dispatch): a small case for a profiler
+                                                    # tc5 | mma | rg16 | dispatch): a small case for a profiler
 
 Cold-HBM protocol: every timed launch reads a different copy of its weights, with enough
 copies that the working set is several times the L2 size, so no launch finds its inputs
@@ -69,8 +69,15 @@ def _copies(nbytes, target=600e6):
 
 def gemm_once(lib, kernel, tokens, N=14336, K=4096, launches=5):
     """One Q4_K x Q8_K product, a few launches, nothing else on the device."""
-    entry = {"tc5": lib.bpd_qmm_q4k_q8k_tc5_cuda, "mma": lib.bpd_qmm_q4k_q8k_mma_cuda}.get(kernel)
+    entry = {"tc5": lib.bpd_qmm_q4k_q8k_tc5_cuda, "mma": lib.bpd_qmm_q4k_q8k_mma_cuda,
+             "rg16": lib.bpd_qmm_q4k_q8k_rg16_cuda}.get(kernel)
     w = _dev(lib, synth.q4k_matrix(N, K, 1))
+    if kernel == "rg16":            # the product on weights re-tiled in groups of 16 rows
+        t = lib.bpdq_alloc(lib.bpd_q4k_rg16_bytes(N, K))
+        capi.check(lib.bpd_repack_q4k_rg16_cuda(w, t, N, K, None))
+        lib.bpdq_sync()
+        lib.bpdq_free(w)
+        w = t
     x = _dev(lib, synth.activations(K, 2, rows=tokens))
     o = lib.bpdq_alloc(tokens * N * 4)
     for _ in range(launches):
@@ -291,9 +298,19 @@ def main():
     W = synth.q4k_matrix(N, K, 1003)
     n = _copies(W.nbytes)
     ws = [_dev(lib, W) for _ in range(n)]
-    for M in (1, 4, 16, 64):
+    # the same weights re-tiled in groups of 16 rows (one copy of each rotating matrix)
+    ts = []
+    for w in ws:
+        t = lib.bpdq_alloc(lib.bpd_q4k_rg16_bytes(N, K))
+        lib.bpd_repack_q4k_rg16_cuda(w, t, N, K, s)
+        ts.append(t)
+    lib.bpdq_stream_sync(s)
+    for M in (1, 4, 8, 16, 32, 64):
         X = _dev(lib, synth.activations(K, 1004, rows=M))
         o = lib.bpdq_alloc(M * N * 4)
+        us = tm.run(lambda i: lib.bpd_qmm_q4k_q8k_rg16_cuda(ts[i % n], X, o, M, N, K, s), 50)
+        report(f"3: same product on re-tiled weights (k_gemm_q4k_rg16), M={M}", us, synth.gemv_bytes_q4k(N, K, M),
+               tflops=round(2.0 * M * N * K / us / 1e6, 2))
         us = tm.run(lambda i: lib.bpd_qmm_q4k_q8k_cuda(ws[i % n], X, o, M, N, K, 0, 0, None, s), 50)
         report(f"3: Q4_K x Q8_K GEMM M={M} N=14336 K=4096", us, synth.gemv_bytes_q4k(N, K, M),
                tflops=round(2.0 * M * N * K / us / 1e6, 2))
@@ -310,7 +327,7 @@ def main():
     x, o = _dev(lib, synth.activations(K, 1005)), lib.bpdq_alloc(N * 4)
     us = tm.run(lambda i: lib.bpd_qmatmul_q4k_gpu_st(ws[i % n], x, o, N, K, s), 20)
     report("W4A32 GEMV 14336x4096 (bpd_qmatmul_q4k_gpu)", us, synth.gemv_bytes_q4k(N, K))
-    for p in ws + [x, o]:
+    for p in ws + ts + [x, o]:
         lib.bpdq_free(p)
     status = lib.bpdq_last_status()
     print(json.dumps({"status": status}))
