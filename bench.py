@@ -484,10 +484,10 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--schedule", default="batched", choices=["persistent", "batched", "grouped", "separate", "chain", "chain4", "chain-separate",
+    ap.add_argument("--schedule", default="persistent", choices=["persistent", "batched", "grouped", "separate", "chain", "chain4", "chain-separate",
                                                                   "chain-persistent"],
-                    help="persistent: all products of the step in one persistent launch; "
-                         "batched: the benchmark (a layer's seven independent products in one launch); grouped / "
+                    help="persistent: the benchmark (the step's independent products as persistent launches of 112 products "
+                         "whose weight stream never drains); batched: a layer's seven products per launch; grouped / "
                          "separate: fewer products per launch; chain: the seven products as a dependent decode chain, "
                          "rms_norm / SwiGLU as small kernels writing quantized records, residual add in the product's "
                          "epilogue (8 launches per layer); chain4: the steps inside the product kernels (4); "

@@ -107,6 +107,8 @@ SIGNATURES = {
     "bpdq_gemv_stream_run": (i32, [vp, vp]),
     "bpdq_gemv_stream_run_ready": (i32, [vp, vp]),
     "bpdq_gemv_stream_launches": (i32, [vp]),
+    "bpdq_gemv_stream_q8_0_workspace_bytes": (sz, [i32, vp]),
+    "bpdq_gemv_stream_create_q8_0": (vp, [i32, vp, vp, sz]),
     "bpdq_gemv_stream_destroy": (None, [vp]),
     "bpdq_chain_create": (vp, [i32, vp]),
     "bpdq_chain_run": (i32, [vp, vp]),

@@ -469,14 +469,18 @@ static int rg16_plan(const RgDesc* d, int n, int tokens, RgPlan& p, std::vector<
     // Row groups per CTA tile (= consumer warps): the SMs' warps run side by side and share the SM's issue slots and
     // bandwidth, so the time of a launch goes with (tiles per SM) x (groups per tile); among equal costs, more warps.
     const int nw_max = 10;
-    int best_nw = 1;
+    long cost_of[nw_max + 1];
     long best_cost = -1;
-    for (int w = nw_max; w >= 1; w--) {
+    for (int w = 1; w <= nw_max; w++) {
         long tiles = 0;
         for (int j = 0; j < n; j++) tiles += ((d[j].M + kRgRows - 1) / kRgRows + w - 1) / w;
-        const long cost = ((tiles + sm_count() - 1) / sm_count()) * w;
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_nw = w; }
+        cost_of[w] = ((tiles + sm_count() - 1) / sm_count()) * w;
+        if (best_cost < 0 || cost_of[w] < best_cost) best_cost = cost_of[w];
     }
+    // more warps hide the MMA's latency: the widest tile within 3 % of the cheapest
+    int best_nw = 1;
+    for (int w = nw_max; w >= 1; w--)
+        if (cost_of[w] * 100 <= best_cost * 103) { best_nw = w; break; }
     p.nw = best_nw;
     const size_t tab_bytes = ((size_t)(n + 1) * sizeof(RgProblem) + 127) / 128 * 128;
     for (;;) {

@@ -276,7 +276,7 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
 
 // Builds the launch plan for descs[0..n); returns BPDQ_ERR_RANGE when the set does not fit one
 // launch (too many activations for shared memory, or rows longer than a ring slot).
-int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt)
+int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt, int ctas_per_sm)
 {
     if (n < 1 || n > kMaxBatch) return BPDQ_ERR_RANGE;
     const Tuning& tu = tuning();
@@ -344,13 +344,20 @@ int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt)
         p.off_xq = take((size_t)xq_bytes);
         p.off_bar = take((size_t)2 * p.nw * p.slots * 8 + 8 + 64);   // barriers, then nine floats of the rms_norm prologue
         p.smem = off;
-        if (p.smem <= (size_t)kSmemLimit) break;
+        // ctas_per_sm = 2: a CTA takes less than half of the SM's shared memory (1 KB per CTA is the system's), so that
+        // the CTAs of the NEXT launch become resident while this launch still runs and have their first weight tiles in
+        // shared memory by the time the data they depend on is complete.  Measured on the dependent decode chain: slower
+        // (1.67 against 1.32 ms per token; half a ring per launch streams too slowly), so no caller asks for it.
+        const size_t limit = ctas_per_sm > 1 ? (size_t)(228 * 1024 / ctas_per_sm - 1024) : (size_t)kSmemLimit;
+        if (p.smem <= limit) break;
         if (p.slots > 2) p.slots--;
-        else if (p.nw > 4) p.nw--;
+        else if (p.nw > (ctas_per_sm > 1 ? 2 : 4)) p.nw--;
+        else if (ctas_per_sm > 1) { ctas_per_sm = 1; p.slots = tu.stages < 2 ? 2 : tu.stages; p.nw = tu.warps < 1 ? 1 : (tu.warps > 16 ? 16 : tu.warps); }
         else return BPDQ_ERR_RANGE;
     }
     long want = (p.n_tiles + p.nw - 1) / p.nw;
     if (want < 1) want = 1;
+    // (still one CTA of THIS launch per SM: the other half of the SM is for the launch behind it)
     p.grid = (int)(want < sm_count() ? want : sm_count());
     // outputs inside the range registered with bpdq_set_peer_outputs: results are stored to every target too
     p.peers.n = 0;
@@ -392,6 +399,9 @@ static int launch_batch(const BatchPlan& p, cudaStream_t s)
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+        if (rc) return rc;
+        // the SM's whole shared memory, also when one CTA asks for less than half of it (two launches side by side)
+        rc = check_cuda(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         if (rc) return rc;
         attr_set[dev] = true;
     }

@@ -445,7 +445,7 @@ unsigned long long* trace_take();
 int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M, int K, int layout, int xsrc,
                  int32_t* dbg, cudaStream_t s, Workspace* ws = nullptr);
 // gemv_batch.cu: plan and launch of the batched kernel (fmt 0: Q4_K weights, 1: Q8_0)
-int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt = 0);
+int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt = 0, int ctas_per_sm = 1);
 int launch_batch_plan(const BatchPlan& p, int fmt, int layout, cudaStream_t s);
 
 // a 256-thread kernel launched programmatically behind the launch before it

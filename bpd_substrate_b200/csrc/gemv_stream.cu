@@ -20,6 +20,9 @@
 //    the warps); a consumer warp waits for a phase's records once, when it enters the phase.  There is
 //    no CTA-wide barrier anywhere in the stream and no CTA waits for another.
 //  * The table of products (32 bytes each) sits in shared memory; a warp walks it monotonically.
+//  * A row longer than a ring slot (more than 64 super-blocks: K > 16384) is a tile of its own that arrives in
+//    pieces of 64 super-blocks, one ring turn each; the warp carries the row's partial sums from piece to piece.
+//    A lane still owns the half-blocks l, l + 32, ... of the row in ascending order: the same sums, the same bits.
 //
 // Arithmetic and accumulation order are those of the batched kernel (batch_tile): same bits.
 // Every wait is bounded; a warp that gives up records an error code and leaves.
@@ -38,7 +41,7 @@ struct StreamProblem {          // 32 bytes
     int M;
     int tile_begin;             // index of this product's first tile in the launch
     unsigned short nb;          // super-blocks per row
-    unsigned char rt, pad;      // rows per tile
+    unsigned char rt, pieces;   // rows per tile; pieces > 1: a row longer than a ring slot arrives in pieces of 64 super-blocks
     unsigned short xq_off16;    // offset of its activation records inside the phase's buffer, in 16-byte units
     unsigned short phase;
 };
@@ -69,6 +72,7 @@ struct VecEntry {               // one distinct activation vector of a stream
 // that the vectors are complete (nothing in flight writes them), so they are read and quantized at once, under
 // the tail of the launch ahead; the records are written only after that launch has completed, because it may
 // still read the same scratch.  early_read = 0: ordered like any launch.
+template <int FMT>
 __global__ void __launch_bounds__(256) k_quant_stream_records(const VecEntry* __restrict__ table, int n_vec, int total_blocks,
                                                                uint8_t* __restrict__ records, int early_read)
 {
@@ -97,21 +101,68 @@ __global__ void __launch_bounds__(256) k_quant_stream_records(const VecEntry* __
                 const float4* xb = reinterpret_cast<const float4*>(e.x + (size_t)blk * 256);
                 v0[u] = __ldcg(xb + lane);
                 v1[u] = __ldcg(xb + 32 + lane);
-                dst[u] = records + e.rec_off + (size_t)(2 * blk) * kXqStride;
+                dst[u] = records + e.rec_off + (FMT == 0 ? (size_t)(2 * blk) * kXqStride : (size_t)(4 * blk) * kQ80PairStride);
             }
         }
         if (early_read) pdl_wait();      // (returns at once after the first time)
 #pragma unroll
-        for (int u = 0; u < kHold; u++)
-            if (dst[u]) write_records(v0[u], v1[u], dst[u], lane);
+        for (int u = 0; u < kHold; u++) {
+            if (!dst[u]) continue;
+            if (FMT == 0) write_records(v0[u], v1[u], dst[u], lane);
+            else write_records_q80(v0[u], v1[u], dst[u], lane);
+        }
     }
     if (early_read) pdl_wait();          // a warp without blocks still joins the stream order
 }
 
-template <int LAYOUT, int ACC>
+// One piece (nsb super-blocks, in shared memory) of a long row against the records of the same K range: lane l
+// adds the piece's half-blocks l, l + 32, ... to the row's running sum.
+template <int LAYOUT>
+__device__ __forceinline__ void row_piece(const uint8_t* piece, const uint8_t* xq, int nsb, int lane, float (&acc)[1])
+{
+    for (int hb = lane; hb < 2 * nsb; hb += 32) {
+        const uint4* rec = reinterpret_cast<const uint4*>(xq + (size_t)hb * kXqStride);
+        uint32_t xr[1][32];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint4 v = rec[i];
+            xr[0][4 * i + 0] = v.x;
+            xr[0][4 * i + 1] = v.y;
+            xr[0][4 * i + 2] = v.z;
+            xr[0][4 * i + 3] = v.w;
+        }
+        const uint4 tail = rec[8];
+        int bs[1][4];
+        bs[0][0] = (int)(short)(tail.x & 0xFFFFu);
+        bs[0][1] = (int)(short)(tail.x >> 16);
+        bs[0][2] = (int)(short)(tail.y & 0xFFFFu);
+        bs[0][3] = (int)(short)(tail.y >> 16);
+        float xd[1] = {__uint_as_float(tail.z)};
+        half_block_fma<1, LAYOUT>(piece + (size_t)(hb >> 1) * BPDQ_Q4K_BYTES, hb & 1, xr, bs, xd, acc, nullptr);
+    }
+}
+// The end of a row that arrived in pieces: batch_tile<1>'s fold over the lanes and its store (peer targets included).
+template <int ACC>
+__device__ __forceinline__ void store_row(float partial, const BatchProblem& pb, int row0, int lane, const PeerTargets* peers)
+{
+    const float v[1] = {partial};
+    const float total = fold_rows<1>(v, lane);
+    if constexpr (ACC == 2) {
+        const float val = __shfl_sync(0xFFFFFFFFu, total, 0);
+        if (lane <= peers->n)
+            *reinterpret_cast<float*>(reinterpret_cast<char*>(pb.out + row0) + (lane == 0 ? 0ll : peers->shift[lane > 0 ? lane - 1 : 0])) = val;
+    } else {
+        if (lane == 0) pb.out[row0] = total;
+    }
+}
+
+// FMT 0: Q4_K weights against Q8_K records; FMT 1: Q8_0 weights (rows of 34-byte blocks, K a multiple of 256) against
+// Q8_0 pair records -- the two modes of the batched kernel.
+template <int FMT, int LAYOUT, int ACC>
 __global__ void __launch_bounds__(kMidCtaThreads, 1)
 k_gemv_stream_q4k_q8k(const StreamPlan p, int* __restrict__ err)
 {
+    constexpr int kRowUnit = FMT == 0 ? BPDQ_Q4K_BYTES : 8 * BPDQ_Q80_BYTES;     // bytes of 256 weights
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem + p.off_ring;                                            // [nw][slots][slot_bytes]
     uint8_t* xq = smem + p.off_xq;                                                // [2][xq_bytes]
@@ -164,20 +215,30 @@ k_gemv_stream_q4k_q8k(const StreamPlan p, int* __restrict__ err)
     uint8_t* my_ring = ring + (size_t)warp * p.slots * p.slot_bytes;
     uint64_t* my_full = full + warp * p.slots;
 
-    // the tile this warp will LOAD next (runs `slots` tiles ahead of the one it computes)
-    int lg = first, lj = 0;
+    // the tile (and piece of it) this warp will LOAD next: runs `slots` ring turns ahead of the one it computes
+    constexpr int kPieceSb = 64;                   // super-blocks per piece of a long row
+    int lg = first, lj = 0, lpiece = 0;
     auto issue = [&](int slot) {
         // all lanes walk the table (uniform); lane 0 issues
         while (lg >= prob[lj + 1].tile_begin) lj++;
         const StreamProblem& q = prob[lj];
-        const int row_bytes = (int)q.nb * BPDQ_Q4K_BYTES;
+        const int row_bytes = (int)q.nb * kRowUnit;
         const int row0 = (lg - q.tile_begin) * (int)q.rt;
-        const uint32_t bytes = (uint32_t)min((int)q.rt, q.M - row0) * (uint32_t)row_bytes;
+        uint32_t bytes = (uint32_t)min((int)q.rt, q.M - row0) * (uint32_t)row_bytes;
+        size_t at = (size_t)row0 * row_bytes;
+        if (q.pieces > 1) {
+            const int sb0 = lpiece * kPieceSb;
+            bytes = (uint32_t)min(kPieceSb, (int)q.nb - sb0) * kRowUnit;
+            at += (size_t)sb0 * kRowUnit;
+        }
         if (lane == 0) {
             mbar_expect_tx(&my_full[slot], bytes);
-            bulk_g2s(my_ring + (size_t)slot * p.slot_bytes, q.W + (size_t)row0 * row_bytes, bytes, &my_full[slot]);
+            bulk_g2s(my_ring + (size_t)slot * p.slot_bytes, q.W + at, bytes, &my_full[slot]);
         }
-        lg += W;
+        if (++lpiece >= (int)q.pieces) {
+            lpiece = 0;
+            lg += W;
+        }
     };
     for (int k = 0; k < p.slots && lg < p.n_tiles; k++) issue(k);    // weights never depend on the launch before
 
@@ -213,22 +274,48 @@ k_gemv_stream_q4k_q8k(const StreamPlan p, int* __restrict__ err)
             leave_phase();
         }
         if (!ok || !(ok = enter_phase())) break;
-        if (!(ok = mbar_wait_bounded(&my_full[slot], parity, err, 2))) break;
         BatchProblem pb;
         pb.W = q.W;
         pb.out = q.out;
         pb.M = q.M;
         pb.nb = q.nb;
-        pb.row_bytes = (int)q.nb * BPDQ_Q4K_BYTES;
+        pb.row_bytes = (int)q.nb * kRowUnit;
         pb.rt = q.rt;
         pb.accumulate = 0;
         const int row0 = (g - q.tile_begin) * (int)q.rt;
-        const uint8_t* tile_smem = my_ring + (size_t)slot * p.slot_bytes;
         const uint8_t* rec = xq + (size_t)(ph & 1) * p.xq_bytes + (size_t)q.xq_off16 * 16;
         const PeerTargets* peers = ACC == 2 ? &p.peers : nullptr;
-        if (q.rt == 4) batch_tile<4, LAYOUT, ACC>(tile_smem, rec, pb, row0, lane, peers);
-        else if (q.rt == 2) batch_tile<2, LAYOUT, ACC>(tile_smem, rec, pb, row0, lane, peers);
-        else batch_tile<1, LAYOUT, ACC>(tile_smem, rec, pb, row0, lane, peers);
+        if (FMT == 0 && q.pieces > 1) {
+            // one long row, piece by piece: lane l adds its half-blocks l, l + 32, ... of the row in ascending order
+            float acc[1] = {0.0f};
+            for (int piece = 0; piece < (int)q.pieces && ok; piece++) {
+                if (!(ok = mbar_wait_bounded(&my_full[slot], parity, err, 2))) break;
+                const uint8_t* tile_smem = my_ring + (size_t)slot * p.slot_bytes;
+                const int sb0 = piece * kPieceSb, nsb = min(kPieceSb, (int)q.nb - sb0);
+                row_piece<LAYOUT>(tile_smem, rec + (size_t)(2 * sb0) * kXqStride, nsb, lane, acc);
+                __syncwarp();
+                if (lg < p.n_tiles) issue(slot);
+                if (++slot == p.slots) {
+                    slot = 0;
+                    parity ^= 1u;
+                }
+            }
+            if (!ok) break;
+            store_row<ACC>(acc[0], pb, row0, lane, peers);
+            continue;
+        }
+        if (!(ok = mbar_wait_bounded(&my_full[slot], parity, err, 2))) break;
+        const uint8_t* tile_smem = my_ring + (size_t)slot * p.slot_bytes;
+        if constexpr (FMT == 0) {
+            if (q.rt == 4) batch_tile<4, LAYOUT, ACC>(tile_smem, rec, pb, row0, lane, peers);
+            else if (q.rt == 2) batch_tile<2, LAYOUT, ACC>(tile_smem, rec, pb, row0, lane, peers);
+            else batch_tile<1, LAYOUT, ACC>(tile_smem, rec, pb, row0, lane, peers);
+        } else {
+            (void)peers;
+            if (q.rt == 4) batch_tile_q80<4>(tile_smem, rec, pb, row0, lane);
+            else if (q.rt == 2) batch_tile_q80<2>(tile_smem, rec, pb, row0, lane);
+            else batch_tile_q80<1>(tile_smem, rec, pb, row0, lane);
+        }
         // every lane has read the slot (its values went into the row sums that were folded over the lanes and
         // stored): the slot can take the tile this warp needs `slots` turns from now
         __syncwarp();
@@ -255,7 +342,7 @@ struct StreamLaunch {
 struct StreamHandle {
     std::vector<StreamLaunch> launches;
     uint8_t* records;
-    int device;
+    int device, fmt;
 };
 
 static void stream_destroy(StreamHandle* h)
@@ -271,25 +358,29 @@ static void stream_destroy(StreamHandle* h)
 
 // Plans `n` independent products as launches of at most kStreamMaxProblems consecutive products, each cut into
 // record phases; lays the records out in `ws` and uploads the tables.
-static StreamHandle* stream_create(int n, const BatchDesc* d, uint8_t* ws, size_t ws_bytes)
+static StreamHandle* stream_create(int n, const BatchDesc* d, uint8_t* ws, size_t ws_bytes, int fmt)
 {
-    if (n < 1 || !d || !ws || ((uintptr_t)ws & 15)) { latch(BPDQ_ERR_ARG); return nullptr; }
+    if (n < 1 || !d || !ws || ((uintptr_t)ws & 15) || (fmt != 0 && fmt != 1)) { latch(BPDQ_ERR_ARG); return nullptr; }
     const Tuning& tu = tuning();
+    const int row_unit = fmt == 0 ? BPDQ_Q4K_BYTES : 8 * BPDQ_Q80_BYTES;                 // bytes of 256 weights
+    const int rec_unit = fmt == 0 ? 2 * kXqStride : 4 * kQ80PairStride;                  // record bytes of 256 activations
     size_t stream_bytes = 0;
     int biggest_vec = 0;
     for (int j = 0; j < n; j++) {
         const BatchDesc& q = d[j];
         if (q.M <= 0 || q.K <= 0 || (q.K % 256) != 0 || !q.W || !q.x || !q.out) { latch(BPDQ_ERR_ARG); return nullptr; }
         if (((uintptr_t)q.W & 15) || ((uintptr_t)q.x & 15) || ((uintptr_t)q.out & 3)) { latch(BPDQ_ERR_ALIGN); return nullptr; }
-        if (q.K / 256 * BPDQ_Q4K_BYTES > 32 * 1024) { latch(BPDQ_ERR_RANGE); return nullptr; }
-        stream_bytes += (size_t)q.M * (q.K / 256) * BPDQ_Q4K_BYTES;
-        if (q.K / 128 * kXqStride > biggest_vec) biggest_vec = q.K / 128 * kXqStride;
+        if (q.K / 256 > 255 * 64 || (fmt == 1 && q.K / 256 * row_unit > 32 * 1024)) { latch(BPDQ_ERR_RANGE); return nullptr; }
+        stream_bytes += (size_t)q.M * (q.K / 256) * row_unit;
+        if (q.K / 256 * rec_unit > biggest_vec) biggest_vec = q.K / 256 * rec_unit;
     }
-    const int tile_budget = (stream_bytes >= kBigLaunchBytes && tu.tile_bytes < kBigLaunchTileBytes) ? kBigLaunchTileBytes : tu.tile_bytes;
+    const int tile_budget = (stream_bytes >= (fmt == 0 ? kBigLaunchBytes : kBigLaunchBytesQ80) && tu.tile_bytes < kBigLaunchTileBytes)
+                                ? kBigLaunchTileBytes : tu.tile_bytes;
     // one record buffer: 20 KB, or the largest single vector
     const int xq_cap = biggest_vec > 20 * 1024 ? (biggest_vec + 127) / 128 * 128 : 20 * 1024;
     StreamHandle* h = new StreamHandle();
     h->records = ws;
+    h->fmt = fmt;
     cudaGetDevice(&h->device);
     size_t ws_used = 0;
     // as few launches as the table size allows, of equal length
@@ -310,7 +401,7 @@ static StreamHandle* stream_create(int n, const BatchDesc* d, uint8_t* ws, size_
         peers.n = 0;
         for (int j = 0; j < cnt; j++) {
             const BatchDesc& q = d[i0 + j];
-            const int nb = q.K / 256, row_bytes = nb * BPDQ_Q4K_BYTES, rec = 2 * nb * kXqStride;
+            const int nb = q.K / 256, row_bytes = nb * row_unit, rec = nb * rec_unit;
             size_t k = vec_first;
             for (; k < table.size(); k++)
                 if (table[k].x == q.x && table[k].nb == nb) break;
@@ -340,13 +431,15 @@ static StreamHandle* stream_create(int n, const BatchDesc* d, uint8_t* ws, size_
             pb.tile_begin = n_tiles;
             pb.nb = (unsigned short)nb;
             pb.rt = (unsigned char)(4 * row_bytes <= tile_budget ? 4 : (2 * row_bytes <= tile_budget ? 2 : 1));
-            pb.pad = 0;
+            // Q4_K rows of more than 64 super-blocks arrive in pieces of 64 (9216 bytes), so the ring slots stay small
+            pb.pieces = (unsigned char)((fmt == 0 && nb > 64) ? (nb + 63) / 64 : 1);
             pb.xq_off16 = (unsigned short)((table[k].rec_off - phases.back().rec_off) / 16);
             pb.phase = (unsigned short)(phases.size() - 1);
             n_tiles += (q.M + pb.rt - 1) / pb.rt;
-            if ((int)pb.rt * row_bytes > slot_bytes) slot_bytes = (int)pb.rt * row_bytes;
+            const int tile_bytes = pb.pieces > 1 ? 64 * row_unit : (int)pb.rt * row_bytes;
+            if (tile_bytes > slot_bytes) slot_bytes = tile_bytes;
             PeerTargets t;
-            if (plain && peer_targets_for(q.out, q.out + q.M, t)) peers = t;
+            if (plain && fmt == 0 && peer_targets_for(q.out, q.out + q.M, t)) peers = t;
             else plain = false;
         }
         phases.back().rec_bytes = (unsigned)ph_bytes;
@@ -409,10 +502,10 @@ static StreamHandle* stream_create(int n, const BatchDesc* d, uint8_t* ws, size_
     return h;
 }
 
-template <int ACC>
+template <int FMT, int ACC>
 static int launch_stream(const StreamPlan& plan, cudaStream_t s)
 {
-    auto kern = k_gemv_stream_q4k_q8k<BPDQ_LAYOUT_BPD, ACC>;
+    auto kern = k_gemv_stream_q4k_q8k<FMT, BPDQ_LAYOUT_BPD, ACC>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -443,10 +536,12 @@ static int stream_run(StreamHandle* h, int early_read, cudaStream_t s)
     cudaGetDevice(&dev);
     if (dev != h->device) return latch(BPDQ_ERR_ARG);
     for (auto& L : h->launches) {
-        int rc = launch_glue(k_quant_stream_records, glue_grid(L.total_blocks), s, (const VecEntry*)L.d_table, L.n_vec, L.total_blocks,
-                             const_cast<uint8_t*>(L.plan.records), early_read);
+        int rc = h->fmt == 0 ? launch_glue(k_quant_stream_records<0>, glue_grid(L.total_blocks), s, (const VecEntry*)L.d_table, L.n_vec,
+                                           L.total_blocks, const_cast<uint8_t*>(L.plan.records), early_read)
+                             : launch_glue(k_quant_stream_records<1>, glue_grid(L.total_blocks), s, (const VecEntry*)L.d_table, L.n_vec,
+                                           L.total_blocks, const_cast<uint8_t*>(L.plan.records), early_read);
         if (rc) return latch(rc);
-        rc = L.plan.peers.n > 0 ? launch_stream<2>(L.plan, s) : launch_stream<0>(L.plan, s);
+        rc = h->fmt == 1 ? launch_stream<1, 0>(L.plan, s) : (L.plan.peers.n > 0 ? launch_stream<0, 2>(L.plan, s) : launch_stream<0, 0>(L.plan, s));
         if (rc) return latch(rc);
     }
     return 0;
@@ -460,7 +555,20 @@ extern "C" {
 
 void* bpdq_gemv_stream_create(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes)
 {
-    return stream_create(n, reinterpret_cast<const BatchDesc*>(descs), (uint8_t*)workspace, workspace_bytes);
+    return stream_create(n, reinterpret_cast<const BatchDesc*>(descs), (uint8_t*)workspace, workspace_bytes, 0);
+}
+
+// The same stream for Q8_0 weights (rows of 34-byte blocks, K a multiple of 256; descs[j].W = the Q8_0 rows): the
+// product of bpd_qmatmul_q8_0_cuda at one token, many matrices per launch.  Workspace: bpdq_gemv_stream_q8_0_workspace_bytes.
+size_t bpdq_gemv_stream_q8_0_workspace_bytes(int n, const bpdq_gemv_desc* descs)
+{
+    size_t total = 0;
+    for (int j = 0; j < n; j++) total += (size_t)(descs[j].K / 256) * 4 * kQ80PairStride + 128;
+    return total;
+}
+void* bpdq_gemv_stream_create_q8_0(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes)
+{
+    return stream_create(n, reinterpret_cast<const BatchDesc*>(descs), (uint8_t*)workspace, workspace_bytes, 1);
 }
 
 int bpdq_gemv_stream_run(void* handle, void* stream) { return stream_run((StreamHandle*)handle, 0, (cudaStream_t)stream); }

@@ -208,6 +208,10 @@ int bpdq_gemv_stream_run(void* handle, void* stream);
 int bpdq_gemv_stream_run_ready(void* handle, void* stream);
 int bpdq_gemv_stream_launches(void* handle);
 void bpdq_gemv_stream_destroy(void* handle);
+/* the same stream for Q8_0 weights (bench/bpd_cpu.c:4295-4315 at one activation row, many matrices per launch):
+ * descs[j].W = Q8_0 rows [M][K/32][34], K a multiple of 256; run / run_ready / destroy as above */
+size_t bpdq_gemv_stream_q8_0_workspace_bytes(int n, const bpdq_gemv_desc* descs);
+void* bpdq_gemv_stream_create_q8_0(int n, const bpdq_gemv_desc* descs, void* workspace, size_t workspace_bytes);
 
 /* ---- Decode glue.  Replaces, around the products of a decoder layer, the separate elementwise
  * launches of the reference's decode loop (inference/llamatov_gpu_llama.py:119-166: gpu_rms_norm,

@@ -290,6 +290,15 @@ def main():
     us = tm.run(lambda i: lib.bpdq_graph_launch(g, s), 50) / n32
     report("1: Q8_0 GEMV 4096x4096 (32 distinct matrices per graph replay, per product)", us, synth.gemv_bytes_q8_0(N, K))
     lib.bpdq_graph_destroy(g)
+    # and as ONE persistent launch of the stream kernel in its Q8_0 mode
+    descs = (capi.GemvDesc * n32)(*[capi.GemvDesc(ws32[j], xs32[j], os32[j], N, K) for j in range(n32)])
+    sbytes = lib.bpdq_gemv_stream_q8_0_workspace_bytes(n32, descs)
+    sws = lib.bpdq_alloc(sbytes)
+    plan = lib.bpdq_gemv_stream_create_q8_0(n32, descs, sws, sbytes)
+    us = tm.run(lambda i: lib.bpdq_gemv_stream_run_ready(plan, s), 50) / n32
+    report("1: Q8_0 GEMV 4096x4096 (32 distinct matrices in one persistent launch, per product)", us, synth.gemv_bytes_q8_0(N, K))
+    lib.bpdq_gemv_stream_destroy(plan)
+    lib.bpdq_free(sws)
     for p in list(set(ws32) | set(ws)) + xs32 + os32 + [x, o]:
         lib.bpdq_free(p)
 

@@ -64,8 +64,8 @@ def test_whole_mistral_layer_in_one_batched_launch(lib, oracle):
 @pytest.mark.parametrize("tokens", [1, 4, 16, 64])
 def test_config3_14336x4096_every_kernel(lib, oracle, tokens):
     """Benchmark configuration 3 (N = 14336, K = 4096) at 1, 4, 16, 64 tokens: the dispatcher, the dp4a kernel
-    (up to 4 tokens: exact sub-block dots of token 0), the mma.sync kernel and the tcgen05 kernel (exact
-    (isum, msum) of every token, row and super-block)."""
+    (up to 4 tokens: exact sub-block dots of token 0), the mma.sync kernel, the tcgen05 kernel and the streaming
+    kernel on re-tiled weights (exact (isum, msum) of every token, row and super-block)."""
     N, K = 14336, 4096
     rng = np.random.default_rng(300 + tokens)
     W = synth.q4k_matrix(N, K, rng)
@@ -84,13 +84,17 @@ def test_config3_14336x4096_every_kernel(lib, oracle, tokens):
             rc = lib.bpd_qmm_q4k_q8k_cuda(dW.ptr, dX.ptr, dO.ptr, tokens, N, K, 0, 0, dI.ptr, None)
         else:
             dI = Dev(lib, nbytes=tokens * N * (K // 256) * 2 * 4, fill=0xEE)
-            rc = getattr(lib, f"bpd_qmm_q4k_q8k_{entry}_ints_cuda")(dW.ptr, dX.ptr, dO.ptr, dI.ptr, tokens, N, K, None)
+            w = dT if entry == "rg16" else dW     # the product on weights re-tiled in groups of 16 rows
+            rc = getattr(lib, f"bpd_qmm_q4k_q8k_{entry}_ints_cuda")(w.ptr, dX.ptr, dO.ptr, dI.ptr, tokens, N, K, None)
         assert rc == 0
         lib.bpdq_sync()
         assert lib.bpdq_last_status() == 0
         return dO.read(np.float32).reshape(tokens, N), dI
 
-    for entry in ("dispatch", "mma", "tc5") + (("dp4a",) if tokens <= 4 else ()):
+    dT = Dev(lib, nbytes=lib.bpd_q4k_rg16_bytes(N, K))
+    assert lib.bpd_repack_q4k_rg16_cuda(dW.ptr, dT.ptr, N, K, None) == 0
+
+    for entry in ("dispatch", "mma", "tc5", "rg16") + (("dp4a",) if tokens <= 4 else ()):
         out, dI = run(entry)
         assert normwise(out, ref64) <= TOL, entry
         if entry == "dp4a":
@@ -140,6 +144,36 @@ def test_llama70b_row_shards(lib, oracle):
     assert normwise(head, oracle.qmatmul_q4k_q8k(W, oracle.quant_q8_K(x), r, cols)[1]) <= TOL
 
 
+def test_llama70b_shard_as_one_persistent_stream(lib, oracle):
+    """The same shard through bpdq_gemv_stream_run: the rows of K = 28672 (112 super-blocks) arrive in two pieces per
+    row; every output equals the batched entry's bit for bit and the checker's within the bar."""
+    rng = np.random.default_rng(72)
+    world = 8
+    mats = []
+    for _, rows, cols in synth.LLAMA70B_LAYER:
+        r = rows // world
+        mats.append((synth.q4k_matrix(r, cols, rng), synth.activations(cols, rng), r, cols))
+    want = _batched(lib, "bpd_qmatmul_q4k_q8k_batch_ws_cuda", mats)
+    dW = [Dev(lib, w) for w, _, _, _ in mats]
+    dX = [Dev(lib, x) for _, x, _, _ in mats]
+    dO = [Dev(lib, nbytes=rows * 4, fill=0xFF) for _, _, rows, _ in mats]
+    n = len(mats)
+    descs = (capi.GemvDesc * n)(*[capi.GemvDesc(dW[j].ptr, dX[j].ptr, dO[j].ptr, rows, cols)
+                                  for j, (_, _, rows, cols) in enumerate(mats)])
+    nbytes = lib.bpdq_batch_workspace_bytes(n, descs)
+    ws = Dev(lib, nbytes=nbytes, fill=0xCD)
+    h = lib.bpdq_gemv_stream_create(n, descs, ws.ptr, nbytes)
+    assert h
+    assert lib.bpdq_gemv_stream_run(h, None) == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == 0
+    for j, (W, x, rows, cols) in enumerate(mats):
+        got = dO[j].read(np.float32)
+        assert np.array_equal(got.view(np.uint32), want[j].view(np.uint32)), j
+        assert normwise(got, oracle.qmatmul_q4k_q8k(W, oracle.quant_q8_K(x), rows, cols)[1]) <= TOL, j
+    lib.bpdq_gemv_stream_destroy(h)
+
+
 def test_llama70b_shard_eight_tokens(lib, oracle):
     """Configuration 4 at batch 8: the w1 shard (3584 x 8192) and the w2 shard (1024 x 28672) at eight tokens
     through the dispatcher."""
@@ -153,3 +187,12 @@ def test_llama70b_shard_eight_tokens(lib, oracle):
         assert lib.bpdq_last_status() == 0
         _, ref64 = oracle.qmm_q4k_q8k(W, X, 8, rows, cols)
         assert normwise(dO.read(np.float32).reshape(8, rows), ref64) <= TOL, (rows, cols)
+        # and on the weights re-tiled in groups of 16 rows (what the 8-token sweep of the benchmark runs)
+        dT = Dev(lib, nbytes=lib.bpd_q4k_rg16_bytes(rows, cols))
+        assert lib.bpd_repack_q4k_rg16_cuda(dW.ptr, dT.ptr, rows, cols, None) == 0
+        dI = Dev(lib, nbytes=8 * rows * (cols // 256) * 8, fill=0xEE)
+        assert lib.bpd_qmm_q4k_q8k_rg16_ints_cuda(dT.ptr, dX.ptr, dO.ptr, dI.ptr, 8, rows, cols, None) == 0
+        lib.bpdq_sync()
+        assert lib.bpdq_last_status() == 0
+        assert normwise(dO.read(np.float32).reshape(8, rows), ref64) <= TOL, (rows, cols)
+        assert np.array_equal(dI.read(np.int32).reshape(8, rows, cols // 256, 2), oracle.qmm_q4k_q8k_ints(W, X, 8, rows, cols))

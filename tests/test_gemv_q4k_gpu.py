@@ -334,6 +334,14 @@ def test_long_stream_many_phases_and_two_launches(lib, oracle):
         for o in outs:
             lib.bpdq_memset_async(o.ptr, 0xFF, o.nbytes, None)
     lib.bpdq_gemv_stream_destroy(h)
+    # rows of K = 28672 arrive in two pieces per ring turn: still the bits of the batched entry
+    for j in (6, 13):
+        m, k = shapes[j]
+        o = Dev(lib, nbytes=m * 4, fill=0xFF)
+        one = (capi.GemvDesc * 1)(capi.GemvDesc(dW[j].ptr, dX[j].ptr, o.ptr, m, k))
+        assert lib.bpd_qmatmul_q4k_q8k_batch_cuda(1, one, None) == 0
+        lib.bpdq_sync()
+        assert np.array_equal(o.read(np.uint32), first[j].view(np.uint32)), j
     # too small a workspace is refused
     assert not lib.bpdq_gemv_stream_create(n, descs, ws.ptr, 1024)
     lib.bpdq_clear_status()

@@ -199,3 +199,37 @@ def test_embed_lookup_refuses_out_of_range_ids(lib, oracle):
     assert lib.bpdq_last_status() == -4
     lib.bpdq_clear_status()
     assert (dO.read(np.uint32).reshape(5, 512)[3] == 0xCDCDCDCD).all()
+
+
+def test_stream_of_q8_0_products(lib, oracle):
+    """40 independent Q8_0 products (several shapes, own vectors) as one persistent launch: the bits of
+    bpd_qmatmul_q8_0_cuda product by product, and the checker's binary64 result within the bar."""
+    from bpd_substrate_b200 import capi
+    rng = np.random.default_rng(66)
+    kinds = [(300, 4096), (64, 1024), (17, 14336), (500, 256), (128, 8192)]
+    Ws = [synth.q8_0_matrix(m, k, rng) for m, k in kinds]
+    dWs = [Dev(lib, w) for w in Ws]
+    shapes = [kinds[j % len(kinds)] for j in range(40)]
+    xs = [synth.activations(k, rng) for _, k in shapes]
+    dXs = [Dev(lib, x) for x in xs]
+    outs = [Dev(lib, nbytes=m * 4, fill=0xFF) for m, _ in shapes]
+    n = len(shapes)
+    descs = (capi.GemvDesc * n)(*[capi.GemvDesc(dWs[j % len(kinds)].ptr, dXs[j].ptr, outs[j].ptr, m, k)
+                                  for j, (m, k) in enumerate(shapes)])
+    nbytes = lib.bpdq_gemv_stream_q8_0_workspace_bytes(n, descs)
+    ws = Dev(lib, nbytes=nbytes, fill=0xCD)
+    h = lib.bpdq_gemv_stream_create_q8_0(n, descs, ws.ptr, nbytes)
+    assert h
+    for run in (lib.bpdq_gemv_stream_run, lib.bpdq_gemv_stream_run_ready):
+        for o in outs:
+            lib.bpdq_memset_async(o.ptr, 0xFF, o.nbytes, None)
+        assert run(h, None) == 0
+        lib.bpdq_sync()
+        assert lib.bpdq_last_status() == 0
+        for j, (m, k) in enumerate(shapes):
+            got = outs[j].read(np.float32)
+            single = gpu_matmul(lib, Ws[j % len(kinds)], xs[j], 1, m, k)[0]
+            assert np.array_equal(got.view(np.uint32), single.view(np.uint32)), j
+            if j < 10:
+                assert normwise(got, oracle.qmatmul_q8_0_f64(Ws[j % len(kinds)], xs[j], 1, m, k)[0]) <= TOL
+    lib.bpdq_gemv_stream_destroy(h)
