@@ -167,7 +167,8 @@ __global__ void __launch_bounds__(256) k_quant_rg16_records(const RgVec* __restr
 
 __device__ __forceinline__ void rg_mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
-    asm volatile(
+    // (not volatile: a pure function of its operands, so that independent MMAs can be scheduled back to back)
+    asm(
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
@@ -333,26 +334,40 @@ k_gemm_q4k_rg16(const RgPlan p, int* __restrict__ err)
                 for (int n = 0; n < NT; n++)
 #pragma unroll
                     for (int i = 0; i < 4; i++) isum[n][i] = 0;
+                // The MMAs of a group of sub-blocks are issued back to back, each into its own registers, and only then
+                // are their results scaled and added: the tensor pipe's latency is paid once per group, not per MMA.
+                constexpr int GS = NT == 1 ? 8 : (NT == 2 ? 4 : 2);          // sub-blocks per group
 #pragma unroll
-                for (int qq = 0; qq < 4; qq++) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(unit + 256 + 512 * qq + 16 * lane);
-                    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                for (int j0 = 0; j0 < 8; j0 += GS) {
+                    int c[GS][NT][4];
 #pragma unroll
-                    for (int e2 = 0; e2 < 2; e2++) {
-                        const int j = 2 * qq + e2;
-                        const uint32_t wa = ww[2 * e2], wb = ww[2 * e2 + 1];
+                    for (int jj = 0; jj < GS; jj += 2) {
+                        const int qq = (j0 + jj) >> 1;
+                        const uint4 wv = *reinterpret_cast<const uint4*>(unit + 256 + 512 * qq + 16 * lane);
+                        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                        for (int e2 = 0; e2 < 2; e2++) {
+                            const int j = j0 + jj + e2;
+                            const uint32_t wa = ww[2 * e2], wb = ww[2 * e2 + 1];
+                            // fragment order: {row g k 0-15, row g+8 k 0-15, row g k 16-31, row g+8 k 16-31}
+                            const uint32_t af[4] = {wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, (wa >> 4) & 0x0F0F0F0Fu, (wb >> 4) & 0x0F0F0F0Fu};
+#pragma unroll
+                            for (int n = 0; n < NT; n++) {
+                                const uint2 bf = *reinterpret_cast<const uint2*>(xa + (size_t)(8 * n + g) * kRgActPitch + 32 * j + 8 * t);
+                                rg_mma_s8(c[jj + e2][n], af, bf.x, bf.y);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < GS; jj++) {
+                        const int j = j0 + jj;
                         const int sa = (int)byte_of(sca[j >> 2], j & 3), sb_ = (int)byte_of(scb[j >> 2], j & 3);
-                        // fragment order: {row g k 0-15, row g+8 k 0-15, row g k 16-31, row g+8 k 16-31}
-                        const uint32_t af[4] = {wa & 0x0F0F0F0Fu, wb & 0x0F0F0F0Fu, (wa >> 4) & 0x0F0F0F0Fu, (wb >> 4) & 0x0F0F0F0Fu};
 #pragma unroll
                         for (int n = 0; n < NT; n++) {
-                            const uint2 bf = *reinterpret_cast<const uint2*>(xa + (size_t)(8 * n + g) * kRgActPitch + 32 * j + 8 * t);
-                            int c[4];
-                            rg_mma_s8(c, af, bf.x, bf.y);
-                            isum[n][0] += sa * c[0];
-                            isum[n][1] += sa * c[1];
-                            isum[n][2] += sb_ * c[2];
-                            isum[n][3] += sb_ * c[3];
+                            isum[n][0] += sa * c[jj][n][0];
+                            isum[n][1] += sa * c[jj][n][1];
+                            isum[n][2] += sb_ * c[jj][n][2];
+                            isum[n][3] += sb_ * c[jj][n][3];
                         }
                     }
                 }

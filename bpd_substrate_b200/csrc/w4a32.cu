@@ -10,9 +10,10 @@
 //   and within one its 128 elements in ascending order, acc = fma(w, x, acc); lanes are then
 //   added by a butterfly (xor 16, 8, 4, 2, 1).
 //
-// The GEMV fast path (k_w4a32_ring) streams the weights through per-warp ring slots as the W4A8 kernels do
-// and spends 2.5 instructions per weight; it is bound by instruction issue, not by HBM (the bandwidth-bound
-// GEMV is the Q8_K-activation kernel).  Its accumulation order is described at the kernel.
+// The GEMV fast path (k_w4a32_ring) streams the weights through per-warp ring slots as the W4A8 kernels do and
+// multiplies them with a 24-bit block-fixed-point copy of the activations, exactly, by integer dot products; its
+// arithmetic and accumulation order are described at the kernel.  The generic kernels below (several activation
+// vectors, strided activations) multiply in fp32, weight by weight.
 #include "bpdq_common.cuh"
 #include "../../include/bpdq.h"
 
@@ -143,21 +144,24 @@ __global__ void __launch_bounds__(256) k_w4a32_gemv(const uint8_t* __restrict__ 
     }
 }
 
-// ---- GEMV fast path: weights through the shared-memory ring.
+// ---- GEMV fast path: weights through the shared-memory ring, activations as 24-bit block fixed point.
 //
 // Structure: one CTA per SM, nw warps, each with its own ring slots that it refills itself with 1-D bulk copies of
-// tiles of R whole rows (gemv_batch.cu's scheme).  The activation vector sits in shared memory as fp32, every
-// half-super-block's 128 floats padded to 132 so that the 16-byte reads of 32 lanes hit distinct banks, next to the
-// sum of every sub-block's 32 activations (S0).
-// Arithmetic per row: lane l takes half-super-blocks l, l + 32, ... in ascending order; per sub-block
-//     S1' = sum_k (1 + q_k / 16) * x_k      (the nibble goes into the top mantissa bits of 1.0f with two bit
-//                                            operations per four weights and one byte permute per weight: no
-//                                            conversion, no subtraction per weight)
-//     acc = fma(16 * d * sc, S1' - S0, acc);  acc = fma(-(dmin * mn), S0, acc)
-// i.e. sum q*x = 16 (S1' - S0) with S0 summed once per launch; lanes are added by fold_rows' fixed butterfly.
-// Against the reference's strictly sequential fp32 sum and against binary64 the result agrees to ~1e-6 norm-wise
-// (the stated bar is 1e-5): the re-association costs about one more bit than the per-weight form.
-constexpr int kW4XPad = 132;            // floats per half-super-block of x in shared memory
+// tiles of R whole rows (gemv_batch.cu's scheme).
+//
+// Arithmetic.  Multiplying every 4-bit weight with an fp32 activation costs a conversion and an FMA per weight, which
+// is more than HBM leaves time for.  Instead every CTA first rewrites the activation vector, per sub-block of 32, as
+//     x_k = s * X_k,   s = amax / (2^23 - 256),   X_k = rint(x_k / s)  (a 24-bit signed integer),
+// split into three byte planes X = 65536 H + 256 M + L (H signed, M and L unsigned), and keeps S0 = sum x_k per
+// sub-block in fp32.  The products are then exact integer dot products of the nibbles with the three planes (dp4a:
+// 24 per 32 weights), joined as D = 65536 D_H + 256 D_M + D_L in fp32, and per sub-block
+//     acc = fma((d * sc) * s, D, acc);   acc = fma(-(dmin * mn), S0, acc),
+// lane l taking half-super-blocks l, l + 32, ... in ascending order, lanes added by a fixed butterfly.
+// The only approximation is the rounding of x_k to 24 bits relative to its sub-block's largest element (fp32 itself
+// carries 24 bits per element): against binary64 the result is closer than the reference's own sequential fp32 sum,
+// norm-wise about 1e-7 (the stated bar is 1e-5).  Inputs must be finite.
+constexpr int kW4RecBytes = 432;        // per half-super-block: three planes of 128 bytes, four scales, four sums, 16 spare
+constexpr float kW4Range = 8388352.0f;  // 2^23 - 256: rint(x * range / amax) stays below 2^23 whatever the roundings
 
 struct W4Plan {
     const uint8_t* W;
@@ -165,19 +169,52 @@ struct W4Plan {
     float* out;
     int M, nb, row_bytes, rt, n_tiles;
     int nw, slots, slot_bytes;
-    int off_ring, off_x, off_s0, off_bar;
+    int off_ring, off_x, off_bar;
     size_t smem;
 };
 
-__device__ __forceinline__ float w4_fold(float v)
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
 {
+    int d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// 256 activations held by a warp (lane l: elements 4l..4l+3 in v0, 128 + 4l.. in v1) -> the two records of the block
+__device__ __forceinline__ void w4_write_records(const float4& v0, const float4& v1, uint8_t* rec0, int lane)
+{
+    const float4 v[2] = {v0, v1};
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
-    return v;
+    for (int h = 0; h < 2; h++) {
+        uint8_t* rec = rec0 + h * kW4RecBytes;
+        float amax = fmaxf(fmaxf(fabsf(v[h].x), fabsf(v[h].y)), fmaxf(fabsf(v[h].z), fabsf(v[h].w)));
+        float s0 = (v[h].x + v[h].y) + (v[h].z + v[h].w);
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {            // eight lanes = one sub-block
+            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+            s0 += __shfl_xor_sync(0xFFFFFFFFu, s0, o);
+        }
+        const float scale = __fdiv_rn(amax, kW4Range);
+        const float inv = amax != 0.0f ? __fdiv_rn(kW4Range, amax) : 0.0f;
+        const int q0 = __float2int_rn(v[h].x * inv), q1 = __float2int_rn(v[h].y * inv), q2 = __float2int_rn(v[h].z * inv),
+                  q3 = __float2int_rn(v[h].w * inv);
+        // byte b of the four integers -> one word per plane
+        const uint32_t a01 = __byte_perm((uint32_t)q0, (uint32_t)q1, 0x5140), a23 = __byte_perm((uint32_t)q2, (uint32_t)q3, 0x5140);   // L M L M
+        const uint32_t b01 = __byte_perm((uint32_t)q0, (uint32_t)q1, 0x6262), b23 = __byte_perm((uint32_t)q2, (uint32_t)q3, 0x6262);   // H H (bytes 0, 1)
+        const uint32_t pl = __byte_perm(a01, a23, 0x5410), pm = __byte_perm(a01, a23, 0x7632), ph = __byte_perm(b01, b23, 0x5410);
+        const int w = lane & 31;                      // word index inside the 128-byte plane = lane (elements 4 lane ..)
+        reinterpret_cast<uint32_t*>(rec)[w] = ph;
+        reinterpret_cast<uint32_t*>(rec + 128)[w] = pm;
+        reinterpret_cast<uint32_t*>(rec + 256)[w] = pl;
+        if ((lane & 7) == 0) {
+            reinterpret_cast<float*>(rec + 384)[lane >> 3] = scale;
+            reinterpret_cast<float*>(rec + 400)[lane >> 3] = s0;
+        }
+    }
 }
 
 template <int R>
-__device__ __forceinline__ void w4_tile(const uint8_t* tile, const float* xs, const float* s0s, const W4Plan& p, int row0, int lane)
+__device__ __forceinline__ void w4_tile(const uint8_t* tile, const uint8_t* xs, const W4Plan& p, int row0, int lane)
 {
     const int rows = min(R, p.M - row0);
     float acc[R];
@@ -186,60 +223,60 @@ __device__ __forceinline__ void w4_tile(const uint8_t* tile, const float* xs, co
     for (int hb = lane; hb < 2 * p.nb; hb += 32) {
         const int half = hb & 1;
         const uint8_t* blk0 = tile + (size_t)(hb >> 1) * BPDQ_Q4K_BYTES;
-        const float4* xv4 = reinterpret_cast<const float4*>(xs + (size_t)hb * kW4XPad);
-        const float4 s0v = *reinterpret_cast<const float4*>(s0s + 4 * hb);
-        const float s0a[4] = {s0v.x, s0v.y, s0v.z, s0v.w};
-        float dsc[R][4], dmn[R][4];
+        const uint8_t* rec = xs + (size_t)hb * kW4RecBytes;
+        const float4 sc4f = *reinterpret_cast<const float4*>(rec + 384);
+        const float4 s04f = *reinterpret_cast<const float4*>(rec + 400);
+        const float xs_scale[4] = {sc4f.x, sc4f.y, sc4f.z, sc4f.w}, xs_s0[4] = {s04f.x, s04f.y, s04f.z, s04f.w};
+        float dd[R], dm[R];
+        uint32_t sc4[R], mn4[R];
 #pragma unroll
         for (int r = 0; r < R; r++) {
             const uint4 hdr = *reinterpret_cast<const uint4*>(blk0 + (size_t)r * p.row_bytes);
-            const float d16 = 16.0f * f16_bits_to_f32(hdr.x & 0xFFFFu), dmin = f16_bits_to_f32(hdr.x >> 16);
-            uint32_t sc4, mn4;
-            q4k_scales4(hdr.y, hdr.z, hdr.w, half, sc4, mn4);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                dsc[r][j] = d16 * (float)byte_of(sc4, j);
-                dmn[r][j] = dmin * (float)byte_of(mn4, j);
-            }
+            dd[r] = f16_bits_to_f32(hdr.x & 0xFFFFu);
+            dm[r] = f16_bits_to_f32(hdr.x >> 16);
+            q4k_scales4(hdr.y, hdr.z, hdr.w, half, sc4[r], mn4[r]);
         }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            float xv[32];
+            // the sub-block's 32 activations as three byte planes: words 0..3 = elements 0..15, 4..7 = 16..31
+            uint32_t pl[3][8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float4 v = xv4[8 * j + i];
-                xv[4 * i + 0] = v.x;
-                xv[4 * i + 1] = v.y;
-                xv[4 * i + 2] = v.z;
-                xv[4 * i + 3] = v.w;
+            for (int k = 0; k < 3; k++) {
+                const uint4 a = *reinterpret_cast<const uint4*>(rec + 128 * k + 32 * j);
+                const uint4 b = *reinterpret_cast<const uint4*>(rec + 128 * k + 32 * j + 16);
+                pl[k][0] = a.x; pl[k][1] = a.y; pl[k][2] = a.z; pl[k][3] = a.w;
+                pl[k][4] = b.x; pl[k][5] = b.y; pl[k][6] = b.z; pl[k][7] = b.w;
             }
 #pragma unroll
             for (int r = 0; r < R; r++) {
                 if (r >= rows) continue;
                 const uint4 qv = *reinterpret_cast<const uint4*>(blk0 + (size_t)r * p.row_bytes + 16 + 64 * half + 16 * j);
                 const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
-                float s1a = 0.0f, s1b = 0.0f;     // two chains: low-nibble and high-nibble elements
+                int lo[3] = {0, 0, 0}, hi[3] = {0, 0, 0};
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
-                    // byte = 0x80 | q << 3: with 0x3F on top, the float 1 + q / 16
-                    const uint32_t lo = ((qw[w] << 3) & 0x78787878u) | 0x80808080u;
-                    const uint32_t hi = ((qw[w] >> 1) & 0x78787878u) | 0x80808080u;
-#pragma unroll
-                    for (int b = 0; b < 4; b++) {
-                        const uint32_t sel = 0x7044u | ((uint32_t)b << 8);
-                        s1a = fmaf(__uint_as_float(__byte_perm(lo, 0x3F000000u, sel)), xv[4 * w + b], s1a);
-                        s1b = fmaf(__uint_as_float(__byte_perm(hi, 0x3F000000u, sel)), xv[16 + 4 * w + b], s1b);
-                    }
+                    const uint32_t ql = qw[w] & 0x0F0F0F0Fu, qh = qw[w] & 0xF0F0F0F0u;     // hi: 16 x the nibble
+                    lo[0] = dp4a_us(ql, pl[0][w], lo[0]);
+                    hi[0] = dp4a_us(qh, pl[0][4 + w], hi[0]);
+                    lo[1] = dp4a_uu(ql, pl[1][w], lo[1]);
+                    hi[1] = dp4a_uu(qh, pl[1][4 + w], hi[1]);
+                    lo[2] = dp4a_uu(ql, pl[2][w], lo[2]);
+                    hi[2] = dp4a_uu(qh, pl[2][4 + w], hi[2]);
                 }
-                const float t = (s1a + s1b) - s0a[j];
-                acc[r] = fmaf(dsc[r][j], t, acc[r]);
-                acc[r] = fmaf(-dmn[r][j], s0a[j], acc[r]);
+                // exact integers: hi[] are multiples of 16
+                const float dH = (float)(lo[0] + (hi[0] >> 4)), dM = (float)(lo[1] + (int)((unsigned)hi[1] >> 4)),
+                            dL = (float)(lo[2] + (int)((unsigned)hi[2] >> 4));
+                const float D = fmaf(65536.0f, dH, fmaf(256.0f, dM, dL));
+                acc[r] = fmaf((dd[r] * (float)byte_of(sc4[r], j)) * xs_scale[j], D, acc[r]);
+                acc[r] = fmaf(-(dm[r] * (float)byte_of(mn4[r], j)), xs_s0[j], acc[r]);
             }
         }
     }
 #pragma unroll
     for (int r = 0; r < R; r++) {
-        const float v = w4_fold(acc[r]);
+        float v = acc[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
         if (lane == 0 && r < rows) p.out[row0 + r] = v;
     }
 }
@@ -248,8 +285,7 @@ __global__ void __launch_bounds__(352, 1) k_w4a32_ring(const W4Plan p, int* __re
 {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem + p.off_ring;
-    float* xs = reinterpret_cast<float*>(smem + p.off_x);        // [2 nb][132]
-    float* s0s = reinterpret_cast<float*>(smem + p.off_s0);      // [8 nb]
+    uint8_t* xs = smem + p.off_x;                                // [2 nb][432]
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bar);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
@@ -273,14 +309,11 @@ __global__ void __launch_bounds__(352, 1) k_w4a32_ring(const W4Plan p, int* __re
         lv += stride;
     };
     for (int k = 0; k < p.slots && lv < p.n_tiles; k++) issue(k);     // weights never depend on the launch before
-    // the activation vector may come from the launch before: wait for it, then stage it (padded) and the sub-block sums
+    // the activation vector may come from the launch before: wait for it, then every CTA makes its own fixed-point copy
     pdl_wait();
-    for (int sub = warp; sub < 8 * p.nb; sub += p.nw) {
-        const float v = __ldcg(p.x + (size_t)sub * 32 + lane);
-        xs[(size_t)(sub >> 2) * kW4XPad + 32 * (sub & 3) + lane] = v;
-        // fixed order: butterfly over the 32 lanes
-        const float s = w4_fold(v);
-        if (lane == 0) s0s[sub] = s;
+    for (int b = warp; b < p.nb; b += p.nw) {
+        const float4* xb = reinterpret_cast<const float4*>(p.x + (size_t)b * 256);
+        w4_write_records(__ldcg(xb + lane), __ldcg(xb + 32 + lane), xs + (size_t)(2 * b) * kW4RecBytes, lane);
     }
     __syncthreads();
     int slot = 0;
@@ -289,9 +322,9 @@ __global__ void __launch_bounds__(352, 1) k_w4a32_ring(const W4Plan p, int* __re
         if (!mbar_wait_bounded(&my_full[slot], parity, err, 2)) return;
         const uint8_t* tile = my_ring + (size_t)slot * p.slot_bytes;
         const int row0 = v * p.rt;
-        if (p.rt == 4) w4_tile<4>(tile, xs, s0s, p, row0, lane);
-        else if (p.rt == 2) w4_tile<2>(tile, xs, s0s, p, row0, lane);
-        else w4_tile<1>(tile, xs, s0s, p, row0, lane);
+        if (p.rt == 4) w4_tile<4>(tile, xs, p, row0, lane);
+        else if (p.rt == 2) w4_tile<2>(tile, xs, p, row0, lane);
+        else w4_tile<1>(tile, xs, p, row0, lane);
         __syncwarp();
         if (lv < p.n_tiles) issue(slot);
         if (++slot == p.slots) {
@@ -318,13 +351,12 @@ static int w4a32_ring(const uint8_t* W, const float* x, float* out, int M, int K
     p.n_tiles = (M + p.rt - 1) / p.rt;
     p.slots = 2;
     p.nw = 10;
-    const size_t x_bytes = (size_t)2 * p.nb * kW4XPad * sizeof(float), s0_bytes = (size_t)8 * p.nb * sizeof(float);
+    const size_t x_bytes = (size_t)2 * p.nb * kW4RecBytes;
     for (;;) {
         size_t off = 0;
         auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
         p.off_ring = take((size_t)p.nw * p.slots * p.slot_bytes);
         p.off_x = take(x_bytes);
-        p.off_s0 = take(s0_bytes);
         p.off_bar = take((size_t)p.nw * p.slots * 8);
         p.smem = off;
         if (p.smem <= (size_t)227 * 1024) break;

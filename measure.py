@@ -10,6 +10,7 @@
                                                     # beside the row-layout kernel, 1..512 tokens
     python measure.py --q8-tiles-once TOKENS [N K]
                                                     # five launches of the re-tiled product: a small case for a profiler
+    python measure.py --w4a32-once [N K]           # five launches of the fp32-activation GEMV: a small case for a profiler
     python measure.py --gemm-once tc5 64 [N K]
                                                     # five launches of one many-token product (kernel
                                                     # tc5 | mma | rg16 | dispatch): a small case for a profiler
@@ -90,6 +91,21 @@ def gemm_once(lib, kernel, tokens, N=14336, K=4096, launches=5):
     for p in (w, x, o):
         lib.bpdq_free(p)
     print(json.dumps({"gemm_once": kernel, "tokens": tokens, "N": N, "K": K, "status": status}))
+    return 0 if status == 0 else 1
+
+
+def w4a32_once(lib, N=14336, K=4096, launches=5):
+    """The fp32-activation GEMV drop-in (bpd_qmatmul_q4k_gpu's kernel), a few launches: a small case for a profiler."""
+    w = _dev(lib, synth.q4k_matrix(N, K, 1))
+    x = _dev(lib, synth.activations(K, 2))
+    o = lib.bpdq_alloc(N * 4)
+    for _ in range(launches):
+        capi.check(lib.bpd_qmatmul_q4k_gpu_st(w, x, o, N, K, None))
+    lib.bpdq_sync()
+    status = lib.bpdq_last_status()
+    for p in (w, x, o):
+        lib.bpdq_free(p)
+    print(json.dumps({"w4a32_once": True, "N": N, "K": K, "status": status}))
     return 0 if status == 0 else 1
 
 
@@ -239,6 +255,8 @@ def main():
         return q8_tiles(lib, *[int(v) for v in sys.argv[2:4]])
     if len(sys.argv) >= 3 and sys.argv[1] == "--q8-tiles-once":
         return q8_tiles_once(lib, *[int(v) for v in sys.argv[2:5]])
+    if len(sys.argv) >= 2 and sys.argv[1] == "--w4a32-once":
+        return w4a32_once(lib, *[int(v) for v in sys.argv[2:4]])
     if len(sys.argv) >= 4 and sys.argv[1] == "--gemm-once":
         extra = [int(v) for v in sys.argv[4:6]]
         return gemm_once(lib, sys.argv[2], int(sys.argv[3]), *extra)

@@ -30,6 +30,9 @@ def build(ref_root=None):
     root = ref_root or os.environ.get("BPD_REFERENCE_ROOT") or os.path.join(os.path.dirname(HERE), os.pardir, "reference")
     if os.path.isdir(os.path.join(root, "bench")):
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", "REF=" + root])
+        import shutil
+        if shutil.which("nvcc"):      # the reference's own GPU kernels, as a second baseline and checker on a GPU box
+            subprocess.check_call(["make", "-s", "-C", HERE, "refgpu", "REF=" + root])
 
 
 def _p(a):
@@ -270,7 +273,12 @@ def load_ref(name):
     bench/test_gemm_q8_0_tiles.py:40-70)."""
     lib = C.CDLL(os.path.join(REF_DIR, name))
     vp, i = C.c_void_p, C.c_int
-    if name == "bpd_quant.so":
+    if name == "bpd_quant_gpu.so":
+        # bench/verify_quant_gpu.py:33-42 of the reference
+        lib.bpd_dequant_q4k_gpu.argtypes = [vp, vp, i]
+        lib.bpd_qmatmul_q4k_gpu.argtypes = [vp, vp, vp, i, i]
+        lib.qgpu_sync.argtypes = []
+    elif name == "bpd_quant.so":
         lib.bpd_dequant_q4k.argtypes = [vp, vp, i]
         lib.bpd_qmatmul_q4k.argtypes = [vp, vp, vp, i, i]
         lib.bpd_qmm_q4k.argtypes = [vp, vp, vp, i, i, i]
