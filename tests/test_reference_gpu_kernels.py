@@ -3,7 +3,6 @@ sm_100a, beside this library's drop-ins for the same two entry points on the sam
 (dequantization bit for bit, the fp32-activation GEMV norm-wise) and both timed with CUDA events on the legacy
 default stream, which is where the reference launches.  The timings are printed as one JSON line (run with -s)."""
 import json
-import os
 
 import numpy as np
 import pytest
@@ -70,9 +69,5 @@ def test_reference_gpu_kernels_beside_the_drop_ins(lib, oracle):
         }
         print("\nREFERENCE_GPU_BASELINE " + json.dumps({"shape": [N, K], **{k: round(v, 2) for k, v in t.items()},
                                                         "gemv_norm_err_mine": normwise(a, exact), "gemv_norm_err_reference": normwise(b, exact)}))
-        out_dir = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-        if os.path.isdir(out_dir):
-            with open(os.path.join(out_dir, "reference_gpu_baseline.json"), "w") as f:
-                json.dump(t, f)
     finally:
         lib.bpdq_set_stream(prev)
