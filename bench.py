@@ -7,9 +7,11 @@
 
 A step is one pass over the 7 x 32 GEMVs.  The metric is effective HBM bandwidth: algorithmic
 bytes (quantized weights + fp32 activations in + fp32 outputs out) divided by device time.
-With N GPUs every rank holds a layer set of the same size (its row shard of an N-times
-larger model), runs the same step, and all-gathers its output slices over NCCL; the value
-is the sum of the ranks' bytes over the slowest rank's time (weak scaling).
+The default schedule runs the step as persistent launches of 112 products each, replayed from a
+CUDA graph.  With N GPUs every rank holds a layer set of the same size (its row shard of an
+N-times larger model), runs the same step, and the ranks' output slices are exchanged by stores
+from the product kernel into every rank's gathered buffer (or, --exchange nccl, by an all-gather);
+the value is the sum of the ranks' bytes over the slowest rank's time (weak scaling).
 
 One JSON line is printed by rank 0.
 """
