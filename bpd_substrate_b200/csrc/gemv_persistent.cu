@@ -10,38 +10,105 @@ namespace bpdq {
 
 // ---- Persistent decode chain: ONE cooperative launch walks a whole program of dependent phases
 // (per decoder layer: rms_norm -> q,k,v | q -> o, += x | rms_norm -> gate,up | silu(gate)*up -> down, += x).
-// The weights of a phase do not depend on the phase before it, so the producer warp streams the
-// tiles of all phases back to back into the ring and HBM never waits for a launch boundary; only
-// the consumer warps wait, at a grid-wide barrier between phases (one counter per phase: every CTA
-// adds one when its rows are written and fenced, thread 0 of every CTA polls with an acquire load,
-// bounded), then rebuild the phase's activation records in shared memory from the vector the
-// previous phase produced.  A cooperative launch keeps all CTAs resident, which the barrier needs.
+// The weights of a phase do not depend on the phase before it.  Every consumer warp owns a private ring
+// that it refills itself: when it has folded a tile it issues the bulk copy of the tile it needs `slots`
+// turns later, which may belong to a later phase, so the ring is full again when the warp comes back from
+// the barrier between phases and HBM works through the barrier and the next phase's records step.  The
+// barrier is grid-wide (one counter per phase: every CTA adds one when its rows are written and fenced,
+// thread 0 of every CTA polls with an acquire load, bounded); after it the CTA rebuilds the phase's
+// activation records in shared memory from the vector the previous phase produced.  A cooperative launch
+// keeps all CTAs resident, which the barrier needs.
+//
+// A gate/up phase followed by a silu(gate)*up phase is planned as PAIRED tiles: a tile holds the same rows
+// of both matrices, the warp folds them together and writes gate, up and silu(gate)*up, and the phase
+// after it quantizes that one vector instead of evaluating 2 x 14336 exponentials in every CTA.  The bits
+// are those of the unpaired program: a row's lanes, its fold and the activation's arithmetic are the same.
 constexpr int kChainMaxProblems = 3;
+constexpr int kChainThreads = 384;   // at most twelve warps, all consumers: 170 registers each
 struct ChainPhase {
     int n_problems, prologue, nb, n_tiles;   // prologue as in BatchPlan: 0 records of a, 1 rms_norm(a, b, eps), 2 silu(a)*b
     const float* a;
     const float* b;
     float eps;
-    int pad;
+    int pair;                                // 1: tiles hold rt/2 rows of prob[0] and the same rows of prob[1]
+    float* act;                              // paired phases: silu(out0) * out1
     BatchProblem prob[kChainMaxProblems];
 };
+static_assert(sizeof(ChainPhase) % 16 == 0, "phase descriptors are copied to shared memory 16 bytes at a time");
+static_assert(sizeof(ChainPhase) / 16 <= 32, "one warp copies a descriptor, a lane per 16 bytes");
+constexpr int kChainWindow = 8;   // descriptors of the current phase and the seven after it are held in shared memory
 struct ChainPlan {
     const ChainPhase* phases;   // device array
     unsigned* arrive;           // [n_phases] grid-barrier counters, zero at launch
     int n_phases;
     int nw, slots, slot_bytes;
-    int off_ring, off_xq, off_bar;
+    int off_ring, off_xq, off_win, off_bar;
     size_t smem;
-    unsigned long long* trace;  // tuning aid: SM-clock stamps of CTA 0, [phase < 64][4], or null
+    unsigned long long* trace;  // tuning aid: SM-clock stamps of CTA 0, [phase < 64][8], or null
 };
 #ifdef BPDQ_TRACE_BUILD
 #define CHAIN_TRACE(ph, k)                                                                     \
     do {                                                                                       \
-        if (p.trace && blockIdx.x == 0 && tid == 0 && (ph) < 64) p.trace[(ph) * 4 + (k)] = clock64(); \
+        if (p.trace && blockIdx.x == 0 && tid == 0 && (ph) < 64) p.trace[(ph) * 8 + (k)] = clock64(); \
     } while (0)
 #else
 #define CHAIN_TRACE(ph, k) do { } while (0)
 #endif
+
+// A paired tile: rows [row0, row0 + H) of the gate matrix, then the same rows of the up matrix, H = R / 2.
+// Lane l adds its half-blocks l, l + 32, ... of every row and the rows are folded as batch_tile<R> folds them.
+template <int R, int LAYOUT>
+__device__ __forceinline__ void pair_tile(const uint8_t* tile_smem, const uint8_t* xq, const BatchProblem& g,
+                                          const BatchProblem& u, float* __restrict__ act, int row0, int lane)
+{
+    constexpr int H = R / 2;
+    const int rows = min(H, g.M - row0);
+    const int n_hb = 2 * g.nb;
+    float acc[R][1];
+#pragma unroll
+    for (int r = 0; r < R; r++) acc[r][0] = 0.0f;
+    for (int hb = lane; hb < n_hb; hb += 32) {
+        const uint4* rec = reinterpret_cast<const uint4*>(xq + (size_t)hb * kXqStride);
+        uint32_t xr[1][32];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint4 v = rec[i];
+            xr[0][4 * i + 0] = v.x;
+            xr[0][4 * i + 1] = v.y;
+            xr[0][4 * i + 2] = v.z;
+            xr[0][4 * i + 3] = v.w;
+        }
+        const uint4 tail = rec[8];
+        int bs[1][4];
+        bs[0][0] = (int)(short)(tail.x & 0xFFFFu);
+        bs[0][1] = (int)(short)(tail.x >> 16);
+        bs[0][2] = (int)(short)(tail.y & 0xFFFFu);
+        bs[0][3] = (int)(short)(tail.y >> 16);
+        float xd[1] = {__uint_as_float(tail.z)};
+        const uint8_t* sbp = tile_smem + (size_t)(hb >> 1) * BPDQ_Q4K_BYTES;
+#pragma unroll
+        for (int r = 0; r < R; r++)
+            if ((r % H) < rows) half_block_fma<1, LAYOUT>(sbp + (size_t)r * g.row_bytes, hb & 1, xr, bs, xd, acc[r], nullptr);
+    }
+    float v[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) v[r] = acc[r][0];
+    const float total = fold_rows<R>(v, lane);
+    constexpr int kLanesPerRow = 32 / R;
+    // the lanes that hold a gate row fetch the up row of the same index
+    const float other = __shfl_sync(0xFFFFFFFFu, total, (lane + H * kLanesPerRow) & 31);
+    const int my_row = lane / kLanesPerRow;
+    if ((lane % kLanesPerRow) == 0) {
+        if (my_row < H) {
+            if (my_row < rows) {
+                g.out[row0 + my_row] = total;
+                act[row0 + my_row] = (total / (1.0f + expf(-total))) * other;   // cta_swiglu_records' arithmetic
+            }
+        } else if (my_row - H < rows) {
+            u.out[row0 + my_row - H] = total;
+        }
+    }
+}
 
 template <int LAYOUT, int MAXTHREADS>
 __global__ void __launch_bounds__(MAXTHREADS, 1)
@@ -50,63 +117,75 @@ k_decode_chain(const ChainPlan p, int* __restrict__ err)
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem + p.off_ring;                                 // [nw][slots][slot_bytes]
     uint8_t* xq = smem + p.off_xq;                                     // activation records of the current phase
+    ChainPhase* win = reinterpret_cast<ChainPhase*>(smem + p.off_win); // [kChainWindow] descriptor of phase q at q % kChainWindow
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bar);    // [nw*slots]
-    uint64_t* empty = full + p.nw * p.slots;
-    float* s_sum = reinterpret_cast<float*>(empty + p.nw * p.slots);   // nine floats of the rms_norm step
+    float* s_sum = reinterpret_cast<float*>(full + p.nw * p.slots);    // nine floats of the rms_norm step
     volatile int* dead = reinterpret_cast<volatile int*>(s_sum + 12);  // a wait gave up: everybody leaves at the next barrier
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nw = p.nw, grid = (int)gridDim.x;
+    constexpr int kDesc16 = (int)(sizeof(ChainPhase) / 16);
+    // the program was uploaded when the chain was planned: plain loads
+    for (int w = tid; w < min(p.n_phases, kChainWindow) * kDesc16; w += blockDim.x)
+        reinterpret_cast<uint4*>(win)[w] = __ldg(reinterpret_cast<const uint4*>(p.phases) + w);
     if (tid == 0) {
-        for (int s = 0; s < nw * p.slots; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
-        }
+        for (int s = 0; s < nw * p.slots; s++) mbar_init(&full[s], 1);
         *dead = 0;
         mbar_init_fence();
     }
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == nw) {
-        // ---- producer: lane g feeds consumer warp g, phase after phase without a pause
-        if (lane < nw) {
-            const int g = lane;
-            int slot = 0;
-            uint32_t wait_parity = 0;
-            bool wrapped = false;
-            for (int ph = 0; ph < p.n_phases; ph++) {
-                const ChainPhase& P = p.phases[ph];
-                const int n_tiles = P.n_tiles, n_prob = P.n_problems;
-                for (int v = g * grid + (int)blockIdx.x; v < n_tiles; v += nw * grid) {
-                    const int s = g * p.slots + slot;
-                    if (wrapped && !mbar_wait_bounded(&empty[s], wait_parity, err, 23)) return;
-                    int j = 0;
+    const int first = warp * grid + (int)blockIdx.x, stride = nw * grid;
+    uint8_t* my_ring = ring + (size_t)warp * p.slots * p.slot_bytes;
+    uint64_t* my_full = full + warp * p.slots;
+
+    // the tile this warp will LOAD next: runs `slots` ring turns ahead of the one it folds, across phases
+    // (lph, lv) always names a tile that exists, or lph == n_phases: the walker never looks back at a phase
+    // that the warp has left, so the window may drop that phase's descriptor
+    int lph = 0, lv = first, cur = 0;
+    auto desc = [&](int q) -> const ChainPhase* { return q < cur + kChainWindow ? &win[q % kChainWindow] : &p.phases[q]; };
+    auto skip = [&]() {
+        while (lph < p.n_phases && lv >= desc(lph)->n_tiles) {
+            lph++;
+            lv = first;
+        }
+    };
+    skip();
+    auto issue = [&](int slot) {
+        if (lph >= p.n_phases) return;
+        if (lane == 0) {
+            const ChainPhase& P = *desc(lph);
+            uint8_t* dst = my_ring + (size_t)slot * p.slot_bytes;
+            if (P.pair) {
+                const BatchProblem& g = P.prob[0];
+                const int half = g.rt >> 1, row0 = lv * half;
+                const uint32_t bytes = (uint32_t)min(half, g.M - row0) * g.row_bytes;
+                mbar_expect_tx(&my_full[slot], 2 * bytes);
+                bulk_g2s(dst, g.W + (size_t)row0 * g.row_bytes, bytes, &my_full[slot]);
+                bulk_g2s(dst + (size_t)half * g.row_bytes, P.prob[1].W + (size_t)row0 * g.row_bytes, bytes, &my_full[slot]);
+            } else {
+                int j = 0;
 #pragma unroll
-                    for (int q = 1; q < kChainMaxProblems; q++)
-                        if (q < n_prob && v >= P.prob[q].tile_begin) j = q;
-                    const BatchProblem& pb = P.prob[j];
-                    const int row0 = (v - pb.tile_begin) * pb.rt;
-                    const uint32_t bytes = (uint32_t)min(pb.rt, pb.M - row0) * pb.row_bytes;
-                    mbar_expect_tx(&full[s], bytes);
-                    bulk_g2s(ring + (size_t)s * p.slot_bytes, pb.W + (size_t)row0 * pb.row_bytes, bytes, &full[s]);
-                    if (++slot == p.slots) {
-                        slot = 0;
-                        if (wrapped) wait_parity ^= 1u;
-                        wrapped = true;
-                    }
-                }
+                for (int q = 1; q < kChainMaxProblems; q++)
+                    if (q < P.n_problems && lv >= P.prob[q].tile_begin) j = q;
+                const BatchProblem& pb = P.prob[j];
+                const int row0 = (lv - pb.tile_begin) * pb.rt;
+                const uint32_t bytes = (uint32_t)min(pb.rt, pb.M - row0) * pb.row_bytes;
+                mbar_expect_tx(&my_full[slot], bytes);
+                bulk_g2s(dst, pb.W + (size_t)row0 * pb.row_bytes, bytes, &my_full[slot]);
             }
         }
-        return;
-    }
+        lv += stride;
+        skip();
+    };
+    for (int k = 0; k < p.slots; k++) issue(k);    // weights never depend on what ran before this launch
 
-    // ---- consumers
     pdl_wait();   // the first phase's input vector comes from whatever ran before this launch
     int slot = 0;
     uint32_t parity = 0;
     for (int ph = 0; ph < p.n_phases; ph++) {
-        const ChainPhase& P = p.phases[ph];
+        const ChainPhase& P = win[ph % kChainWindow];
         if (ph > 0) {
             // grid-wide barrier: every CTA has written and fenced the rows of phase ph-1
             if (tid == 0) {
@@ -125,6 +204,12 @@ k_decode_chain(const ChainPlan p, int* __restrict__ err)
             }
             named_bar_sync(3, nw * 32);
             if (*dead) break;
+            // the window moves on: the slot of phase ph-1 takes phase ph-1+kChainWindow (complete before the
+            // barrier that ends the records step; nobody reads descriptors in between)
+            cur = ph;
+            const int q = ph - 1 + kChainWindow;
+            if (q < p.n_phases && warp == nw - 1 && lane < kDesc16)
+                reinterpret_cast<uint4*>(&win[q % kChainWindow])[lane] = __ldg(reinterpret_cast<const uint4*>(p.phases + q) + lane);
         }
         CHAIN_TRACE(ph, 0);
         // ---- the phase's activation records
@@ -134,29 +219,39 @@ k_decode_chain(const ChainPlan p, int* __restrict__ err)
         named_bar_sync(2, nw * 32);
         CHAIN_TRACE(ph, 1);
         // ---- this warp's tiles of the phase
-        const int n_tiles = P.n_tiles, n_prob = P.n_problems;
-        for (int v = warp * grid + (int)blockIdx.x; v < n_tiles; v += nw * grid) {
-            const int s = warp * p.slots + slot;
-            if (!mbar_wait_bounded(&full[s], parity, err, 22)) {
+        const int n_tiles = P.n_tiles, n_prob = P.n_problems, pair = P.pair;
+        for (int v = first; v < n_tiles; v += stride) {
+            if (!mbar_wait_bounded(&my_full[slot], parity, err, 22)) {
                 *dead = 1;
                 break;
             }
+            if (v == first) CHAIN_TRACE(ph, 4);
+            const uint8_t* tile_smem = my_ring + (size_t)slot * p.slot_bytes;
+            if (pair) {
+                const BatchProblem& g = P.prob[0];
+                const int row0 = v * (g.rt >> 1);
+                if (g.rt == 4) pair_tile<4, LAYOUT>(tile_smem, xq, g, P.prob[1], P.act, row0, lane);
+                else pair_tile<2, LAYOUT>(tile_smem, xq, g, P.prob[1], P.act, row0, lane);
+            } else {
+                int j = 0;
+#pragma unroll
+                for (int q = 1; q < kChainMaxProblems; q++)
+                    if (q < n_prob && v >= P.prob[q].tile_begin) j = q;
+                const BatchProblem& pb = P.prob[j];
+                const int row0 = (v - pb.tile_begin) * pb.rt;
+                if (pb.rt == 4) batch_tile<4, LAYOUT, 1>(tile_smem, xq, pb, row0, lane);
+                else if (pb.rt == 2) batch_tile<2, LAYOUT, 1>(tile_smem, xq, pb, row0, lane);
+                else batch_tile<1, LAYOUT, 1>(tile_smem, xq, pb, row0, lane);
+            }
+            // every lane has read the slot: it takes the tile this warp needs `slots` turns from now
+            __syncwarp();
+            if (v == first) CHAIN_TRACE(ph, 5);
+            issue(slot);
+            if (v == first) CHAIN_TRACE(ph, 6);
             if (++slot == p.slots) {
                 slot = 0;
                 parity ^= 1u;
             }
-            int j = 0;
-#pragma unroll
-            for (int q = 1; q < kChainMaxProblems; q++)
-                if (q < n_prob && v >= P.prob[q].tile_begin) j = q;
-            const BatchProblem& pb = P.prob[j];
-            const int row0 = (v - pb.tile_begin) * pb.rt;
-            const uint8_t* tile_smem = ring + (size_t)s * p.slot_bytes;
-            if (pb.rt == 4) batch_tile<4, LAYOUT, 1>(tile_smem, xq, pb, row0, lane);
-            else if (pb.rt == 2) batch_tile<2, LAYOUT, 1>(tile_smem, xq, pb, row0, lane);
-            else batch_tile<1, LAYOUT, 1>(tile_smem, xq, pb, row0, lane);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
         }
         // ---- publish: rows written by this CTA are visible device-wide before its arrival counts
         CHAIN_TRACE(ph, 2);
@@ -172,6 +267,7 @@ struct ChainHandle {
     ChainPlan plan;
     ChainPhase* d_phases;
     unsigned* d_arrive;
+    float* d_act;      // silu(gate)*up vectors of the paired phases, one after the other
     int device;
 };
 
@@ -201,7 +297,8 @@ static ChainHandle* chain_create(int n_phases, const ChainPhaseDesc* ph)
         P.a = d.a;
         P.b = d.b;
         P.eps = d.eps;
-        P.pad = 0;
+        P.pair = 0;
+        P.act = nullptr;
         P.n_tiles = 0;
         const int K = d.prod[0].K;
         if (K <= 0 || (K % 256) != 0) { latch(BPDQ_ERR_ARG); return nullptr; }
@@ -235,18 +332,33 @@ static ChainHandle* chain_create(int n_phases, const ChainPhaseDesc* ph)
         }
         if (2 * P.nb * kXqStride > xq_bytes) xq_bytes = 2 * P.nb * kXqStride;
     }
+    // gate/up followed by silu(gate)*up: paired tiles, and the next phase reads the product's own activation vector
+    size_t act_floats = 0;
+    std::vector<size_t> act_at((size_t)n_phases, 0);
+    for (int i = 0; i + 1 < n_phases; i++) {
+        const ChainPhaseDesc& d = ph[i];
+        const ChainPhaseDesc& e = ph[i + 1];
+        ChainPhase& P = prog[i];
+        if (d.n != 2 || d.accumulate_mask || d.prod[0].M != d.prod[1].M || P.prob[0].rt < 2 || e.prologue != 2 ||
+            e.a != d.prod[0].out || e.b != d.prod[1].out || e.prod[0].K != d.prod[0].M) continue;
+        P.pair = 1;
+        P.n_tiles = (P.prob[0].M + P.prob[0].rt / 2 - 1) / (P.prob[0].rt / 2);
+        act_at[i] = act_floats;
+        act_floats += ((size_t)P.prob[0].M + 63) / 64 * 64;
+    }
     ChainHandle* h = new ChainHandle();
     ChainPlan& p = h->plan;
     p.n_phases = n_phases;
     p.slot_bytes = slot_bytes;
     p.slots = tu.stages < 2 ? 2 : tu.stages;
-    p.nw = tu.warps < 1 ? 1 : (tu.warps > 16 ? 16 : tu.warps);
+    p.nw = tu.warps < 1 ? 1 : (tu.warps > kChainThreads / 32 ? kChainThreads / 32 : tu.warps);
     for (;;) {
         size_t off = 0;
         auto take = [&off](size_t bytes) { size_t at = off; off += (bytes + 127) / 128 * 128; return (int)at; };
         p.off_ring = take((size_t)p.nw * p.slots * p.slot_bytes);
         p.off_xq = take((size_t)xq_bytes);
-        p.off_bar = take((size_t)2 * p.nw * p.slots * 8 + 64);
+        p.off_win = take(sizeof(ChainPhase) * kChainWindow);
+        p.off_bar = take((size_t)p.nw * p.slots * 8 + 128);
         p.smem = off;
         if (p.smem <= (size_t)kSmemLimit) break;
         if (p.slots > 2) p.slots--;
@@ -256,16 +368,29 @@ static ChainHandle* chain_create(int n_phases, const ChainPhaseDesc* ph)
     cudaGetDevice(&h->device);
     void* dp = nullptr;
     void* da = nullptr;
-    if (check_cuda(cudaMalloc(&dp, sizeof(ChainPhase) * (size_t)n_phases)) || check_cuda(cudaMalloc(&da, sizeof(unsigned) * (size_t)n_phases)) ||
-        check_cuda(cudaMemcpy(dp, prog.data(), sizeof(ChainPhase) * (size_t)n_phases, cudaMemcpyHostToDevice))) {
+    void* dv = nullptr;
+    bool bad = check_cuda(cudaMalloc(&dp, sizeof(ChainPhase) * (size_t)n_phases)) || check_cuda(cudaMalloc(&da, sizeof(unsigned) * (size_t)n_phases)) ||
+               (act_floats && check_cuda(cudaMalloc(&dv, sizeof(float) * act_floats)));
+    if (!bad) {
+        for (int i = 0; i + 1 < n_phases; i++) {
+            if (!prog[i].pair) continue;
+            prog[i].act = (float*)dv + act_at[i];
+            prog[i + 1].prologue = 0;
+            prog[i + 1].a = prog[i].act;
+        }
+        bad = check_cuda(cudaMemcpy(dp, prog.data(), sizeof(ChainPhase) * (size_t)n_phases, cudaMemcpyHostToDevice)) != 0;
+    }
+    if (bad) {
         if (dp) cudaFree(dp);
         if (da) cudaFree(da);
+        if (dv) cudaFree(dv);
         delete h;
         latch(BPDQ_ERR_CUDA);
         return nullptr;
     }
     h->d_phases = (ChainPhase*)dp;
     h->d_arrive = (unsigned*)da;
+    h->d_act = (float*)dv;
     p.phases = h->d_phases;
     p.arrive = h->d_arrive;
     p.trace = nullptr;
@@ -275,7 +400,7 @@ static ChainHandle* chain_create(int n_phases, const ChainPhaseDesc* ph)
 static int chain_run(ChainHandle* h, cudaStream_t s)
 {
     if (!h) return latch(BPDQ_ERR_ARG);
-    auto kern = k_decode_chain<BPDQ_LAYOUT_BPD, kMidCtaThreads>;
+    auto kern = k_decode_chain<BPDQ_LAYOUT_BPD, kChainThreads>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -289,7 +414,7 @@ static int chain_run(ChainHandle* h, cudaStream_t s)
     if (rc) return latch(rc);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)sm_count());     // one CTA per SM, all resident: the barrier between phases needs that
-    cfg.blockDim = dim3((unsigned)(h->plan.nw + 1) * 32);
+    cfg.blockDim = dim3((unsigned)h->plan.nw * 32);
     cfg.dynamicSmemBytes = h->plan.smem;
     cfg.stream = s;
     cudaLaunchAttribute at[1];
@@ -309,6 +434,7 @@ static void chain_destroy(ChainHandle* h)
     if (!h) return;
     cudaFree(h->d_phases);
     cudaFree(h->d_arrive);
+    if (h->d_act) cudaFree(h->d_act);
     delete h;
 }
 

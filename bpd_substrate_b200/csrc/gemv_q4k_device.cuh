@@ -380,6 +380,22 @@ __device__ __forceinline__ void cta_rmsnorm_records(const float* __restrict__ a,
                                                     uint8_t* xq, float* s_sum, int warp, int lane, int nw)
 {
     const int cols = nb * 256;
+    // the values this warp scales after the sum is known are fetched now: their latency (the vector was written by
+    // other SMs a moment ago, the weights come from HBM) runs under the sum of squares instead of after it
+    constexpr int kPre = 2;
+    float4 pa[kPre][2], pw[kPre][2];
+#pragma unroll
+    for (int i = 0; i < kPre; i++) {
+        const int b = warp + i * nw;
+        if (b < nb) {
+            const float4* xb = reinterpret_cast<const float4*>(a + (size_t)b * 256);
+            const float4* wb = reinterpret_cast<const float4*>(w + (size_t)b * 256);
+            pa[i][0] = __ldcg(xb + lane);
+            pa[i][1] = __ldcg(xb + 32 + lane);
+            pw[i][0] = __ldg(wb + lane);
+            pw[i][1] = __ldg(wb + 32 + lane);
+        }
+    }
     for (int vw = warp; vw < 8; vw += nw) {
         float t = 0.0f;
         for (int base = 0; base < cols; base += 16 * 256) {     // sixteen loads in flight, same chain of FMAs
@@ -400,34 +416,73 @@ __device__ __forceinline__ void cta_rmsnorm_records(const float* __restrict__ a,
 #pragma unroll
     for (int i = 1; i < 8; i++) tot += s_sum[i];
     const float scale = rsqrtf(tot / (float)cols + eps);
-    for (int b = warp; b < nb; b += nw) {
-        const float4* xb = reinterpret_cast<const float4*>(a + (size_t)b * 256);
-        const float4* wb = reinterpret_cast<const float4*>(w + (size_t)b * 256);
-        const float4 a0 = __ldcg(xb + lane), a1 = __ldcg(xb + 32 + lane), w0 = __ldg(wb + lane), w1 = __ldg(wb + 32 + lane);
+    auto emit = [&](int b, const float4& a0, const float4& a1, const float4& w0, const float4& w1) {
         const float4 v0 = make_float4(a0.x * scale * w0.x, a0.y * scale * w0.y, a0.z * scale * w0.z, a0.w * scale * w0.w);
         const float4 v1 = make_float4(a1.x * scale * w1.x, a1.y * scale * w1.y, a1.z * scale * w1.z, a1.w * scale * w1.w);
         write_records(v0, v1, xq + (size_t)(2 * b) * kXqStride, lane);
+    };
+#pragma unroll
+    for (int i = 0; i < kPre; i++) {
+        const int b = warp + i * nw;
+        if (b < nb) emit(b, pa[i][0], pa[i][1], pw[i][0], pw[i][1]);
+    }
+    for (int b = warp + kPre * nw; b < nb; b += nw) {
+        const float4* xb = reinterpret_cast<const float4*>(a + (size_t)b * 256);
+        const float4* wb = reinterpret_cast<const float4*>(w + (size_t)b * 256);
+        emit(b, __ldcg(xb + lane), __ldcg(xb + 32 + lane), __ldg(wb + lane), __ldg(wb + 32 + lane));
     }
 }
-// silu(gate) * up with k_elementwise's arithmetic
+// silu(gate) * up with k_elementwise's arithmetic; three blocks' loads in flight per warp
 __device__ __forceinline__ void cta_swiglu_records(const float* __restrict__ gate, const float* __restrict__ up, int nb,
                                                    uint8_t* xq, int warp, int lane, int nw)
 {
     auto act = [](float g, float u) { return (g / (1.0f + expf(-g))) * u; };
-    for (int b = warp; b < nb; b += nw) {
-        const float4* gb = reinterpret_cast<const float4*>(gate + (size_t)b * 256);
-        const float4* ub = reinterpret_cast<const float4*>(up + (size_t)b * 256);
-        const float4 g0 = __ldcg(gb + lane), g1 = __ldcg(gb + 32 + lane), u0 = __ldcg(ub + lane), u1 = __ldcg(ub + 32 + lane);
-        const float4 v0 = make_float4(act(g0.x, u0.x), act(g0.y, u0.y), act(g0.z, u0.z), act(g0.w, u0.w));
-        const float4 v1 = make_float4(act(g1.x, u1.x), act(g1.y, u1.y), act(g1.z, u1.z), act(g1.w, u1.w));
-        write_records(v0, v1, xq + (size_t)(2 * b) * kXqStride, lane);
+    constexpr int kPre = 3;
+    for (int b0 = warp; b0 < nb; b0 += kPre * nw) {
+        float4 g[kPre][2], u[kPre][2];
+#pragma unroll
+        for (int i = 0; i < kPre; i++) {
+            const int b = b0 + i * nw;
+            if (b < nb) {
+                const float4* gb = reinterpret_cast<const float4*>(gate + (size_t)b * 256);
+                const float4* ub = reinterpret_cast<const float4*>(up + (size_t)b * 256);
+                g[i][0] = __ldcg(gb + lane);
+                g[i][1] = __ldcg(gb + 32 + lane);
+                u[i][0] = __ldcg(ub + lane);
+                u[i][1] = __ldcg(ub + 32 + lane);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kPre; i++) {
+            const int b = b0 + i * nw;
+            if (b < nb) {
+                const float4 v0 = make_float4(act(g[i][0].x, u[i][0].x), act(g[i][0].y, u[i][0].y), act(g[i][0].z, u[i][0].z), act(g[i][0].w, u[i][0].w));
+                const float4 v1 = make_float4(act(g[i][1].x, u[i][1].x), act(g[i][1].y, u[i][1].y), act(g[i][1].z, u[i][1].z), act(g[i][1].w, u[i][1].w));
+                write_records(v0, v1, xq + (size_t)(2 * b) * kXqStride, lane);
+            }
+        }
     }
 }
+// records of a plain vector; three blocks per warp are in flight before the first is quantized
 __device__ __forceinline__ void cta_vector_records(const float* __restrict__ x, int nb, uint8_t* xq, int warp, int lane, int nw)
 {
-    for (int b = warp; b < nb; b += nw) {
-        const float4* xb = reinterpret_cast<const float4*>(x + (size_t)b * 256);
-        write_records(__ldcg(xb + lane), __ldcg(xb + 32 + lane), xq + (size_t)(2 * b) * kXqStride, lane);
+    constexpr int kPre = 3;
+    for (int b0 = warp; b0 < nb; b0 += kPre * nw) {
+        float4 v[kPre][2];
+#pragma unroll
+        for (int i = 0; i < kPre; i++) {
+            const int b = b0 + i * nw;
+            if (b < nb) {
+                const float4* xb = reinterpret_cast<const float4*>(x + (size_t)b * 256);
+                v[i][0] = __ldcg(xb + lane);
+                v[i][1] = __ldcg(xb + 32 + lane);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kPre; i++) {
+            const int b = b0 + i * nw;
+            if (b < nb) write_records(v[i][0], v[i][1], xq + (size_t)(2 * b) * kXqStride, lane);
+        }
     }
 }
 
