@@ -211,13 +211,13 @@ k_gemm_q4k_rg16(const RgPlan p, int* __restrict__ err)
         for (int w = tid; w < n16; w += blockDim.x)
             reinterpret_cast<uint4*>(smem + p.off_tab)[w] = src ? __ldg(src + w) : reinterpret_cast<const uint4*>(p.inline_tab)[w];
     }
-    if (tid == 0) {
-        for (int s = 0; s < nw * p.slots; s++) mbar_init(&full[s], 1);
-        for (int b = 0; b < 2; b++) {
-            mbar_init(&xfull[b], 1);
-            mbar_init(&xempty[b], nw);
+    {
+        // the barriers are set up by as many threads: full[nw*slots], xfull[2], xempty[2] (one arrival per consumer warp)
+        const int n_bars = nw * p.slots + 4, first_xempty = nw * p.slots + 2;
+        for (int b = tid; b < n_bars; b += blockDim.x) {
+            mbar_init(&full[b], b >= first_xempty ? nw : 1);
+            mbar_init_fence();
         }
-        mbar_init_fence();
     }
     __syncthreads();
 

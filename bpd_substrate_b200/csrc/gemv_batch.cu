@@ -152,9 +152,9 @@ k_gemv_batch_q4k_q8k(const BatchPlan p, int* __restrict__ err)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     BPDQ_TRACE(0);
-    if (tid == 0) {
-        for (int s = 0; s < p.nw * p.slots; s++) mbar_init(&full[s], 1);
-        mbar_init(xbar, 1);
+    // the barriers are set up by as many threads as there are barriers
+    for (int b = tid; b <= p.nw * p.slots; b += blockDim.x) {
+        mbar_init(b < p.nw * p.slots ? &full[b] : xbar, 1);
         mbar_init_fence();
     }
     __syncthreads();

@@ -128,11 +128,11 @@ k_decode_chain(const ChainPlan p, int* __restrict__ err)
     // the program was uploaded when the chain was planned: plain loads
     for (int w = tid; w < min(p.n_phases, kChainWindow) * kDesc16; w += blockDim.x)
         reinterpret_cast<uint4*>(win)[w] = __ldg(reinterpret_cast<const uint4*>(p.phases) + w);
-    if (tid == 0) {
-        for (int s = 0; s < nw * p.slots; s++) mbar_init(&full[s], 1);
-        *dead = 0;
+    for (int b = tid; b < nw * p.slots; b += blockDim.x) {       // the barriers are set up by as many threads
+        mbar_init(&full[b], 1);
         mbar_init_fence();
     }
+    if (tid == 0) *dead = 0;
     __syncthreads();
     pdl_launch_dependents();
 

@@ -182,12 +182,9 @@ k_gemv_stream_q4k_q8k(const StreamPlan p, int* __restrict__ err)
         for (int w = tid; w < p.n_phases; w += blockDim.x)
             reinterpret_cast<uint2*>(smem + p.off_phase)[w] = __ldg(reinterpret_cast<const uint2*>(p.phases) + w);
     }
-    if (tid == 0) {
-        for (int s = 0; s < nw * p.slots; s++) mbar_init(&full[s], 1);
-        for (int b = 0; b < 2; b++) {
-            mbar_init(&xfull[b], 1);
-            mbar_init(&xempty[b], nw);
-        }
+    // the barriers are set up by as many threads: full[nw*slots], xfull[2], xempty[2] (an arrival per consumer warp)
+    for (int b = tid; b < nw * p.slots + 4; b += blockDim.x) {
+        mbar_init(&full[b], b >= nw * p.slots + 2 ? nw : 1);
         mbar_init_fence();
     }
     __syncthreads();

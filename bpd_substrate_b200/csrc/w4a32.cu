@@ -288,8 +288,8 @@ __global__ void __launch_bounds__(352, 1) k_w4a32_ring(const W4Plan p, int* __re
     uint8_t* xs = smem + p.off_x;                                // [2 nb][432]
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.off_bar);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) {
-        for (int s = 0; s < p.nw * p.slots; s++) mbar_init(&full[s], 1);
+    for (int b = tid; b < p.nw * p.slots; b += blockDim.x) {     // the barriers are set up by as many threads
+        mbar_init(&full[b], 1);
         mbar_init_fence();
     }
     __syncthreads();
