@@ -254,11 +254,14 @@ k_decode_chain(const ChainPlan p, int* __restrict__ err)
             }
         }
         // ---- publish: rows written by this CTA are visible device-wide before its arrival counts
+        // (the CTA's barrier orders every warp's stores before thread 0, whose fence is cumulative: one fence per CTA)
         CHAIN_TRACE(ph, 2);
-        __threadfence();
         named_bar_sync(2, nw * 32);
         if (*dead) break;
-        if (tid == 0) atomicAdd(p.arrive + ph, 1u);
+        if (tid == 0) {
+            __threadfence();
+            atomicAdd(p.arrive + ph, 1u);
+        }
         CHAIN_TRACE(ph, 3);
     }
 }

@@ -373,8 +373,10 @@ class DecodeChain:
     * ``"chain-separate"`` -- the reference's call sequence (gpu_rms_norm, gpu_silu, gpu_mul,
       gpu_add and one product per matrix);
     * ``"chain-persistent"`` -- ONE cooperative launch per token (plus the memset of its barrier
-      counters): the 4-phase program of ``"chain4"`` for all layers inside one kernel whose producer
-      warps stream the weights of all phases back to back (``bpdq_chain_run``).
+      counters): the 4-phase program of ``"chain4"`` for all layers inside one kernel whose warps refill
+      their own rings across the phases, so the weights of the next phase are on their way during the barrier
+      between phases; gate and up rows travel in pairs and the activation is formed where they meet
+      (``bpdq_chain_run``).
     """
 
     MODES = {"chain": 8, "chain4": 4, "chain-separate": 13, "chain-persistent": 0}

@@ -162,6 +162,25 @@ def test_chain_fused_equals_reference_call_sequence(chain):
     assert [chain.launches_per_token(m) for m in ("chain", "chain4", "chain-separate")] == [24, 12, 39]
 
 
+def test_chain_wide_rows(lib):
+    """Rows of 32 super-blocks: the product kernels take two rows per tile, and the one-launch program pairs ONE
+    row of the gate matrix with the same row of the up matrix per tile.  Same bits as the 13-call sequence."""
+    c = DecodeChain(hidden=8192, kv=256, ffn=1024, n_layers=2, seed=12, lib=lib)
+    try:
+        x0 = np.random.default_rng(6).standard_normal(c.hidden, dtype=np.float32)
+        results = []
+        for mode in ("chain-separate", "chain", "chain-persistent", "chain-persistent"):
+            c.set_state(x0)
+            c.enqueue_token(mode)
+            results.append(c.get_state())
+            assert lib.bpdq_last_status() == 0
+        assert np.isfinite(results[0]).all()
+        for other in results[1:]:
+            assert np.array_equal(results[0].view(np.uint32), other.view(np.uint32))
+    finally:
+        c.close()
+
+
 def records_as_q8k(raw, K):
     """The 144-byte records of a vector as the checker's 292-byte Q8_K blocks (group sums recomputed from the
     int8 values; the records' own sums are compared with them by the caller)."""
