@@ -8,7 +8,10 @@
 //   SwiGLU, residual add, argmax (lowest index)    bench/bpd_cpu.c:5504-5507, 5466, 4512-4529
 // Weights, caches and activations are device memory; the descriptor structs are host memory holding
 // device pointers, with the reference's field order.  Everything runs on one stream in the reference's
-// order; no kernel waits on another.
+// order; no kernel waits on another.  The small kernels are launched programmatically like the products: each lets the
+// launch behind it be scheduled at once (a product then fetches its first weights meanwhile) and waits for the
+// launch ahead of it before it touches memory, so activations and caches are read with plain loads, never through
+// the read-only path (only weights are).
 #include "bpdq_common.cuh"
 #include "../../include/bpdq.h"
 
@@ -54,9 +57,10 @@ __device__ __forceinline__ void cta_rmsnorm_row(const float* x, const float* __r
     }
 }
 
-__global__ void __launch_bounds__(256) k_rmsnorm_llama(const float* __restrict__ in, const float* __restrict__ w,
-                                                        float* __restrict__ out, int cols, float eps)
+__global__ void __launch_bounds__(256) k_rmsnorm_llama(const float* in, const float* __restrict__ w, float* out, int cols, float eps)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const float* x = in + (size_t)blockIdx.x * cols;
     double t = 0.0;
     for (int c = threadIdx.x; c < cols; c += 256) {
@@ -71,6 +75,8 @@ __global__ void __launch_bounds__(256) k_rmsnorm_llama(const float* __restrict__
 __global__ void __launch_bounds__(256) k_add_rmsnorm_llama(float* x_io, const float* r, const float* __restrict__ w, float* out,
                                                             int cols, float eps)   // out may be r
 {
+    pdl_launch_dependents();
+    pdl_wait();
     float* x = x_io + (size_t)blockIdx.x * cols;
     const float* rr = r + (size_t)blockIdx.x * cols;
     double t = 0.0;
@@ -123,10 +129,12 @@ __device__ __forceinline__ void rope_pair(float x0, float x1, int pair, int half
     }
 }
 
-__global__ void __launch_bounds__(256) k_rope_norm(const float* __restrict__ in, float* __restrict__ out,
-                                                    const int32_t* __restrict__ pos_ids, const float* __restrict__ freq_factors,
+__global__ void __launch_bounds__(256) k_rope_norm(const float* in, float* out, const int32_t* pos_ids,
+                                                    const float* __restrict__ freq_factors,
                                                     int n_tokens, int n_heads, int head_dim, int n_dims, float theta_scale)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int half = n_dims / 2;
     const long total = (long)n_tokens * n_heads * (head_dim / 2);
     for (long u = (long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long)gridDim.x * blockDim.x) {
@@ -146,13 +154,14 @@ __global__ void __launch_bounds__(256) k_rope_norm(const float* __restrict__ in,
 // and stored to its cache row, v stored to its cache row (f16 rounding of the same fp32 values the separate
 // steps round).  Thread = (token, head of q|k|v, pair).
 template <int F16>
-__global__ void __launch_bounds__(256) k_rope_qk_store_kv(float* __restrict__ q, const float* __restrict__ k,
-                                                           const float* __restrict__ v, void* __restrict__ k_cache,
-                                                           void* __restrict__ v_cache, const int32_t* __restrict__ pos_ids,
+__global__ void __launch_bounds__(256) k_rope_qk_store_kv(float* q, const float* k, const float* v, void* k_cache, void* v_cache,
+                                                           const int32_t* pos_ids,
                                                            const float* __restrict__ freq_factors, int n_tokens, int n_heads,
                                                            int n_kv_heads, int head_dim, int n_dims, float theta_scale,
-                                                           int max_seq_len, int* __restrict__ err)
+                                                           int max_seq_len, int* err)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const int half = n_dims / 2, pairs = head_dim / 2, heads = n_heads + 2 * n_kv_heads;
     const long total = (long)n_tokens * heads * pairs;
     for (long u = (long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long)gridDim.x * blockDim.x) {
@@ -192,10 +201,11 @@ __global__ void __launch_bounds__(256) k_rope_qk_store_kv(float* __restrict__ q,
 // cache[pos[t]][:] = f16(src[t][:]) (round to nearest even) or the fp32 copy.  A position outside
 // [0, max_seq_len) has no cache row: nothing is stored for that token and code 20 is recorded.
 template <int F16>
-__global__ void __launch_bounds__(256) k_kv_write(void* __restrict__ cache, const float* __restrict__ src,
-                                                   const int32_t* __restrict__ pos_ids, int n_tokens, int row, int max_seq_len,
-                                                   int* __restrict__ err)
+__global__ void __launch_bounds__(256) k_kv_write(void* cache, const float* src, const int32_t* pos_ids, int n_tokens, int row,
+                                                   int max_seq_len, int* err)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     const long total = (long)n_tokens * row;
     for (long u = (long)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (long)gridDim.x * blockDim.x) {
         const int t = (int)(u / row), i = (int)(u - (long)t * row);
@@ -218,10 +228,11 @@ __global__ void __launch_bounds__(256) k_kv_write(void* __restrict__ cache, cons
 // the reference adds them); normalisation by the reciprocal; then thread d adds v[ic][d] * w[ic] over
 // the rows in order.
 template <int F16>
-__global__ void __launch_bounds__(256) k_gqa_attn(const float* __restrict__ q, const void* __restrict__ kc,
-                                                   const void* __restrict__ vc, float* __restrict__ dst, int n_kv,
+__global__ void __launch_bounds__(256) k_gqa_attn(const float* q, const void* kc, const void* vc, float* dst, int n_kv,
                                                    int n_q_heads, int n_kv_heads, int head_dim, float scale, int kv_offset)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float sh[];
     float* scores = sh;                   // [n_kv]
     float* sq = sh + n_kv;                // [head_dim]
@@ -298,9 +309,10 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const float* __restrict__ q, c
     }
 }
 
-__global__ void __launch_bounds__(256) k_swiglu_f32(const float* __restrict__ gate, const float* __restrict__ up,
-                                                     float* __restrict__ dst, long n)
+__global__ void __launch_bounds__(256) k_swiglu_f32(const float* gate, const float* up, float* dst, long n)   // dst may be gate
 {
+    pdl_launch_dependents();
+    pdl_wait();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
         const float g = gate[i];
         dst[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, exp_rounded(-g))), up[i]);
@@ -308,13 +320,17 @@ __global__ void __launch_bounds__(256) k_swiglu_f32(const float* __restrict__ ga
 }
 __global__ void __launch_bounds__(256) k_add_f32(const float* a, const float* b, float* dst, long n)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
         dst[i] = __fadd_rn(a[i], b[i]);
 }
 
 // One CTA per row; the largest value wins, the lowest index among equals (v > best in index order).
-__global__ void __launch_bounds__(256) k_argmax_rows(const float* __restrict__ x, long long* __restrict__ out, int n)
+__global__ void __launch_bounds__(256) k_argmax_rows(const float* x, long long* out, int n)
 {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float s_v[256];
     __shared__ int s_i[256];
     const float* row = x + (size_t)blockIdx.x * n;
@@ -341,6 +357,24 @@ __global__ void __launch_bounds__(256) k_argmax_rows(const float* __restrict__ x
     if (threadIdx.x == 0) out[blockIdx.x] = s_i[0];
 }
 
+// A launch that may be scheduled while the launch ahead of it on the stream still runs (every kernel here waits for that
+// launch before it touches memory).
+template <typename... KArgs, typename... Args>
+static int launch_ordered(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t s, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = tuning().pdl ? 1 : 0;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...));
+}
+
 static int grid_1d(long n)
 {
     long want = (n + 255) / 256, cap = (long)sm_count() * 8;
@@ -361,8 +395,8 @@ static int launch_attn(const float* q, const void* kc, const void* vc, float* ds
         if (rc) return rc;
         attr_set[f16 ? 1 : 0][dev] = true;
     }
-    if (f16) k_gqa_attn<1><<<n_q * H, 256, sh, s>>>(q, kc, vc, dst, n_kv, H, HKV, D, scale, kv_offset);
-    else k_gqa_attn<0><<<n_q * H, 256, sh, s>>>(q, kc, vc, dst, n_kv, H, HKV, D, scale, kv_offset);
+    if (f16) launch_ordered(k_gqa_attn<1>, n_q * H, 256, sh, s, q, kc, vc, dst, n_kv, H, HKV, D, scale, kv_offset);
+    else launch_ordered(k_gqa_attn<0>, n_q * H, 256, sh, s, q, kc, vc, dst, n_kv, H, HKV, D, scale, kv_offset);
     return check_cuda(cudaGetLastError());
 }
 
@@ -371,7 +405,7 @@ static int launch_rope(const float* in, float* out, const int32_t* pos_ids, cons
 {
     // the step between consecutive pairs' angles, computed where the reference computes it: on the host
     const float theta_scale = powf(freq_base, -2.0f / (float)n_dims);
-    k_rope_norm<<<grid_1d((long)n_tokens * n_heads * head_dim / 2), 256, 0, s>>>(in, out, pos_ids, ff, n_tokens, n_heads,
+    launch_ordered(k_rope_norm, grid_1d((long)n_tokens * n_heads * head_dim / 2), 256, 0, s, in, out, pos_ids, ff, n_tokens, n_heads,
                                                                                  head_dim, n_dims, theta_scale);
     return check_cuda(cudaGetLastError());
 }
@@ -379,8 +413,8 @@ static int launch_rope(const float* in, float* out, const int32_t* pos_ids, cons
 static int launch_kv_write(void* cache, const float* src, const int32_t* pos_ids, int n_tokens, int row, int f16, int max_seq_len,
                            cudaStream_t s)
 {
-    if (f16) k_kv_write<1><<<grid_1d((long)n_tokens * row), 256, 0, s>>>(cache, src, pos_ids, n_tokens, row, max_seq_len, device_error_flag());
-    else k_kv_write<0><<<grid_1d((long)n_tokens * row), 256, 0, s>>>(cache, src, pos_ids, n_tokens, row, max_seq_len, device_error_flag());
+    if (f16) launch_ordered(k_kv_write<1>, grid_1d((long)n_tokens * row), 256, 0, s, cache, src, pos_ids, n_tokens, row, max_seq_len, device_error_flag());
+    else launch_ordered(k_kv_write<0>, grid_1d((long)n_tokens * row), 256, 0, s, cache, src, pos_ids, n_tokens, row, max_seq_len, device_error_flag());
     return check_cuda(cudaGetLastError());
 }
 
@@ -429,9 +463,9 @@ static int launch_rope_qk_store_kv(float* q, const float* k, const float* v, voi
 {
     const float theta_scale = powf(freq_base, -2.0f / (float)n_dims);
     const int grid = grid_1d((long)n_tokens * (H + 2 * HKV) * (D / 2));
-    if (f16) k_rope_qk_store_kv<1><<<grid, 256, 0, s>>>(q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale,
+    if (f16) launch_ordered(k_rope_qk_store_kv<1>, grid, 256, 0, s, q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale,
                                                         max_seq_len, device_error_flag());
-    else k_rope_qk_store_kv<0><<<grid, 256, 0, s>>>(q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale,
+    else launch_ordered(k_rope_qk_store_kv<0>, grid, 256, 0, s, q, k, v, k_cache, v_cache, pos_ids, ff, n_tokens, H, HKV, D, n_dims, theta_scale,
                                                     max_seq_len, device_error_flag());
     return check_cuda(cudaGetLastError());
 }
@@ -453,7 +487,7 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
     // whenever two or more query heads share a KV head; otherwise V is computed after K is stored)
     const bool kv_together = (size_t)2 * row <= (size_t)H * D;
     float* vbuf = kv_together ? s3 + (size_t)n_tokens * row : s3;
-    if (!x_normed) k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, lw->attn_norm_w, s1, E, cfg->rms_eps);
+    if (!x_normed) launch_ordered(k_rmsnorm_llama, n_tokens, 256, 0, s, x, lw->attn_norm_w, s1, E, cfg->rms_eps);
     {
         const uint8_t* Ws[3] = {lw->w_q, lw->w_k, lw->w_v};
         const uint8_t* Ts[3] = {lt ? lt->w_q : nullptr, lt ? lt->w_k : nullptr, lt ? lt->w_v : nullptr};
@@ -476,7 +510,7 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
                           cfg->kv_cache_f16, s)))
         return rc;
     if ((rc = product(lw->w_o, lt ? lt->w_o : nullptr, s1, s2, n_tokens, E, H * D, s, ws))) return rc;
-    k_add_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, s2, lw->ffn_norm_w, s1, E, cfg->rms_eps);
+    launch_ordered(k_add_rmsnorm_llama, n_tokens, 256, 0, s, x, s2, lw->ffn_norm_w, s1, E, cfg->rms_eps);
     {
         const uint8_t* Ws[2] = {lw->w_gate, lw->w_up};
         const uint8_t* Ts[2] = {lt ? lt->w_gate : nullptr, lt ? lt->w_up : nullptr};
@@ -484,10 +518,10 @@ static int block_forward(float* x, const bpd_llama_layer_weights* lw, const bpd_
         const int Ns[2] = {F, F};
         if ((rc = products_shared_input(2, Ws, Ts, outs, Ns, s1, n_tokens, E, s, ws))) return rc;
     }
-    k_swiglu_f32<<<grid_1d((long)n_tokens * F), 256, 0, s>>>(s2, s3, s2, (long)n_tokens * F);
+    launch_ordered(k_swiglu_f32, grid_1d((long)n_tokens * F), 256, 0, s, s2, s3, s2, (long)n_tokens * F);
     if ((rc = product(lw->w_down, lt ? lt->w_down : nullptr, s2, s1, n_tokens, E, F, s, ws))) return rc;
-    if (fuse_next) k_add_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, s1, next_norm_w, s1, E, cfg->rms_eps);
-    else k_add_f32<<<grid_1d((long)n_tokens * E), 256, 0, s>>>(x, s1, x, (long)n_tokens * E);
+    if (fuse_next) launch_ordered(k_add_rmsnorm_llama, n_tokens, 256, 0, s, x, s1, next_norm_w, s1, E, cfg->rms_eps);
+    else launch_ordered(k_add_f32, grid_1d((long)n_tokens * E), 256, 0, s, x, s1, x, (long)n_tokens * E);
     return check_cuda(cudaGetLastError());
 }
 
@@ -503,7 +537,7 @@ int bpd_rmsnorm_llama_cuda(const float* input, const float* weight, float* outpu
 {
     if (n_rows < 0 || row_len <= 0 || (n_rows > 0 && (!input || !output))) return latch(BPDQ_ERR_ARG);
     if (n_rows == 0) return 0;
-    k_rmsnorm_llama<<<n_rows, 256, 0, (cudaStream_t)stream>>>(input, weight, output, row_len, eps);
+    launch_ordered(k_rmsnorm_llama, n_rows, 256, 0, (cudaStream_t)stream, input, weight, output, row_len, eps);
     int rc = check_cuda(cudaGetLastError());
     return rc ? latch(rc) : 0;
 }
@@ -550,7 +584,7 @@ int bpd_swiglu_fuse_cuda(const float* gate, const float* up, float* dst, int n, 
 {
     if (n < 0 || (n > 0 && (!gate || !up || !dst))) return latch(BPDQ_ERR_ARG);
     if (n == 0) return 0;
-    k_swiglu_f32<<<grid_1d(n), 256, 0, (cudaStream_t)stream>>>(gate, up, dst, n);
+    launch_ordered(k_swiglu_f32, grid_1d(n), 256, 0, (cudaStream_t)stream, gate, up, dst, n);
     int rc = check_cuda(cudaGetLastError());
     return rc ? latch(rc) : 0;
 }
@@ -558,7 +592,7 @@ int bpd_argmax_dim_cuda(const float* x, long long* out, int outer, int dim_size,
 {
     if (outer < 0 || dim_size < 1 || inner != 1 || (outer > 0 && (!x || !out))) return latch(BPDQ_ERR_ARG);
     if (outer == 0) return 0;
-    k_argmax_rows<<<outer, 256, 0, (cudaStream_t)stream>>>(x, out, dim_size);
+    launch_ordered(k_argmax_rows, outer, 256, 0, (cudaStream_t)stream, x, out, dim_size);
     int rc = check_cuda(cudaGetLastError());
     return rc ? latch(rc) : 0;
 }
@@ -611,10 +645,10 @@ static int llama_forward(const int32_t* token_ids, int n_tokens, const bpd_llama
                            last ? weights->output_norm_w : weights->layers[layer + 1].attn_norm_w, s, ws);
         if (rc) return latch(rc);
     }
-    if (cfg->n_layers == 0) k_rmsnorm_llama<<<n_tokens, 256, 0, s>>>(x, weights->output_norm_w, s1, E, cfg->rms_eps);
+    if (cfg->n_layers == 0) launch_ordered(k_rmsnorm_llama, n_tokens, 256, 0, s, x, weights->output_norm_w, s1, E, cfg->rms_eps);
     if ((rc = product(weights->output_w, tiles ? tiles->output_w : nullptr, s1, logits_out, n_tokens, cfg->vocab_size, E, s, ws)))
         return rc;
-    if (token_out) k_argmax_rows<<<n_tokens, 256, 0, s>>>(logits_out, token_out, cfg->vocab_size);
+    if (token_out) launch_ordered(k_argmax_rows, n_tokens, 256, 0, s, logits_out, token_out, cfg->vocab_size);
     rc = check_cuda(cudaGetLastError());
     return rc ? latch(rc) : 0;
 }

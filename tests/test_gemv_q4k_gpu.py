@@ -345,3 +345,47 @@ def test_long_stream_many_phases_and_two_launches(lib, oracle):
     # too small a workspace is refused
     assert not lib.bpdq_gemv_stream_create(n, descs, ws.ptr, 1024)
     lib.bpdq_clear_status()
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5])
+def test_stream_of_random_shapes(lib, oracle, seed):
+    """Seeded random launches of the persistent kernel: 1-40 products, 1-600 rows, 1-65 super-blocks per row
+    (65 = rows that arrive in two pieces), some products sharing a vector.  Every output against the CPU checker,
+    and the launch repeated gives the same bits."""
+    from bpd_substrate_b200 import capi
+    rng = np.random.default_rng(1000 + seed)
+    n = int(rng.integers(1, 41))
+    ks = [256, 512, 1024, 2048, 4096, 8192, 14336, 65 * 256]
+    shapes = [(int(rng.integers(1, 601)), int(ks[rng.integers(0, len(ks))])) for _ in range(n)]
+    hW = [synth.q4k_matrix(m, k, rng) for m, k in shapes]
+    hx, dx = [], []
+    for j, (m, k) in enumerate(shapes):
+        share = [i for i in range(j) if shapes[i][1] == k]
+        if share and rng.random() < 0.3:
+            i = share[0]
+            hx.append(hx[i])
+            dx.append(dx[i])
+        else:
+            hx.append(synth.activations(k, rng))
+            dx.append(Dev(lib, hx[-1]))
+    dW = [Dev(lib, w) for w in hW]
+    outs = [Dev(lib, nbytes=m * 4, fill=0xFF) for m, _ in shapes]
+    descs = (capi.GemvDesc * n)(*[capi.GemvDesc(dW[j].ptr, dx[j].ptr, outs[j].ptr, m, k) for j, (m, k) in enumerate(shapes)])
+    ws_bytes = lib.bpdq_batch_workspace_bytes(n, descs)
+    ws = Dev(lib, nbytes=ws_bytes, fill=0xAB)
+    h = lib.bpdq_gemv_stream_create(n, descs, ws.ptr, ws_bytes)
+    assert h
+    assert lib.bpdq_gemv_stream_run(h, None) == 0
+    lib.bpdq_sync()
+    assert lib.bpdq_last_status() == 0
+    first = [o.read(np.float32) for o in outs]
+    for j, (m, k) in enumerate(shapes):
+        _, ref64 = oracle.qmatmul_q4k_q8k(hW[j], oracle.quant_q8_K(hx[j]), m, k)
+        assert normwise(first[j], ref64) <= TOL, (seed, j, m, k)
+    for o in outs:
+        lib.bpdq_memset_async(o.ptr, 0xFF, o.nbytes, None)
+    assert lib.bpdq_gemv_stream_run(h, None) == 0
+    lib.bpdq_sync()
+    for j in range(n):
+        assert np.array_equal(outs[j].read(np.uint32), first[j].view(np.uint32)), (seed, j)
+    lib.bpdq_gemv_stream_destroy(h)
