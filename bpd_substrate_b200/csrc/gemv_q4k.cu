@@ -188,14 +188,12 @@ k_gemv_q4k_q8k(const void* __restrict__ xin, int K, const GemvPlan p, int* __res
     const uint32_t tile_bytes_full = (uint32_t)R * p.row_bytes;
     BPDQ_TRACE(0);
 
-    if (tid == 0) {
-        for (int s = 0; s < p.ng * p.slots; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], p.kc);
-        }
-        *abort_flag = 0;
+    for (int s = tid; s < p.ng * p.slots; s += blockDim.x) {     // the barriers are set up by as many threads
+        mbar_init(&full[s], 1);
+        mbar_init(&empty[s], p.kc);
         mbar_init_fence();
     }
+    if (tid == 0) *abort_flag = 0;
     __syncthreads();
 
     // Programmatic dependent launch: the next kernel in the stream may start once every CTA
