@@ -126,26 +126,6 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-// two signed 16-bit halves of a times the low (lo) or high (hi) two unsigned bytes of b
-__device__ __forceinline__ int dp2a_lo_su(uint32_t a16x2, uint32_t b8x4, int c)
-{
-    int d;
-    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a16x2), "r"(b8x4), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp2a_hi_su(uint32_t a16x2, uint32_t b8x4, int c)
-{
-    int d;
-    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a16x2), "r"(b8x4), "r"(c));
-    return d;
-}
-// a - b as an instruction of its own: subtraction issues at full rate on this GPU, a second mask would not
-__device__ __forceinline__ uint32_t sub_u32(uint32_t a, uint32_t b)
-{
-    uint32_t d;
-    asm("sub.u32 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c)
 {
     int d;

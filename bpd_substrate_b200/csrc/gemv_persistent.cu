@@ -79,7 +79,11 @@ __device__ __forceinline__ void pair_tile(const uint8_t* tile_smem, const uint8_
             xr[0][4 * i + 3] = v.w;
         }
         const uint4 tail = rec[8];
-        const uint32_t bs[1][2] = {{tail.x, tail.y}};
+        int bs[1][4];
+        bs[0][0] = (int)(short)(tail.x & 0xFFFFu);
+        bs[0][1] = (int)(short)(tail.x >> 16);
+        bs[0][2] = (int)(short)(tail.y & 0xFFFFu);
+        bs[0][3] = (int)(short)(tail.y >> 16);
         float xd[1] = {__uint_as_float(tail.z)};
         const uint8_t* sbp = tile_smem + (size_t)(hb >> 1) * BPDQ_Q4K_BYTES;
 #pragma unroll

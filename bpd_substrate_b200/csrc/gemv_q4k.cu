@@ -253,7 +253,7 @@ k_gemv_q4k_q8k(const void* __restrict__ xin, int K, const GemvPlan p, int* __res
     BPDQ_TRACE(3);
 
     uint32_t xr[T][32];
-    uint32_t bs[T][2];               // the four sub-block sums as int16 pairs
+    int bs[T][4];
     float xd[T];
 #pragma unroll
     for (int t = 0; t < T; t++) {
@@ -273,16 +273,13 @@ k_gemv_q4k_q8k(const void* __restrict__ xin, int K, const GemvPlan p, int* __res
             for (int i = 0; i < 32; i++) xr[t][i] = 0;
             xd[t] = 0.0f;
         }
-        int sums[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             int s = 0;
 #pragma unroll
             for (int w = 0; w < 8; w++) s = dp4a_ss(xr[t][8 * j + w], 0x01010101u, s);
-            sums[j] = s;
+            bs[t][j] = s;
         }
-        bs[t][0] = ((uint32_t)sums[0] & 0xFFFFu) | ((uint32_t)sums[1] << 16);
-        bs[t][1] = ((uint32_t)sums[2] & 0xFFFFu) | ((uint32_t)sums[3] << 16);
     }
     BPDQ_TRACE(4);
 

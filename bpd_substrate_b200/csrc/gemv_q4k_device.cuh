@@ -55,14 +55,14 @@ __device__ __forceinline__ void quantize_block_256(const float4& v0, const float
 // ---------------------------------------------------------------- inner product of one half-super-block
 
 // sbp: shared-memory super-block (144 B).  half: which four sub-blocks.  xr[t]: this lane's
-// 128 quantized activations of token t, bs[t]: their four sub-block sums as int16 pairs (two words), xd[t]: the Q8_K
-// block scale.  Masks, shifts, dp4a and integer multiplies issue at half rate on this GPU and bound the loop: the
-// high nibbles are q - (q & 0x0F..) (a full-rate subtraction, 16 x their value, divided out exactly once per
-// sub-block) and the mins meet the sub-block sums in two dp2a.  dbg: optional global int32[8] slot of this (row, super-block) for the exact
-// sub-block dots of token 0.
+// 128 quantized activations of token t, bs[t][j]: their per-sub-block sums, xd[t]: the Q8_K
+// block scale.  dbg: optional global int32[8] slot of this (row, super-block) for the exact
+// sub-block dots of token 0.  (Tried on this loop and not kept: the high nibbles by a full-rate subtraction
+// q - (q & 0x0F..) instead of a second mask, within +-1 % on the benchmark step depending on how the compiler
+// schedules around it; the mins through two dp2a on packed sub-block sums instead of four multiply-adds, -3.5 %.)
 template <int T, int LAYOUT>
 __device__ __forceinline__ void half_block_fma(const uint8_t* sbp, int half, const uint32_t (&xr)[T][32],
-                                               const uint32_t (&bs)[T][2], const float (&xd)[T], float (&acc)[T],
+                                               const int (&bs)[T][4], const float (&xd)[T], float (&acc)[T],
                                                int32_t* dbg)
 {
     const uint4 hdr = *reinterpret_cast<const uint4*>(sbp);
@@ -88,9 +88,8 @@ __device__ __forceinline__ void half_block_fma(const uint8_t* sbp, int half, con
                 int lo = 0, hi = 0;
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
-                    const uint32_t ql = qw[w] & 0x0F0F0F0Fu;
-                    lo = dp4a_us(ql, xr[t][8 * i + w], lo);
-                    hi = dp4a_us(sub_u32(qw[w], ql), xr[t][8 * i + 4 + w], hi);  // 16 x the high-nibble dot
+                    lo = dp4a_us(qw[w] & 0x0F0F0F0Fu, xr[t][8 * i + w], lo);
+                    hi = dp4a_us(qw[w] & 0xF0F0F0F0u, xr[t][8 * i + 4 + w], hi);  // 16 x the high-nibble dot
                 }
                 const int dot = lo + (hi >> 4);  // exact: hi is a multiple of 16
                 isum[t] += sc * dot;
@@ -109,9 +108,8 @@ __device__ __forceinline__ void half_block_fma(const uint8_t* sbp, int half, con
                 int lo = 0, hi = 0;
 #pragma unroll
                 for (int w = 0; w < 8; w++) {
-                    const uint32_t ql = qw[w] & 0x0F0F0F0Fu;
-                    lo = dp4a_us(ql, xr[t][16 * c + w], lo);
-                    hi = dp4a_us(sub_u32(qw[w], ql), xr[t][16 * c + 8 + w], hi);
+                    lo = dp4a_us(qw[w] & 0x0F0F0F0Fu, xr[t][16 * c + w], lo);
+                    hi = dp4a_us(qw[w] & 0xF0F0F0F0u, xr[t][16 * c + 8 + w], hi);
                 }
                 hi >>= 4;
                 isum[t] += sc_lo * lo + sc_hi * hi;
@@ -124,7 +122,9 @@ __device__ __forceinline__ void half_block_fma(const uint8_t* sbp, int half, con
     }
 #pragma unroll
     for (int t = 0; t < T; t++) {
-        const int msum = dp2a_hi_su(bs[t][1], mn4, dp2a_lo_su(bs[t][0], mn4, 0));
+        int msum = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) msum += (int)byte_of(mn4, j) * bs[t][j];
         acc[t] = fmaf(d * xd[t], (float)isum[t], acc[t]);
         acc[t] = fmaf(-(dmin * xd[t]), (float)msum, acc[t]);
     }
@@ -326,7 +326,11 @@ __device__ __forceinline__ void batch_tile(const uint8_t* tile_smem, const uint8
             xr[0][4 * i + 3] = v.w;
         }
         const uint4 tail = rec[8];
-        const uint32_t bs[1][2] = {{tail.x, tail.y}};
+        int bs[1][4];
+        bs[0][0] = (int)(short)(tail.x & 0xFFFFu);
+        bs[0][1] = (int)(short)(tail.x >> 16);
+        bs[0][2] = (int)(short)(tail.y & 0xFFFFu);
+        bs[0][3] = (int)(short)(tail.y >> 16);
         float xd[1] = {__uint_as_float(tail.z)};
         const uint8_t* sbp = tile_smem + (size_t)(hb >> 1) * BPDQ_Q4K_BYTES;
 #pragma unroll
