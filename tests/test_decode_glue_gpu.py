@@ -181,6 +181,54 @@ def test_chain_wide_rows(lib):
         c.close()
 
 
+@pytest.mark.parametrize("tile_bytes,stages,warps", [(4096, 2, 4), (8192, 3, 8), (9216, 4, 6), (2048, 2, 16), (9216, 2, 11)])
+def test_ring_geometries_give_the_same_bits(lib, tile_bytes, stages, warps):
+    """Other tile sizes, ring depths and warp counts (bpdq_set_tuning) change how often a warp's ring wraps and which
+    warp folds which rows, not the results: the dependent chain in its launch-per-step, fused and one-launch forms and
+    a stream of independent products give the bits of the default geometry."""
+    rng = np.random.default_rng(21)
+    c = DecodeChain(hidden=1024, kv=256, ffn=2816, n_layers=2, seed=13, lib=lib)
+    shapes = [(300, 1024), (64, 4096), (1, 256), (130, 2816), (77, 4096)]
+    Ws = [Dev(lib, synth.q4k_matrix(m, k, rng)) for m, k in shapes]
+    xs = [Dev(lib, synth.activations(k, rng)) for _, k in shapes]
+    x0 = rng.standard_normal(c.hidden, dtype=np.float32)
+
+    def run_all():
+        got = []
+        for mode in ("chain", "chain4", "chain-persistent"):
+            if c.program:
+                lib.bpdq_chain_destroy(c.program)
+                c.program = None
+            c.set_state(x0)
+            c.enqueue_token(mode)
+            got.append(c.get_state().view(np.uint32))
+        outs = [Dev(lib, nbytes=m * 4, fill=0xFF) for m, _ in shapes]
+        n = len(shapes)
+        descs = (capi.GemvDesc * n)(*[capi.GemvDesc(Ws[j].ptr, xs[j].ptr, outs[j].ptr, m, k) for j, (m, k) in enumerate(shapes)])
+        ws_bytes = lib.bpdq_batch_workspace_bytes(n, descs)
+        ws = Dev(lib, nbytes=ws_bytes)
+        h = lib.bpdq_gemv_stream_create(n, descs, ws.ptr, ws_bytes)
+        assert h
+        assert lib.bpdq_gemv_stream_run(h, None) == 0
+        lib.bpdq_sync()
+        lib.bpdq_gemv_stream_destroy(h)
+        got += [o.read(np.uint32) for o in outs]
+        assert lib.bpdq_last_status() == 0
+        return got
+
+    try:
+        want = run_all()
+        for other in want[1:3]:
+            assert np.array_equal(want[0], other)
+        lib.bpdq_set_tuning(tile_bytes, stages, 0, warps, -1)
+        got = run_all()
+        for a, b in zip(want, got):
+            assert np.array_equal(a, b)
+    finally:
+        lib.bpdq_set_tuning(8192, 2, 0, 16, -1)     # the library's defaults
+        c.close()
+
+
 def records_as_q8k(raw, K):
     """The 144-byte records of a vector as the checker's 292-byte Q8_K blocks (group sums recomputed from the
     int8 values; the records' own sums are compared with them by the caller)."""
