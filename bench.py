@@ -255,6 +255,7 @@ def run_gpu(args):
     else:
         ls = LayerSet(shapes, args.layers, seed=2000 + (rank if args.workload == "mistral7b" else 0), row_shard=shard,
                       d_out=out_local.data_ptr() if out_local is not None else None, tokens=args.tokens)
+    ls.even_ranges = bool(args.even_ranges)
     step_bytes = ls.algorithmic_bytes()
     launches = ls.launches_per_step(schedule)
     # launches of the dominant kernel (the batched schedule adds one small quantizer per layer,
@@ -497,6 +498,7 @@ def main():
                          "one cooperative launch with grid-wide barriers between dependent phases")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-check", action="store_true", help="skip the comparison of one layer with the CPU checker")
+    ap.add_argument("--even-ranges", action="store_true", help="end-to-end leg: ranges of equal size instead of tapered ones")
     ap.add_argument("--copy-chunks", type=int, default=4,
                     help="end-to-end leg: ranges of layers whose host copies run on their own streams under the other "
                          "ranges' GEMVs (1: copy in, step, copy out in sequence)")

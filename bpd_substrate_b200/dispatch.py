@@ -96,6 +96,7 @@ class LayerSet:
         self.ws = None             # scratch for quantized activations (batched schedule)
         self.stream_plans = {}     # (first, last) -> (plan, scratch) of the persistent schedule
         self.copy_streams = self.copy_events = None   # second and third stream of step_host
+        self.even_ranges = False                      # True: step_host's ranges of layers all the same size
         capi.check(lib.bpdq_last_status(), "LayerSet setup")
 
     # ---- sizes
@@ -275,8 +276,7 @@ class LayerSet:
             self.copy_streams = (lib.bpdq_stream_create(), lib.bpdq_stream_create())
             self.copy_events = [(lib.bpdq_event_create(), lib.bpdq_event_create()) for _ in range(self.n_layers)]
         s_in, s_out = self.copy_streams
-        bounds = [self.n_layers * c // n for c in range(n + 1)]
-        ranges = [(bounds[c], bounds[c + 1]) for c in range(n)]
+        ranges = self.host_ranges(chunks)
         for c, (first, last) in enumerate(ranges):
             begin, nbytes = self.layer_input_range(first, last)
             capi.check(lib.bpdq_h2d_async(self.d_x + begin, x_host_ptr + begin, nbytes, s_in))
@@ -296,8 +296,17 @@ class LayerSet:
     def host_ranges(self, chunks):
         """The ranges of layers that step_host(chunks=...) runs as separate recordings."""
         n = max(1, min(chunks, self.n_layers))
-        bounds = [self.n_layers * c // n for c in range(n + 1)]
-        return [None] if n == 1 else [(bounds[c], bounds[c + 1]) for c in range(n)]
+        if n == 1:
+            return [None]
+        # Only the first range's copy-in and the last range's copy-out cannot hide behind other ranges' GEMVs, so
+        # the ranges taper towards both ends (1 : 2 : 4 ... 4 : 2 : 1) when there are layers enough for that.
+        taper = [min(1 << c, 1 << (n - 1 - c), 4) for c in range(n)] if self.n_layers >= 2 * n and not self.even_ranges else [1] * n
+        total, acc, bounds = sum(taper), 0, [0]
+        for c in range(n):
+            acc += taper[c]
+            bounds.append(max(bounds[-1] + 1, min(self.n_layers - (n - 1 - c), round(self.n_layers * acc / total))))
+        bounds[-1] = self.n_layers
+        return [(bounds[c], bounds[c + 1]) for c in range(n)]
 
     def layer_input_range(self, first, last):
         """(byte offset, bytes) of the activations of layers [first, last) in the input arena."""
