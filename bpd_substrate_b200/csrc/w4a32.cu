@@ -311,9 +311,22 @@ __global__ void __launch_bounds__(352, 1) k_w4a32_ring(const W4Plan p, int* __re
     for (int k = 0; k < p.slots && lv < p.n_tiles; k++) issue(k);     // weights never depend on the launch before
     // the activation vector may come from the launch before: wait for it, then every CTA makes its own fixed-point copy
     pdl_wait();
-    for (int b = warp; b < p.nb; b += p.nw) {
-        const float4* xb = reinterpret_cast<const float4*>(p.x + (size_t)b * 256);
-        w4_write_records(__ldcg(xb + lane), __ldcg(xb + 32 + lane), xs + (size_t)(2 * b) * kW4RecBytes, lane);
+    for (int b0 = warp; b0 < p.nb; b0 += 4 * p.nw) {      // four blocks' loads in flight per warp
+        float4 v[4][2];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int b = b0 + i * p.nw;
+            if (b < p.nb) {
+                const float4* xb = reinterpret_cast<const float4*>(p.x + (size_t)b * 256);
+                v[i][0] = __ldcg(xb + lane);
+                v[i][1] = __ldcg(xb + 32 + lane);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int b = b0 + i * p.nw;
+            if (b < p.nb) w4_write_records(v[i][0], v[i][1], xs + (size_t)(2 * b) * kW4RecBytes, lane);
+        }
     }
     __syncthreads();
     int slot = 0;
