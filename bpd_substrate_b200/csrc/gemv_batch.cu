@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(256) k_quant_records(const QuantVectors q, uin
 // those of k_rms_norm in decode_ops.cu (lib/kernel_templates_llama.pl:529-593 of the reference):
 // per-thread fmaf chain over c = t, t+256, ..., butterfly over the warp, the eight warp sums added
 // in order, scale = rsqrtf(sum/cols + eps), y = (x*scale)*w; then the rule of quantize_block_256.
-__global__ void __launch_bounds__(256) k_rmsnorm_records(const float* __restrict__ in, const float* __restrict__ w,
+__global__ void __launch_bounds__(512) k_rmsnorm_records(const float* __restrict__ in, const float* __restrict__ w,
                                                           uint8_t* __restrict__ records, int cols, float eps)
 {
     __shared__ float s_sum[8];
@@ -68,32 +68,51 @@ __global__ void __launch_bounds__(256) k_rmsnorm_records(const float* __restrict
     pdl_wait();   // the row is the previous product's output (residual stream)
     const float* x = in + (size_t)blockIdx.x * cols;
     uint8_t* rec = records + (size_t)blockIdx.x * (cols / 256) * 2 * kXqStride;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    float t = 0.0f;
-    // (data written by the launch before this one is read past L1: ld.global.cg).  The chain of FMAs
-    // is k_rms_norm's, but sixteen loads go out before the first of them is used: one L2 round trip
-    // per 4096 columns instead of sixteen.  A column past the end contributes fmaf(0, 0, t) = t.
-    for (int base = 0; base < cols; base += 16 * 256) {
-        float v[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            const int c = base + i * 256 + (int)threadIdx.x;
-            v[i] = c < cols ? __ldcg(x + c) : 0.0f;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; i++) t = fmaf(v[i], v[i], t);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (int)blockDim.x >> 5, nb = cols / 256;
+    // Sixteen warps: the first eight form the sum of squares the way k_rms_norm's 256 threads do; all sixteen then scale
+    // and quantize a 256-block each.  The block a warp will scale is fetched before the sum (it comes from L2, its
+    // weights from HBM), so that latency runs under the sum instead of after it.
+    float4 a0, a1, w0, w1;
+    if (warp < nb) {
+        const float4* xb = reinterpret_cast<const float4*>(x + (size_t)warp * 256);
+        const float4* wb = reinterpret_cast<const float4*>(w + (size_t)warp * 256);
+        a0 = __ldcg(xb + lane);
+        a1 = __ldcg(xb + 32 + lane);
+        w0 = __ldg(wb + lane);
+        w1 = __ldg(wb + 32 + lane);
     }
-    t = warp_sum(t);
-    if (lane == 0) s_sum[warp] = t;
+    if (threadIdx.x < 256) {
+        float t = 0.0f;
+        // (data written by the launch before this one is read past L1: ld.global.cg).  The chain of FMAs
+        // is k_rms_norm's, but sixteen loads go out before the first of them is used: one L2 round trip
+        // per 4096 columns instead of sixteen.  A column past the end contributes fmaf(0, 0, t) = t.
+        for (int base = 0; base < cols; base += 16 * 256) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int c = base + i * 256 + (int)threadIdx.x;
+                v[i] = c < cols ? __ldcg(x + c) : 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i++) t = fmaf(v[i], v[i], t);
+        }
+        t = warp_sum(t);
+        if (lane == 0) s_sum[warp] = t;
+    }
     __syncthreads();
     float tot = s_sum[0];
 #pragma unroll
     for (int i = 1; i < 8; i++) tot += s_sum[i];
     const float scale = rsqrtf(tot / (float)cols + eps);
-    for (int b = warp; b < cols / 256; b += 8) {
-        const float4* xb = reinterpret_cast<const float4*>(x + (size_t)b * 256);
-        const float4* wb = reinterpret_cast<const float4*>(w + (size_t)b * 256);
-        const float4 a0 = __ldcg(xb + lane), a1 = __ldcg(xb + 32 + lane), w0 = __ldg(wb + lane), w1 = __ldg(wb + 32 + lane);
+    for (int b = warp; b < nb; b += n_warps) {
+        if (b != warp) {
+            const float4* xb = reinterpret_cast<const float4*>(x + (size_t)b * 256);
+            const float4* wb = reinterpret_cast<const float4*>(w + (size_t)b * 256);
+            a0 = __ldcg(xb + lane);
+            a1 = __ldcg(xb + 32 + lane);
+            w0 = __ldg(wb + lane);
+            w1 = __ldg(wb + 32 + lane);
+        }
         const float4 v0 = make_float4(a0.x * scale * w0.x, a0.y * scale * w0.y, a0.z * scale * w0.z, a0.w * scale * w0.w);
         const float4 v1 = make_float4(a1.x * scale * w1.x, a1.y * scale * w1.y, a1.z * scale * w1.z, a1.w * scale * w1.w);
         write_records(v0, v1, rec + (size_t)(2 * b) * kXqStride, lane);
@@ -693,7 +712,7 @@ int bpd_rmsnorm_q8k_records_cuda(const float* x, const float* w, void* records, 
     if (rows < 0 || K <= 0 || (K % 256) != 0 || (rows > 0 && (!x || !w || !records))) return latch(BPDQ_ERR_ARG);
     if (rows == 0) return 0;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)records & 15)) return latch(BPDQ_ERR_ALIGN);
-    int rc = launch_glue(k_rmsnorm_records, rows, (cudaStream_t)stream, x, w, (uint8_t*)records, K, eps);
+    int rc = launch_glue<512>(k_rmsnorm_records, rows, (cudaStream_t)stream, x, w, (uint8_t*)records, K, eps);
     return rc ? latch(rc) : 0;
 }
 

@@ -505,13 +505,13 @@ int gemm_q4k_q8k(const uint8_t* W, const void* x, float* out, int tokens, int M,
 int make_batch_plan(const BatchDesc* d, int n, BatchPlan& p, int fmt = 0, int ctas_per_sm = 1);
 int launch_batch_plan(const BatchPlan& p, int fmt, int layout, cudaStream_t s);
 
-// a 256-thread kernel launched programmatically behind the launch before it
-template <typename Kern, typename... Args>
+// a small kernel (256 threads per CTA unless said otherwise) launched programmatically behind the launch before it
+template <int THREADS = 256, typename Kern, typename... Args>
 static int launch_glue(Kern kern, int grid, cudaStream_t s, Args... args)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(THREADS);
     cfg.stream = s;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
