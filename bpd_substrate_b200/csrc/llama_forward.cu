@@ -57,10 +57,68 @@ __device__ __forceinline__ void cta_rmsnorm_row(const float* x, const float* __r
     }
 }
 
+// Rows of up to 4096 columns: every thread keeps its sixteen elements in registers and fetches their weights before
+// the sum is joined, so the row is read once and the weights' latency runs under the reduction.  r: the residual to
+// add first (x_io = x + r is written back), or null.  Same operations on the same values, in the same order, as the
+// general path (thread t: columns t, t + 256, ...).
+__device__ __forceinline__ void cta_add_rmsnorm_row_4096(float* x_io, const float* x, const float* r, const float* __restrict__ w,
+                                                         float* y, int cols, float eps)
+{
+    __shared__ double s_part[8];
+    float v[16], wv[16];
+    double t = 0.0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const int c = (int)threadIdx.x + 256 * i;
+        v[i] = c < cols ? x[c] : 0.0f;
+        wv[i] = (w && c < cols) ? w[c] : 1.0f;
+    }
+    if (r) {
+        float rv[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int c = (int)threadIdx.x + 256 * i;
+            rv[i] = c < cols ? r[c] : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int c = (int)threadIdx.x + 256 * i;
+            if (c < cols) {
+                v[i] = __fadd_rn(v[i], rv[i]);
+                x_io[c] = v[i];
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++)
+        if ((int)threadIdx.x + 256 * i < cols) t += (double)v[i] * (double)v[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = t;
+    __syncthreads();
+    double tot = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) tot += s_part[i];
+    const float mean = (float)(tot / (double)cols);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const int c = (int)threadIdx.x + 256 * i;
+        if (c < cols) {
+            const float u = __fmul_rn(v[i], scale);
+            y[c] = w ? __fmul_rn(u, wv[i]) : u;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) k_rmsnorm_llama(const float* in, const float* __restrict__ w, float* out, int cols, float eps)
 {
     pdl_launch_dependents();
     pdl_wait();
+    if (cols <= 4096) {
+        cta_add_rmsnorm_row_4096(nullptr, in + (size_t)blockIdx.x * cols, nullptr, w, out + (size_t)blockIdx.x * cols, cols, eps);
+        return;
+    }
     const float* x = in + (size_t)blockIdx.x * cols;
     double t = 0.0;
     for (int c = threadIdx.x; c < cols; c += 256) {
@@ -79,6 +137,10 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_llama(float* x_io, const fl
     pdl_wait();
     float* x = x_io + (size_t)blockIdx.x * cols;
     const float* rr = r + (size_t)blockIdx.x * cols;
+    if (cols <= 4096) {
+        cta_add_rmsnorm_row_4096(x, x, rr, w, out + (size_t)blockIdx.x * cols, cols, eps);
+        return;
+    }
     double t = 0.0;
     for (int c0 = threadIdx.x; c0 < cols; c0 += 256 * 8) {
         float xv[8], rv[8];
