@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const float* q, const void* kc
         if (vec_ok) {
             const uint4* p = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(kc) + row * (F16 ? 2 : 4));
             for (int j = 0; j < head_dim / kVec; j++) {
-                const uint4 w = __ldg(p + j);
+                const uint4 w = __ldcg(p + j);     // the cache rows may have been written by the launch before this one
                 float kf[kVec];
                 if (F16) {
                     const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
@@ -355,7 +355,15 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const float* q, const void* kc
     __syncthreads();
     if (tid == 0) {
         float t = 0.0f;
-        for (int ic = 0; ic < n_kv; ic++) t = __fadd_rn(t, scores[ic]);
+        int ic = 0;
+        for (; ic + 8 <= n_kv; ic += 8) {            // eight loads in flight, the additions in index order
+            float e[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) e[i] = scores[ic + i];
+#pragma unroll
+            for (int i = 0; i < 8; i++) t = __fadd_rn(t, e[i]);
+        }
+        for (; ic < n_kv; ic++) t = __fadd_rn(t, scores[ic]);
         s_red[0] = t;
     }
     __syncthreads();
@@ -365,7 +373,15 @@ __global__ void __launch_bounds__(256) k_gqa_attn(const float* q, const void* kc
     __syncthreads();
     for (int d = tid; d < head_dim; d += 256) {
         float acc = 0.0f;
-        for (int ic = 0; ic < n_kv; ic++)
+        int ic = 0;
+        for (; ic + 8 <= n_kv; ic += 8) {            // eight rows' loads in flight, the additions in index order
+            float e[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) e[i] = load(vc, ((size_t)(ic + i) * n_kv_heads + kv_head) * head_dim + d);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc = __fadd_rn(acc, __fmul_rn(e[i], scores[ic + i]));
+        }
+        for (; ic < n_kv; ic++)
             acc = __fadd_rn(acc, __fmul_rn(load(vc, ((size_t)ic * n_kv_heads + kv_head) * head_dim + d), scores[ic]));
         pdst[d] = acc;
     }
